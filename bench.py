@@ -1,0 +1,343 @@
+"""Benchmark of the quantized-expert hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens M] [--impl reference]
+
+Workload (BASELINE.json configs[1]): one Mixtral expert FFN, HQQ 2-bit / group 16 with
+8-bit scale and zero in groups of 256 — w1, w3 14336x4096 and w2 4096x14336 quantised from
+bf16 N(0, 0.02^2) weights (seeded), activations bf16 N(0, 1).  A step is one pass of
+y = w2(silu(w1 x) * w3 x) over a batch of M tokens (default 1: decode at batch 1).  Steps
+rotate over a pool of distinct experts larger than L2, so every step streams its weights
+from HBM.  With N GPUs each rank runs its own experts on its own tokens (experts are
+independent; no data-path collective) and the value is the sum over ranks.
+
+One JSON line is printed by rank 0; see DESIGN.md for the meaning of each key.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HIDDEN, FFN = 4096, 14336
+NBITS, GROUP = 2, 16
+POOL = 8                                     # distinct experts rotated through: 8 x 66.4 MB = 531 MB > 126 MB L2
+METRIC = "decode_tokens_per_s_expert_ffn"
+UNIT = "tok/s"
+
+
+def layer_bytes(N, K, nbits=NBITS, group=GROUP):
+    """Algorithmic weight-side bytes of one layer: packed codes + scale_q + zero_q + fp16 meta."""
+    G = N // group
+    codes = {2: N // 4 * K, 4: N // 2 * K, 3: (N + 9) // 10 * K * 4}[nbits]
+    return codes + 2 * G * K + 4 * 2 * (G * K // 256)
+
+
+EXPERT_BYTES = 2 * layer_bytes(FFN, HIDDEN) + layer_bytes(HIDDEN, FFN)
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def workload_name(tokens):
+    return (f"configs[1]: one Mixtral expert FFN, HQQ 2-bit g16 + 8-bit scale/zero g256 "
+            f"(w1,w3 14336x4096; w2 4096x14336), tokens={tokens}")
+
+
+# --------------------------------------------------------------------------- reference / CPU arm
+def oracle_dict(layer):
+    m = layer.meta
+    return dict(N=m["shape"][0], K=m["shape"][1], nbits=m["nbits"], group_size=m["group_size"], meta_group=256,
+                W_q=layer.W_q.cpu().numpy(), scale_q=m["scale_q"].cpu().numpy().reshape(-1),
+                zero_q=m["zero_q"].cpu().numpy().reshape(-1),
+                ms_scale=m["meta_scale"]["scale"].cpu().numpy().reshape(-1),
+                mz_scale=m["meta_scale"]["zero"].cpu().numpy().reshape(-1),
+                ms_zero=m["meta_zero"]["scale"].cpu().numpy().reshape(-1),
+                mz_zero=m["meta_zero"]["zero"].cpu().numpy().reshape(-1))
+
+
+def cpu_expert_dicts(seed=0, ffn=FFN):
+    """The same expert the GPU arm builds (for ffn == FFN), quantised on the CPU by the oracle."""
+    from oracle import hqq_oracle as O
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for N, K in ((ffn, HIDDEN), (HIDDEN, ffn), (ffn, HIDDEN)):
+        W = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+        out.append(O.quantize(W, NBITS, GROUP, 256))
+    return out
+
+
+def time_cpu_expert(ods, tokens, steps, warmup):
+    """dequantize() + matmul of the reference's CPU-runnable path (custom_layers.py:95-116,
+    253-256), torch's own threading; returns seconds per step."""
+    from oracle import hqq_oracle as O
+    x = torch.randn(tokens, HIDDEN, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
+    for _ in range(warmup):
+        O.reference_cpu_expert(x, *ods)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        O.reference_cpu_expert(x, *ods)
+    return (time.perf_counter() - t0) / steps
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    # One full pass tells how long a step is; if K steps would not fit in ~2 minutes, each step
+    # runs an expert with the intermediate size cut by `cut` (bytes and flops are linear in it)
+    # and the time is scaled back.
+    ods = cpu_expert_dicts()
+    t_full = time_cpu_expert(ods, args.tokens, 1, 1)
+    cut = 1
+    while cut < 16 and (args.steps + args.warmup) * t_full / cut > 120.0:
+        cut *= 2
+    if cut > 1:
+        ods = cpu_expert_dicts(ffn=FFN // cut)
+    sec = time_cpu_expert(ods, args.tokens, args.steps, args.warmup) * cut
+    value = args.tokens / sec
+    cores = torch.get_num_threads()
+    sample = (f"{args.steps} passes of {args.tokens} token(s) after {args.warmup} warm-up; each pass an expert FFN "
+              f"with intermediate size {FFN // cut} (1/{cut} of 14336), time scaled by {cut}")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args.tokens), "path": "oracle port of the reference's torch CPU "
+                   "dequantize()+matmul (the reference tree itself does not travel to the GPU box)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                         "os_cpu_count": os.cpu_count()},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# --------------------------------------------------------------------------- GPU arm
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        self.file.close()
+        os.unlink(self.file.name)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), samples=len(sm))
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def build_pool(device, n_experts, seed0):
+    """Experts built through the package's own constructors from seeded N(0, 0.02^2) weights."""
+    from mixtral_offloading_b200 import BaseQuantizeConfig, MixtralExpertWrapper, QuantConfig, make_empty_expert
+
+    class ModelCfg:
+        hidden_size, intermediate_size, num_local_experts, num_experts_per_tok, hidden_act = HIDDEN, FFN, 8, 2, "silu"
+    ffn_cfg = BaseQuantizeConfig(nbits=NBITS, group_size=GROUP, quant_zero=True, quant_scale=True)
+    qc = QuantConfig(ffn_config=ffn_cfg, attn_config=BaseQuantizeConfig(nbits=4, group_size=64, quant_zero=True,
+                                                                       quant_scale=True))
+    pool = []
+    for e in range(n_experts):
+        g = torch.Generator(device="cpu").manual_seed(seed0 + e)
+        expert = make_empty_expert(ModelCfg, qc)
+        for name in ("w1", "w2", "w3"):
+            lyr = getattr(expert, name)
+            N, K = lyr.meta["shape"]
+            if e == 0:      # expert 0 is the one the CPU baseline also builds: identical values
+                W = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16).to(device)
+            else:
+                W = (torch.randn(N, K, device=device) * 0.02).to(torch.bfloat16)
+            lyr.quantize(W, **lyr.quant_config)
+            del W
+        pool.append(MixtralExpertWrapper(expert, device))
+    return pool
+
+
+def run_b200(args):
+    from mixtral_offloading_b200 import _cabi
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _cabi.lib()
+    torch.manual_seed(1234 + rank)
+    pool = build_pool(dev, POOL, seed0=0)
+    M = args.tokens
+    x_host = torch.randn(M, HIDDEN, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).pin_memory()
+    y_host = torch.empty(M, HIDDEN, dtype=torch.bfloat16).pin_memory()
+    x = x_host.to(dev)
+    stream = torch.cuda.current_stream(dev)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident throughput: K steps back to back
+    for i in range(args.warmup):
+        pool[i % POOL](x)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    launches0 = lib.hqm_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for i in range(args.steps):
+        y = pool[i % POOL](x)
+    ev1.record(stream)
+    barrier()
+    launches = lib.hqm_launch_count() - launches0
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    ms_step = ms_total / args.steps
+
+    # ---- end to end through the public module call: host input, host result, every step
+    for i in range(min(args.warmup, 3)):
+        pool[i % POOL](x_host.to(dev, non_blocking=True)).cpu()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(args.steps):
+        xd = x_host.to(dev, non_blocking=True)
+        y_host.copy_(pool[i % POOL](xd), non_blocking=True)
+        stream.synchronize()
+    e1.record(stream)
+    barrier()
+    e2e_ms_step = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+
+    # ---- the dominant kernel alone: one quantized linear (w1 / w3 shape), rotating over the pool
+    layers = [getattr(w._expert, n) for w in pool for n in ("w1", "w3")]
+    reps = max(args.steps, 32)
+    for l in layers[:4]:
+        l(x)
+    barrier()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record(stream)
+    for i in range(reps):
+        layers[i % len(layers)](x)
+    k1.record(stream)
+    barrier()
+    clocks = sampler.stop() if sampler is not None else None
+    kernel_ms = k0.elapsed_time(k1) / reps
+    lin_bytes = layer_bytes(FFN, HIDDEN) + 2 * M * (HIDDEN + FFN)
+    peak, peak_kind = measured_peak()
+    achieved = lin_bytes / (kernel_ms * 1e-3) / 1e9
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    # ---- CPU baseline on this box's host cores: expert 0, a bounded sample
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        ods = [oracle_dict(getattr(pool[0]._expert, n)) for n in ("w1", "w2", "w3")]
+        cpu_steps = 3
+        sec = time_cpu_expert(ods, M, cpu_steps, 1)
+        cpu = {"value": M / sec, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+               "sample": f"{cpu_steps} expert-FFN passes of {M} token(s) after 1 warm-up, expert 0 of the pool",
+               "os_cpu_count": os.cpu_count()}
+
+    value = world * M / (ms_step * 1e-3)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": workload_name(M), "l2": f"steps rotate over {POOL} distinct experts "
+                   f"({POOL * EXPERT_BYTES / 1e6:.0f} MB > 126 MB L2)", "per_gpu": "own experts, own tokens"},
+        "hbm_gbs_per_gpu_step": EXPERT_BYTES / (ms_step * 1e-3) / 1e9,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "kernel": "quantized linear 14336x4096 2-bit g16 (w1/w3 of the pool), "
+                     f"{reps} launches, CUDA events", "algorithmic_bytes": lin_bytes, "us_per_launch": kernel_ms * 1e3,
+                     "peak_kind": f"{peak_kind} HBM copy bandwidth", "frac_of_8tbs": achieved / 8000.0},
+        "cpu_baseline": cpu,
+        "e2e": {"value": world * M / (e2e_ms_step * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms_step,
+                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--tokens", type=int, default=1)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        args.steps = 3 if args.steps is None else args.steps
+        args.warmup = 1 if args.warmup is None else args.warmup
+        run_reference(args)
+    else:
+        args.steps = 200 if args.steps is None else args.steps
+        args.warmup = max(3, 8 if args.warmup is None else args.warmup)
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,168 @@
+/*
+ * hqq_moe.h — C ABI of the B200 (sm_100a) quantized-expert library.
+ *
+ * Every entry point takes plain pointers and sizes, returns an int status
+ * (HQM_OK = 0, negative = error; hqm_last_error() gives the message of the
+ * calling thread's last failure), never throws, and — unless its comment says
+ * otherwise — allocates no device memory: the caller owns every buffer and
+ * passes the CUDA stream (a cudaStream_t cast to void*) the work is queued on.
+ *
+ * Activations are bf16 (uint16_t bit patterns here), row-major, contiguous.
+ *
+ * Weight layout (the one the reference keeps in memory after repack(),
+ * src/custom_layers.py:41-47 and src/packing.py):
+ *   W is (N, K) = (out_features, in_features); K is the contiguous axis and the
+ *   packing runs along N: 4-bit uint8 (N/2, K), even row in the high nibble;
+ *   2-bit uint8 (N/4, K), row n%4==0 in bits 7-6; 3-bit int32 (ceil(N/10), K),
+ *   row n%10==i at bits 3*(9-i)+2..3*(9-i), rows past N zero.
+ *   scale/zero: one pair per (n % G, k), G = N / group_size
+ *   (src/triton_kernels.py:86-88,110-118); they are stored 8-bit (scale_q,
+ *   zero_q: G*K bytes each) and decoded as (q - mz[c]) * ms[c] with
+ *   c = (flat index) % (G*K / meta_group), ms/mz fp16 (src/custom_layers.py:62-66).
+ */
+#ifndef HQQ_MOE_H
+#define HQQ_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HQM_OK 0
+#define HQM_ERR_ARG (-1)      /* bad argument (null pointer, unsupported shape, misaligned buffer) */
+#define HQM_ERR_CUDA (-2)     /* a CUDA runtime call failed */
+#define HQM_ERR_SCRATCH (-3)  /* scratch buffer too small */
+#define HQM_ERR_STATE (-4)    /* cache protocol violated (re-entrant request, unknown uid, full) */
+
+/* One quantized linear layer: the tensors HQQLinearTritonSavable holds
+ * (src/custom_layers.py:139-162: W_q, meta.scale_q, meta.meta_scale.{scale,zero},
+ * meta.zero_q, meta.meta_zero.{scale,zero}) plus the non-tensor meta it reads in
+ * forward_triton (src/custom_layers.py:68-84: shape, nbits, group_size). */
+typedef struct hqm_weight {
+    int32_t N, K;             /* meta['shape'] */
+    int32_t nbits;            /* 2, 3 or 4 */
+    int32_t group_size;       /* rows per quantisation group (axis 0) */
+    int32_t meta_group;       /* group size of the 8-bit scale/zero quantisation (256) */
+    int32_t reserved;
+    const void* W_q;          /* packed codes, device pointer, 16-byte aligned */
+    const uint8_t* scale_q;   /* G*K */
+    const uint8_t* zero_q;    /* G*K */
+    const uint16_t* ms_scale; /* fp16, G*K/meta_group: meta_scale.scale */
+    const uint16_t* mz_scale; /* fp16: meta_scale.zero */
+    const uint16_t* ms_zero;  /* fp16: meta_zero.scale */
+    const uint16_t* mz_zero;  /* fp16: meta_zero.zero */
+} hqm_weight;
+
+const char* hqm_last_error(void);
+int hqm_version(void);
+/* Number of CUDA kernels this library has launched in the process so far (for benchmarks). */
+int64_t hqm_launch_count(void);
+
+/* ---- bit packing: src/packing.py --------------------------------------- */
+/* pack_4bit_u8_common, packing.py:10-17.  codes (N, K) uint8 -> packed (N/2, K). */
+int hqm_pack_4bit_u8(uint8_t* packed, const uint8_t* codes, int64_t N, int64_t K, void* stream);
+/* unpack_4bit_u8_common, packing.py:19-27.  packed (rows, K) -> codes (2*rows, K). */
+int hqm_unpack_4bit_u8(uint8_t* codes, const uint8_t* packed, int64_t rows, int64_t K, void* stream);
+/* pack_2bit_u8_common, packing.py:36-41.  codes (N, K) -> packed (N/4, K). */
+int hqm_pack_2bit_u8(uint8_t* packed, const uint8_t* codes, int64_t N, int64_t K, void* stream);
+/* unpack_2bit_u8_common, packing.py:43-53.  packed (rows, K) -> codes (4*rows, K). */
+int hqm_unpack_2bit_u8(uint8_t* codes, const uint8_t* packed, int64_t rows, int64_t K, void* stream);
+/* pack_3bit_i32_common, packing.py:62-81.  codes (N, K) -> packed (ceil(N/10), K) int32. */
+int hqm_pack_3bit_i32(int32_t* packed, const uint8_t* codes, int64_t N, int64_t K, void* stream);
+/* unpack_3bit_i32_common, packing.py:83-97.  packed (rows, K) -> codes (10*rows, K). */
+int hqm_unpack_3bit_i32(uint8_t* codes, const int32_t* packed, int64_t rows, int64_t K, void* stream);
+
+/* ---- quantized linear: src/custom_layers.py:49-116, src/triton_kernels.py -- */
+/* HQQLinearTritonSavable.dequantize, custom_layers.py:95-116: the full (N, K)
+ * weight.  out_dtype: 0 = bf16, 1 = fp16, 2 = fp32. */
+int hqm_dequantize(void* W_out, int out_dtype, const hqm_weight* w, void* stream);
+
+/* Bytes of scratch hqm_linear needs for M rows of this layer (0 if none). */
+size_t hqm_linear_scratch_bytes(int64_t M, const hqm_weight* w);
+
+/* HQQLinearTritonSavable.forward / forward_triton (custom_layers.py:49-92) with the
+ * kernels of triton_kernels.py:37-191 (4-bit), :225-380 (2-bit), :414-564 (3-bit)
+ * and the per-call 8-bit scale/zero decode fused in:
+ *   y[M, N] = x[M, K] . W_est^T (+ bias[N]),  fp32 accumulation, bf16 in/out.
+ * bias may be NULL.  scratch may be NULL when hqm_linear_scratch_bytes() is 0. */
+int hqm_linear(uint16_t* y, const uint16_t* x, int64_t M, const hqm_weight* w, const uint16_t* bias,
+               void* scratch, size_t scratch_bytes, void* stream);
+
+/* ---- expert FFN: src/custom_layers.py:243-256 and :297-312 --------------- */
+/* Bytes of scratch hqm_expert_ffn needs for M routed rows. */
+size_t hqm_expert_ffn_scratch_bytes(int64_t M, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3);
+
+/* MixtralBLockSparseTop2MLP_HQQ.forward (custom_layers.py:253-256) for the rows an
+ * expert was routed, fused with the gather / routing-weight / index_add_ of
+ * SparseMoeWrapper.forward (custom_layers.py:297-312):
+ *   for i < M:  t = token_idx ? token_idx[i] : i
+ *     h = w2( silu(w1 x[t]) * w3 x[t] )
+ *     out[t] = (accumulate ? out[t] : 0) + (route_w ? route_w[i] : 1) * h
+ * x and out are (tokens, hidden) bf16; token_idx int32[M] with distinct entries;
+ * route_w float[M]. */
+int hqm_expert_ffn(uint16_t* out, const uint16_t* x, int64_t M, const int32_t* token_idx, const float* route_w,
+                   int accumulate, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3,
+                   void* scratch, size_t scratch_bytes, void* stream);
+
+/* ---- router: src/custom_layers.py:276-302 --------------------------------- */
+/* Gate linear, fp32 softmax, top-2, renormalise (custom_layers.py:276-282) and the
+ * per-expert token lists that one_hot/where build (custom_layers.py:290,297-302).
+ *   x (M, K) bf16, gate_w (E, K) bf16, E <= 32.
+ *   router_logits (M, E) bf16; topk_w (M, 2) float, rounded to bf16 as :282 casts;
+ *   topk_idx (M, 2) int32; counts int32[E]; offsets int32[E+1];
+ *   token_idx int32[2M] and token_w float[2M]: expert e owns
+ *   [offsets[e], offsets[e+1]), tokens ascending. */
+int hqm_router_top2(uint16_t* router_logits, float* topk_w, int32_t* topk_idx, int32_t* counts, int32_t* offsets,
+                    int32_t* token_idx, float* token_w, const uint16_t* x, const uint16_t* gate_w, int64_t M,
+                    int64_t K, int32_t E, void* stream);
+
+/* ---- expert residency: src/expert_cache.py -------------------------------- */
+/* ExpertCache (expert_cache.py:55-201).  The handle owns the bookkeeping of
+ * ExpertInfo / EvictionGroupInfo (expert_cache.py:12-52), a side copy stream and
+ * the events that order it against the compute stream.  Slab memory stays with
+ * the caller: `device_slabs` are main_size + buffer_size device buffers,
+ * `host_slabs` one pinned buffer per registered expert (weights are immutable, so
+ * an evicted expert is not copied back as expert_cache.py:189 does; its host copy
+ * is still valid).  Passing NULL for both arrays gives a bookkeeping-only handle
+ * (no CUDA calls), which is what the CPU tests drive. */
+typedef struct hqm_cache hqm_cache;
+
+int hqm_cache_create(hqm_cache** out, int32_t main_size, int32_t offload_size, int32_t buffer_size,
+                     size_t slab_bytes, void* const* device_slabs, int32_t device_id);
+void hqm_cache_destroy(hqm_cache* c);
+
+/* add_expert_storage, expert_cache.py:93-118.  uid is any caller-chosen 64-bit key.
+ * offload: 0 = device, 1 = host, -1 = device if room else host (None).
+ * host_slab: this expert's pinned copy (may be NULL for a bookkeeping-only handle);
+ * when the expert is placed on the device its bytes are copied there on `stream`.
+ * *placed_offloaded receives 0/1.  HQM_ERR_STATE "Cache is full" when nothing fits. */
+int hqm_cache_add(hqm_cache* c, int64_t uid, int32_t eviction_group, int32_t offload, const void* host_slab,
+                  int32_t* placed_offloaded, void* stream);
+
+/* load_experts, expert_cache.py:120-179, split into begin / next / end because a C
+ * ABI has no generators.  begin: validates (distinct uids, one group, not
+ * re-entrant), marks all as used, issues the first window of host->device copies
+ * on the copy stream.  order_out receives the uids in the order they will be
+ * yielded. */
+int hqm_cache_begin(hqm_cache* c, const int64_t* uids, int32_t n, int32_t unordered, int64_t* order_out,
+                    void* compute_stream);
+/* Yields the next expert: *uid_out, and *slab_out = the device slab its bytes are
+ * (or will be, in stream order) in.  The compute stream is made to wait for the
+ * copy that fills it; the previous expert's compute is fenced so its slab can be
+ * reused; one more copy is issued as expert_cache.py:171-175 does.  Returns 1 when
+ * nothing is left (and then behaves as hqm_cache_end). */
+int hqm_cache_next(hqm_cache* c, int64_t* uid_out, void** slab_out, int32_t* slot_out, void* compute_stream);
+int hqm_cache_end(hqm_cache* c, void* compute_stream);
+
+/* hits / misses of a group (expert_cache.py:25-26) and copy counters. */
+int hqm_cache_stats(hqm_cache* c, int32_t eviction_group, int64_t* hits, int64_t* misses, int64_t* h2d_bytes,
+                    int64_t* swaps);
+/* The group's resident uids, least recently used first; returns how many. */
+int hqm_cache_resident(hqm_cache* c, int32_t eviction_group, int64_t* uids_out, int32_t cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HQQ_MOE_H */

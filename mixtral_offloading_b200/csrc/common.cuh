@@ -1,0 +1,84 @@
+// Shared helpers for the sm_100a kernels: error reporting, dtype conversion,
+// layout arithmetic of the packed weight format.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/hqq_moe.h"
+
+namespace hqm {
+
+// Message of the calling thread's last failure (returned by hqm_last_error()).
+void set_error(const char* fmt, ...);
+// Counts kernel launches made by the library (read by hqm_launch_count()).
+void count_launch();
+
+#define HQM_CHECK_ARG(cond, ...)          \
+    do {                                  \
+        if (!(cond)) {                    \
+            hqm::set_error(__VA_ARGS__);  \
+            return HQM_ERR_ARG;           \
+        }                                 \
+    } while (0)
+
+#define HQM_CUDA(call)                                                                    \
+    do {                                                                                  \
+        cudaError_t e_ = (call);                                                          \
+        if (e_ != cudaSuccess) {                                                          \
+            hqm::set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
+            return HQM_ERR_CUDA;                                                          \
+        }                                                                                 \
+    } while (0)
+
+#define HQM_LAUNCH_CHECK()                                                                \
+    do {                                                                                  \
+        cudaError_t e_ = cudaGetLastError();                                              \
+        hqm::count_launch();                                                              \
+        if (e_ != cudaSuccess) {                                                          \
+            hqm::set_error("kernel launch failed: %s (%s:%d)", cudaGetErrorString(e_), __FILE__, __LINE__); \
+            return HQM_ERR_CUDA;                                                          \
+        }                                                                                 \
+    } while (0)
+
+__host__ __device__ constexpr int codes_per_word(int nbits) { return nbits == 2 ? 4 : (nbits == 4 ? 2 : 10); }
+
+// Storage rows of W_q for N output rows.
+__host__ __device__ inline int64_t storage_rows(int64_t N, int nbits) {
+    int per = codes_per_word(nbits);
+    return (N + per - 1) / per;
+}
+
+// Validates a weight descriptor; fills G (groups along N) and C (columns of the
+// (meta_group, C) view of the flat scale/zero vector).
+int check_weight(const hqm_weight* w, int* G, int* C);
+
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }
+__device__ __forceinline__ float f16_bits_to_float(uint16_t b) { return __half2float(__ushort_as_half(b)); }
+__device__ __forceinline__ uint16_t float_to_bf16_bits(float f) { return __bfloat16_as_ushort(__float2bfloat16_rn(f)); }
+__device__ __forceinline__ float round_bf16(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Streaming 16-byte load that does not pollute L1 (weights are read exactly once).
+__device__ __forceinline__ uint4 ld_stream_16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_stream_4(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+}  // namespace hqm

@@ -1,0 +1,93 @@
+// Expert FFN: w2( silu(w1 x) * w3 x ), with the gather of the routed rows in
+// front and the routing-weight scale + accumulate into the MoE output behind
+// (MixtralBLockSparseTop2MLP_HQQ.forward and the per-expert body of
+// SparseMoeWrapper.forward in the reference's custom_layers.py).
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace hqm {
+
+// h = silu(a) * b, in place in a.  Both operands are the bf16 outputs of the
+// w1 / w3 linears, the product is rounded to bf16 as the reference rounds to fp16.
+__global__ void silu_mul_kernel(uint16_t* __restrict__ a, const uint16_t* __restrict__ b, int64_t n) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const float av = bf16_bits_to_float(a[i]), bv = bf16_bits_to_float(b[i]);
+        const float act = round_bf16(av / (1.f + __expf(-av)));
+        a[i] = float_to_bf16_bits(act * bv);
+    }
+}
+
+// out[t] = (accumulate ? out[t] : 0) + w_i * y[i]; one expert touches a token at
+// most once, so plain read-modify-write is race free.
+__global__ void scale_scatter_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ y,
+                                     const int32_t* __restrict__ token_idx, const float* __restrict__ route_w,
+                                     int64_t M, int H, int accumulate) {
+    const int64_t total = M * H;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / H;
+        const int h = (int)(i % H);
+        const int64_t t = token_idx ? token_idx[m] : m;
+        const float wgt = route_w ? route_w[m] : 1.f;
+        const float v = round_bf16(bf16_bits_to_float(y[i]) * wgt);
+        uint16_t* dst = out + t * H + h;
+        *dst = float_to_bf16_bits(accumulate ? bf16_bits_to_float(*dst) + v : v);
+    }
+}
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace hqm
+
+extern "C" {
+
+size_t hqm_expert_ffn_scratch_bytes(int64_t M, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3) {
+    if (!w1 || !w2 || !w3 || M <= 0) return 0;
+    const size_t a = hqm::align_up((size_t)M * (size_t)w1->N * 2, 256);
+    const size_t b = hqm::align_up((size_t)M * (size_t)w3->N * 2, 256);
+    const size_t c = hqm::align_up((size_t)M * (size_t)w2->N * 2, 256);
+    return a + b + c;
+}
+
+int hqm_expert_ffn(uint16_t* out, const uint16_t* x, int64_t M, const int32_t* token_idx, const float* route_w,
+                   int accumulate, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3, void* scratch,
+                   size_t scratch_bytes, void* stream) {
+    using namespace hqm;
+    HQM_CHECK_ARG(M >= 0 && M <= INT32_MAX, "expert_ffn: bad row count %lld", (long long)M);
+    if (M == 0) return HQM_OK;
+    HQM_CHECK_ARG(out && x && w1 && w2 && w3, "expert_ffn: null pointer");
+    HQM_CHECK_ARG(w1->N == w3->N && w1->K == w3->K, "expert_ffn: w1 (%d,%d) and w3 (%d,%d) differ", w1->N, w1->K,
+                  w3->N, w3->K);
+    HQM_CHECK_ARG(w2->K == w1->N && w2->N == w1->K, "expert_ffn: w2 (%d,%d) does not map (%d) back to (%d)", w2->N,
+                  w2->K, w1->N, w1->K);
+    const size_t need = hqm_expert_ffn_scratch_bytes(M, w1, w2, w3);
+    if (scratch == nullptr || scratch_bytes < need) {
+        set_error("expert_ffn: scratch of %zu bytes given, %zu needed", scratch_bytes, need);
+        return HQM_ERR_SCRATCH;
+    }
+    HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "expert_ffn: scratch must be 256-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int F = w1->N, H = w2->N;
+    uint8_t* p = (uint8_t*)scratch;
+    uint16_t* a = (uint16_t*)p;
+    p += align_up((size_t)M * F * 2, 256);
+    uint16_t* b = (uint16_t*)p;
+    p += align_up((size_t)M * F * 2, 256);
+    uint16_t* c = (uint16_t*)p;
+
+    int rc = launch_linear(a, x, token_idx, M, w1, nullptr, st);
+    if (rc != HQM_OK) return rc;
+    rc = launch_linear(b, x, token_idx, M, w3, nullptr, st);
+    if (rc != HQM_OK) return rc;
+    const int64_t nf = M * F;
+    silu_mul_kernel<<<(int)((nf + 255) / 256 > 148 * 8 ? 148 * 8 : (nf + 255) / 256), 256, 0, st>>>(a, b, nf);
+    HQM_LAUNCH_CHECK();
+    rc = launch_linear(c, a, nullptr, M, w2, nullptr, st);
+    if (rc != HQM_OK) return rc;
+    const int64_t nh = M * H;
+    scale_scatter_kernel<<<(int)((nh + 255) / 256 > 148 * 8 ? 148 * 8 : (nh + 255) / 256), 256, 0, st>>>(
+        out, c, token_idx, route_w, M, H, accumulate);
+    HQM_LAUNCH_CHECK();
+    return HQM_OK;
+}
+
+}  // extern "C"

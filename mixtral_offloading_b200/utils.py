@@ -1,0 +1,32 @@
+"""Helpers that define orderings the rest of the package relies on."""
+from __future__ import annotations
+
+from contextlib import contextmanager
+
+import torch
+
+
+def nested_flatten(t):
+    """Depth-first leaves of nested lists / tuples / dicts, dict entries by sorted key.
+
+    This is the order in which the reference lays an expert's tensors into its slab
+    (src/utils.py:34-45 as used by src/expert_wrapper.py:52-66)."""
+    if isinstance(t, (list, tuple)):
+        for item in t:
+            yield from nested_flatten(item)
+    elif isinstance(t, dict):
+        for key in sorted(t):
+            yield from nested_flatten(t[key])
+    else:
+        yield t
+
+
+@contextmanager
+def with_default_dtype(dtype):
+    """src/utils.py:93-101."""
+    saved = torch.get_default_dtype()
+    torch.set_default_dtype(dtype)
+    try:
+        yield
+    finally:
+        torch.set_default_dtype(saved)

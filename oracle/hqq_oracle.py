@@ -214,10 +214,13 @@ def expert_ffn(x: torch.Tensor, w1: dict, w2: dict, w3: dict, round_to=torch.bfl
     return rnd(linear(h, w2))
 
 
-def router_top2(x: torch.Tensor, gate_w: torch.Tensor, top_k: int = 2):
-    """SparseMoeWrapper.forward, custom_layers.py:276-282: gate linear, fp32 softmax,
-    top-k, renormalise.  Returns (router_logits, weights, expert indices)."""
+def router_top2(x: torch.Tensor, gate_w: torch.Tensor, top_k: int = 2, round_to=None):
+    """SparseMoeWrapper.forward, custom_layers.py:276-282: gate linear (whose output the
+    reference holds in the activation dtype, hence round_to), fp32 softmax, top-k,
+    renormalise.  Returns (router_logits, weights, expert indices)."""
     logits = x.to(torch.float32) @ gate_w.to(torch.float32).T
+    if round_to is not None:
+        logits = logits.to(round_to).to(torch.float32)
     probs = torch.softmax(logits, dim=1, dtype=torch.float32)
     w, idx = torch.topk(probs, top_k, dim=-1)
     w = w / w.sum(dim=-1, keepdim=True)
@@ -227,7 +230,7 @@ def router_top2(x: torch.Tensor, gate_w: torch.Tensor, top_k: int = 2):
 def moe_forward(x: torch.Tensor, gate_w: torch.Tensor, experts: list, round_to=torch.bfloat16):
     """SparseMoeWrapper.forward, custom_layers.py:272-314, with every expert resident.
     `experts` is a list of (w1, w2, w3) layer dictionaries."""
-    logits, w, idx = router_top2(x, gate_w)
+    logits, w, idx = router_top2(x, gate_w, round_to=round_to)
     if round_to is not None:
         w = w.to(round_to).to(torch.float32)                              # custom_layers.py:282
     out = torch.zeros(x.shape[0], x.shape[1], dtype=torch.float32)
