@@ -11,8 +11,9 @@ namespace hqm {
 
 __device__ __forceinline__ void decode_scale_zero(const hqm_weight& w, int64_t idx, int C, float& s, float& z) {
     const int col = (int)(idx % C);
-    s = ((float)w.scale_q[idx] - f16_bits_to_float(w.mz_scale[col])) * f16_bits_to_float(w.ms_scale[col]);
-    z = ((float)w.zero_q[idx] - f16_bits_to_float(w.mz_zero[col])) * f16_bits_to_float(w.ms_zero[col]);
+    // explicit rounding steps (no fused multiply-add) so the fp32 result equals the CPU restatement bit for bit
+    s = __fmul_rn(__fsub_rn((float)w.scale_q[idx], f16_bits_to_float(w.mz_scale[col])), f16_bits_to_float(w.ms_scale[col]));
+    z = __fmul_rn(__fsub_rn((float)w.zero_q[idx], f16_bits_to_float(w.mz_zero[col])), f16_bits_to_float(w.ms_zero[col]));
 }
 
 template <int NBITS>
@@ -116,7 +117,7 @@ __global__ void dequantize_kernel(T* __restrict__ out, hqm_weight w, int G, int 
                 const float code = (float)((word >> (NBITS * (PER - 1 - s))) & MASK);
                 float sc, zr;
                 decode_scale_zero(w, (n % G) * w.K + k, C, sc, zr);
-                out[n * w.K + k] = cast_out<T>((code - zr) * sc);
+                out[n * w.K + k] = cast_out<T>(__fmul_rn(__fsub_rn(code, zr), sc));
             }
         }
     }

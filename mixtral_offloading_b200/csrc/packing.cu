@@ -131,9 +131,9 @@ static inline bool aligned4(const void* p) { return (reinterpret_cast<uintptr_t>
 
 template <int BITS, int PER>
 static int unpack_u8(uint8_t* codes, const uint8_t* packed, int64_t rows, int64_t K, void* stream) {
-    HQM_CHECK_ARG(codes && packed, "unpack: null pointer");
     HQM_CHECK_ARG(rows >= 0 && K >= 0, "unpack: negative size");
     if (rows == 0 || K == 0) return HQM_OK;
+    HQM_CHECK_ARG(codes && packed, "unpack: null pointer");
     cudaStream_t st = (cudaStream_t)stream;
     if (K % 16 == 0 && aligned16(codes) && aligned16(packed)) {
         unpack_u8_kernel<BITS, PER, uint4><<<grid_for(rows * (K / 16), 256), 256, 0, st>>>(codes, packed, rows, K);
@@ -146,9 +146,9 @@ static int unpack_u8(uint8_t* codes, const uint8_t* packed, int64_t rows, int64_
 
 template <int BITS, int PER>
 static int pack_u8(uint8_t* packed, const uint8_t* codes, int64_t N, int64_t K, void* stream) {
-    HQM_CHECK_ARG(codes && packed, "pack: null pointer");
     HQM_CHECK_ARG(N >= 0 && K >= 0 && N % PER == 0, "pack: the row count must be a multiple of %d", PER);
     if (N == 0 || K == 0) return HQM_OK;
+    HQM_CHECK_ARG(codes && packed, "pack: null pointer");
     const int64_t rows = N / PER;
     cudaStream_t st = (cudaStream_t)stream;
     if (K % 16 == 0 && aligned16(codes) && aligned16(packed)) {
@@ -179,9 +179,9 @@ int hqm_unpack_2bit_u8(uint8_t* codes, const uint8_t* packed, int64_t rows, int6
 
 int hqm_pack_3bit_i32(int32_t* packed, const uint8_t* codes, int64_t N, int64_t K, void* stream) {
     using namespace hqm;
-    HQM_CHECK_ARG(codes && packed, "pack_3bit: null pointer");
     HQM_CHECK_ARG(N >= 0 && K >= 0, "pack_3bit: negative size");
     if (N == 0 || K == 0) return HQM_OK;
+    HQM_CHECK_ARG(codes && packed, "pack_3bit: null pointer");
     HQM_CHECK_ARG(aligned4(packed), "pack_3bit: packed must be 4-byte aligned");
     const int64_t rows = (N + 9) / 10;
     cudaStream_t st = (cudaStream_t)stream;
@@ -196,9 +196,9 @@ int hqm_pack_3bit_i32(int32_t* packed, const uint8_t* codes, int64_t N, int64_t 
 
 int hqm_unpack_3bit_i32(uint8_t* codes, const int32_t* packed, int64_t rows, int64_t K, void* stream) {
     using namespace hqm;
-    HQM_CHECK_ARG(codes && packed, "unpack_3bit: null pointer");
     HQM_CHECK_ARG(rows >= 0 && K >= 0, "unpack_3bit: negative size");
     if (rows == 0 || K == 0) return HQM_OK;
+    HQM_CHECK_ARG(codes && packed, "unpack_3bit: null pointer");
     HQM_CHECK_ARG(aligned4(packed), "unpack_3bit: packed must be 4-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
     if (K % 4 == 0 && aligned16(packed) && aligned4(codes)) {

@@ -39,7 +39,8 @@ def test_argument_errors_are_reported_not_raised_in_c(lib):
     with pytest.raises(ValueError):
         _cabi.check(_cabi.HQM_ERR_ARG)
     assert lib.hqm_pack_4bit_u8(None, None, 3, 16, None) == _cabi.HQM_ERR_ARG      # odd row count
-    assert lib.hqm_unpack_2bit_u8(None, None, 0, 0, None) == _cabi.HQM_ERR_ARG     # null pointers
+    assert lib.hqm_unpack_2bit_u8(None, None, 4, 16, None) == _cabi.HQM_ERR_ARG    # null pointers
+    assert lib.hqm_unpack_2bit_u8(None, None, 0, 16, None) == 0                    # nothing to do
 
 
 class PolicyHandle:
