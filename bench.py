@@ -200,6 +200,19 @@ def build_pool(device, n_experts, seed0):
     return pool
 
 
+def profile_linear(args):
+    """A few launches of the dominant kernel on HBM-cold weights, nothing else (for ncu)."""
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    pool = build_pool(dev, 2, seed0=0)                      # 2 experts = 6 layers = 133 MB > 126 MB L2
+    layers = [getattr(w._expert, n) for w in pool for n in ("w1", "w3")]
+    x = torch.randn(args.tokens, HIDDEN, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(dev)
+    for i in range(args.profile_linear):
+        layers[i % len(layers)](x)
+    torch.cuda.synchronize(dev)
+    print(json.dumps({"profile_linear": args.profile_linear, "tokens": args.tokens}))
+
+
 def run_b200(args):
     from mixtral_offloading_b200 import _cabi
 
@@ -219,7 +232,6 @@ def run_b200(args):
     x_host = torch.randn(M, HIDDEN, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).pin_memory()
     y_host = torch.empty(M, HIDDEN, dtype=torch.bfloat16).pin_memory()
     x = x_host.to(dev)
-    stream = torch.cuda.current_stream(dev)
 
     def barrier():
         torch.cuda.synchronize(dev)
@@ -234,32 +246,47 @@ def run_b200(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- device-resident throughput: K steps back to back
+    def capture(fn):
+        """Record fn() into a CUDA graph (the launch-bound loop is replayed, not re-issued from Python)."""
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        return graph
+
+    # ---- device-resident throughput: K steps back to back, replayed as one CUDA graph
     for i in range(args.warmup):
         pool[i % POOL](x)
+    torch.cuda.synchronize(dev)
+    launches0 = lib.hqm_launch_count()
+    steps_graph = capture(lambda: [pool[i % POOL](x) for i in range(args.steps)])
+    launches = lib.hqm_launch_count() - launches0
+    steps_graph.replay()
     barrier()
     sampler = ClockSampler(local) if rank == 0 else None
-    launches0 = lib.hqm_launch_count()
+    stream = torch.cuda.current_stream(dev)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record(stream)
-    for i in range(args.steps):
-        y = pool[i % POOL](x)
+    steps_graph.replay()
     ev1.record(stream)
     barrier()
-    launches = lib.hqm_launch_count() - launches0
     ms_total = max_over_ranks(ev0.elapsed_time(ev1))
     ms_step = ms_total / args.steps
 
-    # ---- end to end through the public module call: host input, host result, every step
-    for i in range(min(args.warmup, 3)):
-        pool[i % POOL](x_host.to(dev, non_blocking=True)).cpu()
+    # ---- end to end through the public module call: host input in, host result out, every step
+    x_dev = torch.empty_like(x)
+
+    def one_step(i):
+        x_dev.copy_(x_host, non_blocking=True)
+        y_host.copy_(pool[i % POOL](x_dev), non_blocking=True)
+    step_graphs = [capture(lambda i=i: one_step(i)) for i in range(POOL)]
+    for gph in step_graphs[:3]:
+        gph.replay()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for i in range(args.steps):
-        xd = x_host.to(dev, non_blocking=True)
-        y_host.copy_(pool[i % POOL](xd), non_blocking=True)
-        stream.synchronize()
+        step_graphs[i % POOL].replay()
+        stream.synchronize()                       # the caller reads y_host here
     e1.record(stream)
     barrier()
     e2e_ms_step = max_over_ranks(e0.elapsed_time(e1)) / args.steps
@@ -269,11 +296,13 @@ def run_b200(args):
     reps = max(args.steps, 32)
     for l in layers[:4]:
         l(x)
+    torch.cuda.synchronize(dev)
+    lin_graph = capture(lambda: [layers[i % len(layers)](x) for i in range(reps)])
+    lin_graph.replay()
     barrier()
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     k0.record(stream)
-    for i in range(reps):
-        layers[i % len(layers)](x)
+    lin_graph.replay()
     k1.record(stream)
     barrier()
     clocks = sampler.stop() if sampler is not None else None
@@ -328,11 +357,16 @@ def main():
     ap.add_argument("--tokens", type=int, default=1)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-linear", type=int, default=0, metavar="N",
+                    help="only launch N quantized linears (w1 shape, rotating over 6 layers > L2) and exit; "
+                         "the small case meant to be run under ncu")
     args = ap.parse_args()
     if args.impl == "reference":
         args.steps = 3 if args.steps is None else args.steps
         args.warmup = 1 if args.warmup is None else args.warmup
         run_reference(args)
+    elif args.profile_linear:
+        profile_linear(args)
     else:
         args.steps = 200 if args.steps is None else args.steps
         args.warmup = max(3, 8 if args.warmup is None else args.warmup)

@@ -1,5 +1,6 @@
 // Error reporting, argument validation and the hqm_linear entry point.
 #include <stdarg.h>
+#include <stdlib.h>
 
 #include <atomic>
 
@@ -42,12 +43,44 @@ int check_weight(const hqm_weight* w, int* G, int* C) {
     return HQM_OK;
 }
 
+// HQM_FORCE_GENERIC=1 in the environment routes every linear through the shape-agnostic
+// kernel (used by the tests to check the two paths against each other).
+static bool force_generic() {
+    static const bool on = [] {
+        const char* v = getenv("HQM_FORCE_GENERIC");
+        return v && v[0] == '1';
+    }();
+    return on;
+}
+
+size_t linear_scratch_bytes(int64_t M, const hqm_weight* w) {
+    int G, C;
+    StreamPlan plan;
+    if (M <= 0 || check_weight(w, &G, &C) != HQM_OK) return 0;
+    if (!gemv_stream_plan(w, G, C, M, &plan)) return 0;
+    return (gemv_stream_scratch_bytes(plan, M, w->N) + 255) / 256 * 256;
+}
+
 int launch_linear(uint16_t* y, const uint16_t* x, const int32_t* x_idx, int64_t M, const hqm_weight* w,
-                  const uint16_t* bias, cudaStream_t st) {
+                  const uint16_t* bias, void* scratch, size_t scratch_bytes, cudaStream_t st) {
     int G, C;
     int rc = check_weight(w, &G, &C);
     if (rc != HQM_OK) return rc;
     if (M == 0) return HQM_OK;
+    StreamPlan plan;
+    const bool x_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+    if (!x_ok || force_generic()) return launch_linear_generic(y, x, x_idx, M, w, G, C, bias, st);
+    if (gemv_stream_plan(w, G, C, M, &plan)) {
+        const size_t need = gemv_stream_scratch_bytes(plan, M, w->N);
+        if (scratch == nullptr || scratch_bytes < need) {
+            set_error("linear: scratch of %zu bytes given, %zu needed", scratch_bytes, need);
+            return HQM_ERR_SCRATCH;
+        }
+        HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 15u) == 0, "linear: scratch must be 16-byte aligned");
+        rc = launch_gemv_stream_partials((float*)scratch, x, x_idx, M, w, G, C, plan, st);
+        if (rc != HQM_OK) return rc;
+        return launch_finalize_linear(y, (const float*)scratch, bias, M, w->N, plan.SK, st);
+    }
     return launch_linear_generic(y, x, x_idx, M, w, G, C, bias, st);
 }
 
@@ -59,20 +92,14 @@ const char* hqm_last_error(void) { return hqm::g_error; }
 int hqm_version(void) { return 1; }
 int64_t hqm_launch_count(void) { return (int64_t)hqm::launches(); }
 
-size_t hqm_linear_scratch_bytes(int64_t M, const hqm_weight* w) {
-    (void)M;
-    (void)w;
-    return 0;
-}
+size_t hqm_linear_scratch_bytes(int64_t M, const hqm_weight* w) { return hqm::linear_scratch_bytes(M, w); }
 
 int hqm_linear(uint16_t* y, const uint16_t* x, int64_t M, const hqm_weight* w, const uint16_t* bias, void* scratch,
                size_t scratch_bytes, void* stream) {
     using namespace hqm;
-    (void)scratch;
-    (void)scratch_bytes;
     HQM_CHECK_ARG(M >= 0 && M <= INT32_MAX, "linear: bad row count %lld", (long long)M);
     HQM_CHECK_ARG(M == 0 || (y && x), "linear: null activation pointer");
-    return launch_linear(y, x, nullptr, M, w, bias, (cudaStream_t)stream);
+    return launch_linear(y, x, nullptr, M, w, bias, scratch, scratch_bytes, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -45,7 +45,10 @@ size_t hqm_expert_ffn_scratch_bytes(int64_t M, const hqm_weight* w1, const hqm_w
     const size_t a = hqm::align_up((size_t)M * (size_t)w1->N * 2, 256);
     const size_t b = hqm::align_up((size_t)M * (size_t)w3->N * 2, 256);
     const size_t c = hqm::align_up((size_t)M * (size_t)w2->N * 2, 256);
-    return a + b + c;
+    size_t lin = hqm::linear_scratch_bytes(M, w1);
+    lin = lin > hqm::linear_scratch_bytes(M, w3) ? lin : hqm::linear_scratch_bytes(M, w3);
+    lin = lin > hqm::linear_scratch_bytes(M, w2) ? lin : hqm::linear_scratch_bytes(M, w2);
+    return a + b + c + lin;
 }
 
 int hqm_expert_ffn(uint16_t* out, const uint16_t* x, int64_t M, const int32_t* token_idx, const float* route_w,
@@ -73,15 +76,18 @@ int hqm_expert_ffn(uint16_t* out, const uint16_t* x, int64_t M, const int32_t* t
     uint16_t* b = (uint16_t*)p;
     p += align_up((size_t)M * F * 2, 256);
     uint16_t* c = (uint16_t*)p;
+    p += align_up((size_t)M * H * 2, 256);
+    void* lin = p;
+    const size_t lin_bytes = scratch_bytes - (size_t)(p - (uint8_t*)scratch);
 
-    int rc = launch_linear(a, x, token_idx, M, w1, nullptr, st);
+    int rc = launch_linear(a, x, token_idx, M, w1, nullptr, lin, lin_bytes, st);
     if (rc != HQM_OK) return rc;
-    rc = launch_linear(b, x, token_idx, M, w3, nullptr, st);
+    rc = launch_linear(b, x, token_idx, M, w3, nullptr, lin, lin_bytes, st);
     if (rc != HQM_OK) return rc;
     const int64_t nf = M * F;
     silu_mul_kernel<<<(int)((nf + 255) / 256 > 148 * 8 ? 148 * 8 : (nf + 255) / 256), 256, 0, st>>>(a, b, nf);
     HQM_LAUNCH_CHECK();
-    rc = launch_linear(c, a, nullptr, M, w2, nullptr, st);
+    rc = launch_linear(c, a, nullptr, M, w2, nullptr, lin, lin_bytes, st);
     if (rc != HQM_OK) return rc;
     const int64_t nh = M * H;
     scale_scatter_kernel<<<(int)((nh + 255) / 256 > 148 * 8 ? 148 * 8 : (nh + 255) / 256), 256, 0, st>>>(

@@ -1,0 +1,440 @@
+// Weight-streaming quantized linear for small row counts (decode): the path that
+// replaces triton_matmul4_transpose / triton_matmul2_transpose of the reference
+// (triton_kernels.py:133-191, 321-380) together with the two per-call
+// Quantizer.dequantize launches in front of them (custom_layers.py:62-66).
+//
+// Algebra.  With r = n % G the residue of output row n and j = n / G its position
+// inside the quantisation group,
+//     y[m, jG + r] = sum_k (x[m,k] s[r,k]) q[jG + r, k]  -  sum_k (x[m,k] s[r,k]) z[r,k].
+// xs[m,r,k] = x[m,k] s[r,k] and the second sum depend only on (m, r): they are shared
+// by the `group_size` rows {jG + r}.  So scale and zero are decoded (8 bit -> fp16)
+// ONCE per (r, k) and folded into the activations; per weight only the bit-field
+// extraction remains.
+//
+// Mapping.  A CTA owns one storage-row residue `rho` (PER adjacent residues r, the rows
+// packed into one byte) and a range of 64-column passes.  In a pass a warp
+//   1. decodes s, z for its PER x 64 (r, k) pairs, 2*PER per lane, and writes
+//      xs (per token) and z to warp-private shared memory as fp16;
+//   2. streams the 16*NB storage rows rho + i*P (the group's members) with 128-bit
+//      loads that bypass L1, 64 contiguous bytes per row;
+//   3. turns each 32-bit word into fp16 fragments holding OFFSET + code with one
+//      LOP3 per two codes (the field is OR-ed into the mantissa of a constant whose
+//      exponent gives that bit position the weight 1) and feeds them to
+//      mma.sync.m16n8k16: rows = 16 members, k = 16 input columns, columns = the
+//      PER slots x 8/PER tokens (each slot keeps its own accumulator tile; only the
+//      columns holding that slot's xs are read back).  The tensor core is used as the
+//      cross-lane reduction, so no shuffles are needed on the way;
+//   4. one extra MMA per word with A = [z ; OFFSET] yields sum xs*z and OFFSET*sum xs,
+//      which are subtracted at the end.
+// Partial sums of the K-splits go to an fp32 scratch [SK][M][N]; a small finalize
+// kernel adds them in fixed order (deterministic), applies bias and rounds to bf16.
+//
+// HBM traffic per launch is the packed codes + scale_q + zero_q once (the meta and x
+// stay in L1/L2), which is the algorithmic minimum.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace hqm {
+
+// --------------------------------------------------------------------------- helpers
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+// Two consecutive bf16 (one 32-bit word) -> fp16 pair.
+__device__ __forceinline__ __half2 bf16pair_to_h2(uint32_t v) {
+    return __floats2half2_rn(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
+
+// (q - mz) * ms on two 8-bit values at once: the bytes land in the mantissa of 1024.0.
+__device__ __forceinline__ __half2 meta_decode(uint32_t two_bytes_as_h2, __half2 mz, __half2 ms) {
+    const __half2 q = __hsub2(bits_h2(two_bytes_as_h2), bits_h2(0x64006400u));   // exact
+    return __hmul2(__hsub2(q, mz), ms);
+}
+
+// Bit-field extraction.  `u` is a storage word after the byte permutation
+// (B0,B2,B1,B3), so in each 16-bit half the low byte belongs to columns k0 / k1 and
+// the high byte to k2 / k3.  lo(s) / hi(s) return the fp16 pair OFFSET + code of slot s
+// for (k0,k1) / (k2,k3).  OFF_LO / OFF_HI are those offsets as fp16 bit patterns.
+template <int NBITS> struct Fields;
+
+template <> struct Fields<2> {
+    static constexpr int PER = 4;
+    uint32_t v0, v1, v2, v3;
+    __device__ __forceinline__ explicit Fields(uint32_t u) : v0(u), v1(u << 4), v2(u >> 4), v3(u >> 8) {}
+    template <int S> __device__ __forceinline__ uint32_t lo() const {
+        if (S == 0) return (v0 & 0x00C000C0u) | 0x4C004C00u;     // bits 7-6            -> 16 + c
+        if (S == 1) return (v0 & 0x00300030u) | 0x54005400u;     // bits 5-4            -> 64 + c
+        if (S == 2) return (v1 & 0x00C000C0u) | 0x4C004C00u;     // bits 3-2 moved to 7-6
+        return (v1 & 0x00300030u) | 0x54005400u;                 // bits 1-0 moved to 5-4
+    }
+    template <int S> __device__ __forceinline__ uint32_t hi() const {
+        if (S == 0) return (v3 & 0x00C000C0u) | 0x4C004C00u;     // bits 15-14 moved to 7-6
+        if (S == 1) return (v2 & 0x03000300u) | 0x44004400u;     // bits 13-12 moved to 9-8 -> 4 + c
+        if (S == 2) return (v2 & 0x00C000C0u) | 0x4C004C00u;     // bits 11-10 moved to 7-6
+        return (v0 & 0x03000300u) | 0x44004400u;                 // bits 9-8
+    }
+    __host__ __device__ static constexpr uint32_t off_lo(int s) { return (s & 1) ? 0x5400u : 0x4C00u; }
+    __host__ __device__ static constexpr uint32_t off_hi(int s) { return (s & 1) ? 0x4400u : 0x4C00u; }
+};
+
+template <> struct Fields<4> {
+    static constexpr int PER = 2;
+    uint32_t v0, v1, v2, v3;
+    __device__ __forceinline__ explicit Fields(uint32_t u) : v0(u), v1(u << 4), v2(u >> 4), v3(u >> 8) {}
+    template <int S> __device__ __forceinline__ uint32_t lo() const {
+        return ((S == 0 ? v0 : v1) & 0x00F000F0u) | 0x54005400u;  // nibble at bits 7-4 -> 64 + c
+    }
+    template <int S> __device__ __forceinline__ uint32_t hi() const {
+        return ((S == 0 ? v3 : v2) & 0x00F000F0u) | 0x54005400u;
+    }
+    __host__ __device__ static constexpr uint32_t off_lo(int) { return 0x5400u; }
+    __host__ __device__ static constexpr uint32_t off_hi(int) { return 0x5400u; }
+};
+
+// --------------------------------------------------------------------------- kernel
+// NB: blocks of 16 group members (group_size = 16*NB).  NT: column tiles of 8/PER tokens.
+template <int NBITS, int NB, int NT>
+__global__ void __launch_bounds__(256)
+gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, const int32_t* __restrict__ x_idx,
+                   int M, int m_base, int M_total, hqm_weight w, int G, int C, int P, int passes_total, int ppu) {
+    using F = Fields<NBITS>;
+    constexpr int PER = F::PER;
+    constexpr int TPT = 8 / PER;            // tokens per column tile
+    constexpr int MTOK = NT * TPT;          // tokens this instantiation handles
+    constexpr int LPS = 32 / PER;           // decode lanes per slot
+    constexpr int DK = 64 / LPS;            // decode columns per lane (8 or 4)
+    constexpr int ROW = 72;                 // 64 columns + padding: rows of different slots hit different banks
+    constexpr int WARP_HALFS = (MTOK + 1) * PER * ROW;
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5, NW = blockDim.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int rho = blockIdx.x % P, ks = blockIdx.x / P;
+    const int K = w.K;
+    __half* xs_w = reinterpret_cast<__half*>(smem_raw) + wi * WARP_HALFS;
+    __half* zz_w = xs_w + MTOK * PER * ROW;
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)NW * WARP_HALFS * sizeof(__half));
+
+    float acc[NB][NT][PER][4];
+    float accc[NT][4];
+#pragma unroll
+    for (int b = 0; b < NB; ++b)
+#pragma unroll
+        for (int tau = 0; tau < NT; ++tau)
+#pragma unroll
+            for (int s = 0; s < PER; ++s)
+#pragma unroll
+                for (int v = 0; v < 4; ++v) acc[b][tau][s][v] = 0.f;
+#pragma unroll
+    for (int tau = 0; tau < NT; ++tau)
+#pragma unroll
+        for (int v = 0; v < 4; ++v) accc[tau][v] = 0.f;
+
+    // rows of x this launch works on
+    const uint16_t* xr[MTOK];
+#pragma unroll
+    for (int m = 0; m < MTOK; ++m) {
+        const int mm = (m < M) ? (m_base + m) : m_base;
+        xr[m] = x + (int64_t)(x_idx ? x_idx[mm] : mm) * K;
+    }
+
+    const uint8_t* Wq = reinterpret_cast<const uint8_t*>(w.W_q);
+    const int sd = lane / LPS;                      // slot this lane decodes
+    const int kd = (lane % LPS) * DK;               // its first column inside the pass
+    const int64_t rbase = (int64_t)(PER * rho + sd) * K;
+    const int sB = g % PER, mB = g / PER;           // slot / token of this lane's B column
+
+    const int pass_end = min(passes_total, (ks + 1) * ppu);
+    for (int pass = ks * ppu + wi; pass < pass_end; pass += NW) {
+        const int k0 = pass * 64;
+        // ---- issue the weight loads first: they are the long-latency part
+        uint4 q0[NB], q1[NB];
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            const int64_t R0 = rho + (int64_t)(16 * b + g) * P;
+            q0[b] = ld_stream_16(Wq + R0 * K + k0 + 16 * t);
+            q1[b] = ld_stream_16(Wq + (R0 + 8 * (int64_t)P) * K + k0 + 16 * t);
+        }
+        // ---- 1. decode scale / zero for (slot sd, columns k0+kd .. +DK) and fold into x
+        {
+            const int64_t idx = rbase + k0 + kd;
+            const int col = (int)(idx % C);
+            uint32_t sq[DK / 4], zq[DK / 4], mss[DK / 2], mzs[DK / 2], msz[DK / 2], mzz[DK / 2];
+            if constexpr (DK == 8) {
+                const uint2 a = *reinterpret_cast<const uint2*>(w.scale_q + idx);
+                const uint2 bq = *reinterpret_cast<const uint2*>(w.zero_q + idx);
+                sq[0] = a.x; sq[(DK / 4) - 1] = a.y; zq[0] = bq.x; zq[(DK / 4) - 1] = bq.y;
+                const uint4 c0 = *reinterpret_cast<const uint4*>(w.ms_scale + col);
+                const uint4 c1 = *reinterpret_cast<const uint4*>(w.mz_scale + col);
+                const uint4 c2 = *reinterpret_cast<const uint4*>(w.ms_zero + col);
+                const uint4 c3 = *reinterpret_cast<const uint4*>(w.mz_zero + col);
+                mss[0] = c0.x; mss[1] = c0.y; mss[(DK / 2) - 2] = c0.z; mss[(DK / 2) - 1] = c0.w;
+                mzs[0] = c1.x; mzs[1] = c1.y; mzs[(DK / 2) - 2] = c1.z; mzs[(DK / 2) - 1] = c1.w;
+                msz[0] = c2.x; msz[1] = c2.y; msz[(DK / 2) - 2] = c2.z; msz[(DK / 2) - 1] = c2.w;
+                mzz[0] = c3.x; mzz[1] = c3.y; mzz[(DK / 2) - 2] = c3.z; mzz[(DK / 2) - 1] = c3.w;
+            } else {
+                sq[0] = *reinterpret_cast<const uint32_t*>(w.scale_q + idx);
+                zq[0] = *reinterpret_cast<const uint32_t*>(w.zero_q + idx);
+                const uint2 c0 = *reinterpret_cast<const uint2*>(w.ms_scale + col);
+                const uint2 c1 = *reinterpret_cast<const uint2*>(w.mz_scale + col);
+                const uint2 c2 = *reinterpret_cast<const uint2*>(w.ms_zero + col);
+                const uint2 c3 = *reinterpret_cast<const uint2*>(w.mz_zero + col);
+                mss[0] = c0.x; mss[1] = c0.y; mzs[0] = c1.x; mzs[1] = c1.y;
+                msz[0] = c2.x; msz[1] = c2.y; mzz[0] = c3.x; mzz[1] = c3.y;
+            }
+            uint32_t s2[DK / 2], z2[DK / 2];
+#pragma unroll
+            for (int j = 0; j < DK / 2; ++j) {
+                const uint32_t sel = (j & 1) ? 0x4342u : 0x4140u;      // bytes (2j, 2j+1) of the word -> two fp16
+                s2[j] = h2_bits(meta_decode(prmt(sq[j / 2], 0x64646464u, sel), bits_h2(mzs[j]), bits_h2(mss[j])));
+                z2[j] = h2_bits(meta_decode(prmt(zq[j / 2], 0x64646464u, sel), bits_h2(mzz[j]), bits_h2(msz[j])));
+            }
+            if constexpr (DK == 8) {
+                *reinterpret_cast<uint4*>(zz_w + sd * ROW + kd) = make_uint4(z2[0], z2[1], z2[(DK / 2) - 2], z2[(DK / 2) - 1]);
+            } else {
+                *reinterpret_cast<uint2*>(zz_w + sd * ROW + kd) = make_uint2(z2[0], z2[1]);
+            }
+#pragma unroll
+            for (int m = 0; m < MTOK; ++m) {
+                uint32_t xs2[DK / 2];
+                if (m < M) {
+                    uint32_t xv[DK / 2];
+                    if constexpr (DK == 8) {
+                        const uint4 xx = *reinterpret_cast<const uint4*>(xr[m] + k0 + kd);
+                        xv[0] = xx.x; xv[1] = xx.y; xv[(DK / 2) - 2] = xx.z; xv[(DK / 2) - 1] = xx.w;
+                    } else {
+                        const uint2 xx = *reinterpret_cast<const uint2*>(xr[m] + k0 + kd);
+                        xv[0] = xx.x; xv[1] = xx.y;
+                    }
+#pragma unroll
+                    for (int j = 0; j < DK / 2; ++j) xs2[j] = h2_bits(__hmul2(bf16pair_to_h2(xv[j]), bits_h2(s2[j])));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < DK / 2; ++j) xs2[j] = 0u;
+                }
+                __half* dst = xs_w + (m * PER + sd) * ROW + kd;
+                if constexpr (DK == 8) {
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(xs2[0], xs2[1], xs2[(DK / 2) - 2], xs2[(DK / 2) - 1]);
+                } else {
+                    *reinterpret_cast<uint2*>(dst) = make_uint2(xs2[0], xs2[1]);
+                }
+            }
+        }
+        __syncwarp();
+        // ---- 2. B fragments: xs of (token mB, slot sB) at this lane's 16 columns
+        uint32_t bf[NT][8];
+#pragma unroll
+        for (int tau = 0; tau < NT; ++tau) {
+            const __half* src = xs_w + ((tau * TPT + mB) * PER + sB) * ROW + 16 * t;
+            const uint4 lo4 = *reinterpret_cast<const uint4*>(src);
+            const uint4 hi4 = *reinterpret_cast<const uint4*>(src + 8);
+            bf[tau][0] = lo4.x; bf[tau][1] = lo4.y; bf[tau][2] = lo4.z; bf[tau][3] = lo4.w;
+            bf[tau][4] = hi4.x; bf[tau][5] = hi4.y; bf[tau][6] = hi4.z; bf[tau][7] = hi4.w;
+        }
+        // ---- 3. correction tile: rows 0..PER-1 = z of slot i, rows 8..8+PER-1 = the offsets
+        {
+            uint32_t zf[8];
+            const __half* src = zz_w + (g < PER ? g : 0) * ROW + 16 * t;
+            const uint4 lo4 = *reinterpret_cast<const uint4*>(src);
+            const uint4 hi4 = *reinterpret_cast<const uint4*>(src + 8);
+            const uint32_t keep = (g < PER) ? 0xffffffffu : 0u;
+            zf[0] = lo4.x & keep; zf[1] = lo4.y & keep; zf[2] = lo4.z & keep; zf[3] = lo4.w & keep;
+            zf[4] = hi4.x & keep; zf[5] = hi4.y & keep; zf[6] = hi4.z & keep; zf[7] = hi4.w & keep;
+            const uint32_t olo = ((g & 1) ? F::off_lo(1) : F::off_lo(0)) * 0x00010001u & keep;
+            const uint32_t ohi = ((g & 1) ? F::off_hi(1) : F::off_hi(0)) * 0x00010001u & keep;
+#pragma unroll
+            for (int wd = 0; wd < 4; ++wd)
+#pragma unroll
+                for (int tau = 0; tau < NT; ++tau)
+                    mma_f16(accc[tau], zf[2 * wd], olo, zf[2 * wd + 1], ohi, bf[tau][2 * wd], bf[tau][2 * wd + 1]);
+        }
+        // ---- 4. the weights
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            const uint32_t r0[4] = {q0[b].x, q0[b].y, q0[b].z, q0[b].w};
+            const uint32_t r1[4] = {q1[b].x, q1[b].y, q1[b].z, q1[b].w};
+#pragma unroll
+            for (int wd = 0; wd < 4; ++wd) {
+                const F f0(prmt(r0[wd], 0u, 0x3120u)), f1(prmt(r1[wd], 0u, 0x3120u));
+#pragma unroll
+                for (int tau = 0; tau < NT; ++tau) {
+                    const uint32_t b0 = bf[tau][2 * wd], b1 = bf[tau][2 * wd + 1];
+                    mma_f16(acc[b][tau][0], f0.template lo<0>(), f1.template lo<0>(), f0.template hi<0>(),
+                            f1.template hi<0>(), b0, b1);
+                    mma_f16(acc[b][tau][1], f0.template lo<1>(), f1.template lo<1>(), f0.template hi<1>(),
+                            f1.template hi<1>(), b0, b1);
+                    if constexpr (PER == 4) {
+                        mma_f16(acc[b][tau][PER - 2], f0.template lo<2>(), f1.template lo<2>(), f0.template hi<2>(),
+                                f1.template hi<2>(), b0, b1);
+                        mma_f16(acc[b][tau][PER - 1], f0.template lo<3>(), f1.template lo<3>(), f0.template hi<3>(),
+                                f1.template hi<3>(), b0, b1);
+                    }
+                }
+            }
+        }
+        __syncwarp();   // the next pass overwrites this warp's shared memory
+    }
+
+    // ---- epilogue: pick the valid columns, subtract the correction, add up the warps
+    // Lane (g, t) holds columns 2t, 2t+1 of every tile: slots sa = (2t) % PER and sa + 1
+    // of token (2t) / PER.  Column n of the correction tile is valid in the lane whose
+    // row index equals the column's slot.
+    const int sa = (2 * t) % PER;
+    constexpr int RED_PER_WARP = NB * NT * 4 * 32;
+#pragma unroll
+    for (int tau = 0; tau < NT; ++tau) {
+        const float mine = (sa == g) ? accc[tau][0] + accc[tau][2] : accc[tau][1] + accc[tau][3];
+        const float ca = __shfl_sync(0xffffffffu, mine, sa * 4 + t);
+        const float cb = __shfl_sync(0xffffffffu, mine, (sa + 1) * 4 + t);
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            float va0 = 0.f, va1 = 0.f, vb0 = 0.f, vb1 = 0.f;
+#pragma unroll
+            for (int s = 0; s < PER; s += 2) {
+                if (s == sa) {
+                    va0 = acc[b][tau][s][0];      // row g,     column 2t
+                    va1 = acc[b][tau][s][2];      // row g + 8, column 2t
+                    vb0 = acc[b][tau][s + 1][1];  // row g,     column 2t + 1
+                    vb1 = acc[b][tau][s + 1][3];  // row g + 8, column 2t + 1
+                }
+            }
+            float* dst = red + wi * RED_PER_WARP + (b * NT + tau) * 128 + lane;
+            dst[0] = va0 - ca;
+            dst[32] = vb0 - cb;
+            dst[64] = va1 - ca;
+            dst[96] = vb1 - cb;
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < RED_PER_WARP; e += blockDim.x) {
+        float sum = 0.f;
+        for (int wv = 0; wv < NW; ++wv) sum += red[wv * RED_PER_WARP + e];
+        const int le = e & 31, v = (e >> 5) & 3, bt = e >> 7;
+        const int tau = bt % NT, b = bt / NT;
+        const int ge = le >> 2, te = le & 3;
+        const int slot = (2 * te) % PER + (v & 1);
+        const int m = tau * TPT + (2 * te) / PER;
+        const int member = 16 * b + ge + 8 * (v >> 1);
+        if (m < M) {
+            const int64_t n = (int64_t)member * G + PER * rho + slot;
+            partial[((int64_t)ks * M_total + m_base + m) * w.N + n] = sum;
+        }
+    }
+}
+
+// y = bf16( sum_ks partial[ks] + bias )
+__global__ void finalize_linear_kernel(uint16_t* __restrict__ y, const float* __restrict__ partial,
+                                       const uint16_t* __restrict__ bias, int64_t MN, int N, int SK) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < MN; i += (int64_t)gridDim.x * blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < SK; ++s) v += partial[s * MN + i];
+        if (bias) v += bf16_bits_to_float(bias[i % N]);
+        y[i] = float_to_bf16_bits(v);
+    }
+}
+
+// --------------------------------------------------------------------------- host side
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+bool gemv_stream_plan(const hqm_weight* w, int G, int C, int64_t M, StreamPlan* plan) {
+    if (w->nbits != 2 && w->nbits != 4) return false;
+    const int per = codes_per_word(w->nbits);
+    const int dk = w->nbits == 2 ? 8 : 4;
+    const int g = w->group_size;
+    const bool group_ok = (w->nbits == 2) ? (g == 16 || g == 32) : (g == 32 || g == 64);
+    if (!group_ok || G % per != 0 || w->K % 64 != 0 || C % dk != 0) return false;
+    if (M < 1 || M > 16) return false;
+    if (!aligned16(w->W_q) || !aligned16(w->scale_q) || !aligned16(w->zero_q) || !aligned16(w->ms_scale) ||
+        !aligned16(w->mz_scale) || !aligned16(w->ms_zero) || !aligned16(w->mz_zero))
+        return false;
+    plan->P = G / per;
+    plan->passes_total = w->K / 64;
+    // enough CTAs for ~3 per SM, but never less than one pass per CTA
+    int sk = (3 * 148 + plan->P - 1) / plan->P;
+    if (sk > plan->passes_total) sk = plan->passes_total;
+    if (sk < 1) sk = 1;
+    plan->ppu = (plan->passes_total + sk - 1) / sk;
+    plan->SK = (plan->passes_total + plan->ppu - 1) / plan->ppu;
+    plan->warps = plan->ppu < 8 ? plan->ppu : 8;
+    return true;
+}
+
+size_t gemv_stream_scratch_bytes(const StreamPlan& plan, int64_t M, int N) {
+    return (size_t)plan.SK * (size_t)M * (size_t)N * sizeof(float);
+}
+
+template <int NBITS, int NB, int NT>
+static int launch_one(float* partial, const uint16_t* x, const int32_t* x_idx, int M, int m_base, int M_total,
+                      const hqm_weight* w, int G, int C, const StreamPlan& plan, cudaStream_t st) {
+    constexpr int PER = codes_per_word(NBITS);
+    constexpr int MTOK = NT * (8 / PER);
+    const size_t smem = (size_t)plan.warps * ((MTOK + 1) * PER * 72 * sizeof(__half) + NB * NT * 4 * 32 * sizeof(float));
+    auto kern = gemv_stream_kernel<NBITS, NB, NT>;
+    if (smem > 48 * 1024) HQM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<plan.P * plan.SK, 32 * plan.warps, smem, st>>>(partial, x, x_idx, M, m_base, M_total, *w, G, C, plan.P,
+                                                          plan.passes_total, plan.ppu);
+    HQM_LAUNCH_CHECK();
+    return HQM_OK;
+}
+
+// Tokens are processed in chunks of at most NT_MAX column tiles per launch.
+template <int NBITS, int NB, int NT_MAX>
+static int launch_chunks(float* partial, const uint16_t* x, const int32_t* x_idx, int M, const hqm_weight* w, int G,
+                         int C, const StreamPlan& plan, cudaStream_t st) {
+    constexpr int TPT = 8 / codes_per_word(NBITS);
+    for (int m0 = 0; m0 < M;) {
+        const int left = M - m0;
+        int rc;
+        if (left <= TPT) {
+            rc = launch_one<NBITS, NB, 1>(partial, x, x_idx, left, m0, M, w, G, C, plan, st);
+            m0 += left;
+        } else if (left <= 2 * TPT || NT_MAX < 4) {
+            const int take = left < 2 * TPT ? left : 2 * TPT;
+            rc = launch_one<NBITS, NB, 2>(partial, x, x_idx, take, m0, M, w, G, C, plan, st);
+            m0 += take;
+        } else {
+            const int take = left < 4 * TPT ? left : 4 * TPT;
+            rc = launch_one<NBITS, NB, (NT_MAX >= 4 ? 4 : 2)>(partial, x, x_idx, take, m0, M, w, G, C, plan, st);
+            m0 += take;
+        }
+        if (rc != HQM_OK) return rc;
+    }
+    return HQM_OK;
+}
+
+int launch_gemv_stream_partials(float* partial, const uint16_t* x, const int32_t* x_idx, int64_t M,
+                                const hqm_weight* w, int G, int C, const StreamPlan& plan, cudaStream_t st) {
+    const int nb = w->group_size / 16;
+    if (w->nbits == 2 && nb == 1) return launch_chunks<2, 1, 4>(partial, x, x_idx, (int)M, w, G, C, plan, st);
+    if (w->nbits == 2 && nb == 2) return launch_chunks<2, 2, 2>(partial, x, x_idx, (int)M, w, G, C, plan, st);
+    if (w->nbits == 4 && nb == 2) return launch_chunks<4, 2, 4>(partial, x, x_idx, (int)M, w, G, C, plan, st);
+    if (w->nbits == 4 && nb == 4) return launch_chunks<4, 4, 2>(partial, x, x_idx, (int)M, w, G, C, plan, st);
+    set_error("gemv_stream: no instantiation for nbits=%d group_size=%d", w->nbits, w->group_size);
+    return HQM_ERR_ARG;
+}
+
+int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bias, int64_t M, int N, int SK,
+                           cudaStream_t st) {
+    const int64_t MN = M * N;
+    int64_t blocks = (MN + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    finalize_linear_kernel<<<(int)blocks, 256, 0, st>>>(y, partial, bias, MN, N, SK);
+    HQM_LAUNCH_CHECK();
+    return HQM_OK;
+}
+
+}  // namespace hqm
