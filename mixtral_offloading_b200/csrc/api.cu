@@ -79,7 +79,7 @@ int launch_linear(uint16_t* y, const uint16_t* x, const int32_t* x_idx, int64_t 
         HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 15u) == 0, "linear: scratch must be 16-byte aligned");
         rc = launch_gemv_stream_partials((float*)scratch, x, x_idx, M, w, G, C, plan, st);
         if (rc != HQM_OK) return rc;
-        return launch_finalize_linear(y, (const float*)scratch, bias, M, w->N, plan.SK, st);
+        return launch_finalize_linear(y, (const float*)scratch, bias, M, w, G, plan, st);
     }
     return launch_linear_generic(y, x, x_idx, M, w, G, C, bias, st);
 }

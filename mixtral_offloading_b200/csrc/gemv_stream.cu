@@ -11,8 +11,12 @@
 // ONCE per (r, k) and folded into the activations; per weight only the bit-field
 // extraction remains.
 //
-// Mapping.  A CTA owns one storage-row residue `rho` (PER adjacent residues r, the rows
-// packed into one byte) and a range of 64-column passes.  In a pass a warp
+// Mapping.  The unit of work is a "pass": one storage-row residue `rho` (PER adjacent
+// residues r, the rows packed into one byte) x 64 input columns.  Passes are numbered
+// rho-major and cut into equal contiguous ranges, one per CTA of a single-wave
+// persistent grid (148 SMs x resident CTAs), so every SM gets the same number of bytes
+// whatever the layer shape; inside a range the warps take passes round-robin and load
+// the next pass into registers before computing the current one.  In a pass a warp
 //   1. decodes s, z for its PER x 64 (r, k) pairs, 2*PER per lane, and writes
 //      xs (per token) and z to warp-private shared memory as fp16;
 //   2. streams the 16*NB storage rows rho + i*P (the group's members) with 128-bit
@@ -26,11 +30,14 @@
 //      cross-lane reduction, so no shuffles are needed on the way;
 //   4. one extra MMA per word with A = [z ; OFFSET] yields sum xs*z and OFFSET*sum xs,
 //      which are subtracted at the end.
-// Partial sums of the K-splits go to an fp32 scratch [SK][M][N]; a small finalize
-// kernel adds them in fixed order (deterministic), applies bias and rounds to bf16.
+// A residue whose passes span several CTAs gets one fp32 partial row-set per CTA in a
+// scratch buffer [slots][M][N]; a small finalize kernel adds them in fixed order
+// (deterministic), applies bias and rounds to bf16.
 //
 // HBM traffic per launch is the packed codes + scale_q + zero_q once (the meta and x
 // stay in L1/L2), which is the algorithmic minimum.
+#include <type_traits>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -106,43 +113,75 @@ template <> struct Fields<4> {
 };
 
 // --------------------------------------------------------------------------- kernel
+// Work split shared by the kernel and the finalize step: passes are numbered
+// L = rho * PT + p (PT = K / 64 passes per residue); CTA c owns [c*Ltot/grid, (c+1)*Ltot/grid).
+// (32-bit arithmetic throughout: the planner rejects layers with total() * grid >= 2^31.)
+struct Split {
+    int P, PT, grid;
+    __host__ __device__ uint32_t total() const { return (uint32_t)P * (uint32_t)PT; }
+    __host__ __device__ uint32_t begin(int c) const { return (uint32_t)c * total() / (uint32_t)grid; }
+    // CTA whose range contains pass L
+    __host__ __device__ int owner(uint32_t L) const {
+        int c = (int)(L * (uint32_t)grid / total());
+        while (c + 1 < grid && begin(c + 1) <= L) ++c;
+        while (c > 0 && begin(c) > L) --c;
+        return c;
+    }
+};
+
 // NB: blocks of 16 group members (group_size = 16*NB).  NT: column tiles of 8/PER tokens.
+template <int NBITS, int NB, int NT>
+struct Pass {
+    static constexpr int PER = codes_per_word(NBITS);
+    static constexpr int MTOK = NT * (8 / PER);
+    static constexpr int DK = 64 / (32 / PER);     // decode columns per lane (8 or 4)
+    uint32_t sq[DK / 4], zq[DK / 4];
+    uint32_t mss[DK / 2], mzs[DK / 2], msz[DK / 2], mzz[DK / 2];
+    uint32_t xv[MTOK][DK / 2];
+};
+
+template <int N> __device__ __forceinline__ void ld_words(uint32_t (&dst)[N], const void* p) {
+    if constexpr (N == 1) {
+        dst[0] = *reinterpret_cast<const uint32_t*>(p);
+    } else if constexpr (N == 2) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        dst[0] = v.x; dst[1] = v.y;
+    } else {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+    }
+}
+template <int N> __device__ __forceinline__ void st_words(void* p, const uint32_t (&src)[N]) {
+    if constexpr (N == 2) {
+        *reinterpret_cast<uint2*>(p) = make_uint2(src[0], src[1]);
+    } else {
+        *reinterpret_cast<uint4*>(p) = make_uint4(src[0], src[1], src[2], src[3]);
+    }
+}
+
 template <int NBITS, int NB, int NT>
 __global__ void __launch_bounds__(256)
 gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, const int32_t* __restrict__ x_idx,
-                   int M, int m_base, int M_total, hqm_weight w, int G, int C, int P, int passes_total, int ppu) {
+                   int M, int m_base, int M_total, hqm_weight w, int G, int C, Split sp) {
     using F = Fields<NBITS>;
+    using PR = Pass<NBITS, NB, NT>;
     constexpr int PER = F::PER;
     constexpr int TPT = 8 / PER;            // tokens per column tile
     constexpr int MTOK = NT * TPT;          // tokens this instantiation handles
     constexpr int LPS = 32 / PER;           // decode lanes per slot
-    constexpr int DK = 64 / LPS;            // decode columns per lane (8 or 4)
+    constexpr int DK = PR::DK;
     constexpr int ROW = 72;                 // 64 columns + padding: rows of different slots hit different banks
     constexpr int WARP_HALFS = (MTOK + 1) * PER * ROW;
+    constexpr int NW = 8;
+    constexpr int RED_PER_WARP = NB * NT * 4 * 32;
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5, NW = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int rho = blockIdx.x % P, ks = blockIdx.x / P;
-    const int K = w.K;
+    const int K = w.K, P = sp.P, PT = sp.PT;
     __half* xs_w = reinterpret_cast<__half*>(smem_raw) + wi * WARP_HALFS;
     __half* zz_w = xs_w + MTOK * PER * ROW;
     float* red = reinterpret_cast<float*>(smem_raw + (size_t)NW * WARP_HALFS * sizeof(__half));
-
-    float acc[NB][NT][PER][4];
-    float accc[NT][4];
-#pragma unroll
-    for (int b = 0; b < NB; ++b)
-#pragma unroll
-        for (int tau = 0; tau < NT; ++tau)
-#pragma unroll
-            for (int s = 0; s < PER; ++s)
-#pragma unroll
-                for (int v = 0; v < 4; ++v) acc[b][tau][s][v] = 0.f;
-#pragma unroll
-    for (int tau = 0; tau < NT; ++tau)
-#pragma unroll
-        for (int v = 0; v < 4; ++v) accc[tau][v] = 0.f;
 
     // rows of x this launch works on
     const uint16_t* xr[MTOK];
@@ -151,204 +190,285 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
         const int mm = (m < M) ? (m_base + m) : m_base;
         xr[m] = x + (int64_t)(x_idx ? x_idx[mm] : mm) * K;
     }
-
     const uint8_t* Wq = reinterpret_cast<const uint8_t*>(w.W_q);
     const int sd = lane / LPS;                      // slot this lane decodes
     const int kd = (lane % LPS) * DK;               // its first column inside the pass
-    const int64_t rbase = (int64_t)(PER * rho + sd) * K;
     const int sB = g % PER, mB = g / PER;           // slot / token of this lane's B column
-
-    const int pass_end = min(passes_total, (ks + 1) * ppu);
-    for (int pass = ks * ppu + wi; pass < pass_end; pass += NW) {
-        const int k0 = pass * 64;
-        // ---- issue the weight loads first: they are the long-latency part
-        uint4 q0[NB], q1[NB];
+    const int sa = (2 * t) % PER;                   // first of the two slots whose columns this lane reads back
+    const uint32_t keep = (g < PER) ? 0xffffffffu : 0u;
+    const uint32_t olo = ((g & 1) ? F::off_lo(1) : F::off_lo(0)) * 0x00010001u & keep;
+    const uint32_t ohi = ((g & 1) ? F::off_hi(1) : F::off_hi(0)) * 0x00010001u & keep;
+    // offsets of this lane's weight rows (bytes from W_q + rho*K + k0) and of its decode element
+    uint32_t qoff[NB];
 #pragma unroll
-        for (int b = 0; b < NB; ++b) {
-            const int64_t R0 = rho + (int64_t)(16 * b + g) * P;
-            q0[b] = ld_stream_16(Wq + R0 * K + k0 + 16 * t);
-            q1[b] = ld_stream_16(Wq + (R0 + 8 * (int64_t)P) * K + k0 + 16 * t);
-        }
-        // ---- 1. decode scale / zero for (slot sd, columns k0+kd .. +DK) and fold into x
-        {
-            const int64_t idx = rbase + k0 + kd;
-            const int col = (int)(idx % C);
-            uint32_t sq[DK / 4], zq[DK / 4], mss[DK / 2], mzs[DK / 2], msz[DK / 2], mzz[DK / 2];
-            if constexpr (DK == 8) {
-                const uint2 a = *reinterpret_cast<const uint2*>(w.scale_q + idx);
-                const uint2 bq = *reinterpret_cast<const uint2*>(w.zero_q + idx);
-                sq[0] = a.x; sq[(DK / 4) - 1] = a.y; zq[0] = bq.x; zq[(DK / 4) - 1] = bq.y;
-                const uint4 c0 = *reinterpret_cast<const uint4*>(w.ms_scale + col);
-                const uint4 c1 = *reinterpret_cast<const uint4*>(w.mz_scale + col);
-                const uint4 c2 = *reinterpret_cast<const uint4*>(w.ms_zero + col);
-                const uint4 c3 = *reinterpret_cast<const uint4*>(w.mz_zero + col);
-                mss[0] = c0.x; mss[1] = c0.y; mss[(DK / 2) - 2] = c0.z; mss[(DK / 2) - 1] = c0.w;
-                mzs[0] = c1.x; mzs[1] = c1.y; mzs[(DK / 2) - 2] = c1.z; mzs[(DK / 2) - 1] = c1.w;
-                msz[0] = c2.x; msz[1] = c2.y; msz[(DK / 2) - 2] = c2.z; msz[(DK / 2) - 1] = c2.w;
-                mzz[0] = c3.x; mzz[1] = c3.y; mzz[(DK / 2) - 2] = c3.z; mzz[(DK / 2) - 1] = c3.w;
-            } else {
-                sq[0] = *reinterpret_cast<const uint32_t*>(w.scale_q + idx);
-                zq[0] = *reinterpret_cast<const uint32_t*>(w.zero_q + idx);
-                const uint2 c0 = *reinterpret_cast<const uint2*>(w.ms_scale + col);
-                const uint2 c1 = *reinterpret_cast<const uint2*>(w.mz_scale + col);
-                const uint2 c2 = *reinterpret_cast<const uint2*>(w.ms_zero + col);
-                const uint2 c3 = *reinterpret_cast<const uint2*>(w.mz_zero + col);
-                mss[0] = c0.x; mss[1] = c0.y; mzs[0] = c1.x; mzs[1] = c1.y;
-                msz[0] = c2.x; msz[1] = c2.y; mzz[0] = c3.x; mzz[1] = c3.y;
+    for (int b = 0; b < NB; ++b) qoff[b] = (uint32_t)(16 * b + g) * (uint32_t)P * (uint32_t)K + 16u * t;
+    const uint32_t qoff8 = 8u * (uint32_t)P * (uint32_t)K;
+
+    const uint32_t L_begin = sp.begin(blockIdx.x), L_end = sp.begin(blockIdx.x + 1);
+    for (uint32_t L = L_begin; L < L_end;) {
+        // ---- one segment: passes [pa, pb) of residue rho
+        const int rho = (int)(L / (uint32_t)PT), pa = (int)(L - (uint32_t)rho * (uint32_t)PT);
+        const int pb = min(PT, pa + (int)(L_end - L));
+        L += (uint32_t)(pb - pa);
+
+        float acc[NB][NT][PER][4];
+        float accc[NT][4];
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int tau = 0; tau < NT; ++tau)
+#pragma unroll
+                for (int s = 0; s < PER; ++s)
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) acc[b][tau][s][v] = 0.f;
+#pragma unroll
+        for (int tau = 0; tau < NT; ++tau)
+#pragma unroll
+            for (int v = 0; v < 4; ++v) accc[tau][v] = 0.f;
+
+        const uint8_t* wrow = Wq + (size_t)rho * K;
+        const uint32_t dbase = (uint32_t)(PER * rho + sd) * (uint32_t)K + kd;     // flat scale/zero index at k0 = 0
+
+        // meta column of a flat scale/zero index: the residue-row part is reduced once per segment,
+        // a pass then adds k0 < K and wraps with compares instead of a division
+        const uint32_t dcol0 = dbase % (uint32_t)C;
+        uint32_t kcol = (uint32_t)((pa + wi) * 64) % (uint32_t)C;     // (k0 % C) of the pass loaded next
+        auto col_of = [&](uint32_t) {
+            const uint32_t c = dcol0 + kcol;
+            kcol += 64u * NW;
+            while (kcol >= (uint32_t)C) kcol -= (uint32_t)C;
+            return c >= (uint32_t)C ? c - (uint32_t)C : c;
+        };
+        auto load_rows = [&](uint4 (&q0)[NB], uint4 (&q1)[NB], int p) {
+            const int k0 = p * 64;
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                q0[b] = ld_stream_16(wrow + k0 + qoff[b]);
+                q1[b] = ld_stream_16(wrow + k0 + qoff[b] + qoff8);
             }
+        };
+        auto load_meta = [&](PR& r, int p) {
+            const int k0 = p * 64;
+            const uint32_t idx = dbase + k0;
+            const uint32_t col = col_of(idx);
+            ld_words(r.sq, w.scale_q + idx);
+            ld_words(r.zq, w.zero_q + idx);
+            ld_words(r.mss, w.ms_scale + col);
+            ld_words(r.mzs, w.mz_scale + col);
+            ld_words(r.msz, w.ms_zero + col);
+            ld_words(r.mzz, w.mz_zero + col);
+#pragma unroll
+            for (int m = 0; m < MTOK; ++m)
+                if (m < M) ld_words(r.xv[m], xr[m] + k0 + kd);
+        };
+
+        auto decode_pass = [&](const PR& r) {
+            // ---- 1. decode scale / zero of (slot sd, DK columns) and fold into x
             uint32_t s2[DK / 2], z2[DK / 2];
 #pragma unroll
             for (int j = 0; j < DK / 2; ++j) {
                 const uint32_t sel = (j & 1) ? 0x4342u : 0x4140u;      // bytes (2j, 2j+1) of the word -> two fp16
-                s2[j] = h2_bits(meta_decode(prmt(sq[j / 2], 0x64646464u, sel), bits_h2(mzs[j]), bits_h2(mss[j])));
-                z2[j] = h2_bits(meta_decode(prmt(zq[j / 2], 0x64646464u, sel), bits_h2(mzz[j]), bits_h2(msz[j])));
+                s2[j] = h2_bits(meta_decode(prmt(r.sq[j / 2], 0x64646464u, sel), bits_h2(r.mzs[j]), bits_h2(r.mss[j])));
+                z2[j] = h2_bits(meta_decode(prmt(r.zq[j / 2], 0x64646464u, sel), bits_h2(r.mzz[j]), bits_h2(r.msz[j])));
             }
-            if constexpr (DK == 8) {
-                *reinterpret_cast<uint4*>(zz_w + sd * ROW + kd) = make_uint4(z2[0], z2[1], z2[(DK / 2) - 2], z2[(DK / 2) - 1]);
-            } else {
-                *reinterpret_cast<uint2*>(zz_w + sd * ROW + kd) = make_uint2(z2[0], z2[1]);
-            }
+            st_words(zz_w + sd * ROW + kd, z2);
 #pragma unroll
             for (int m = 0; m < MTOK; ++m) {
                 uint32_t xs2[DK / 2];
-                if (m < M) {
-                    uint32_t xv[DK / 2];
-                    if constexpr (DK == 8) {
-                        const uint4 xx = *reinterpret_cast<const uint4*>(xr[m] + k0 + kd);
-                        xv[0] = xx.x; xv[1] = xx.y; xv[(DK / 2) - 2] = xx.z; xv[(DK / 2) - 1] = xx.w;
-                    } else {
-                        const uint2 xx = *reinterpret_cast<const uint2*>(xr[m] + k0 + kd);
-                        xv[0] = xx.x; xv[1] = xx.y;
+#pragma unroll
+                for (int j = 0; j < DK / 2; ++j)
+                    xs2[j] = (m < M) ? h2_bits(__hmul2(bf16pair_to_h2(r.xv[m][j]), bits_h2(s2[j]))) : 0u;
+                st_words(xs_w + (m * PER + sd) * ROW + kd, xs2);
+            }
+            __syncwarp();
+        };
+        auto mma_pass = [&](const uint4 (&q0)[NB], const uint4 (&q1)[NB]) {
+            // ---- 2. B fragments: xs of (token mB, slot sB) at this lane's 16 columns
+            uint32_t bf[NT][8];
+#pragma unroll
+            for (int tau = 0; tau < NT; ++tau) {
+                const __half* src = xs_w + ((tau * TPT + mB) * PER + sB) * ROW + 16 * t;
+                const uint4 lo4 = *reinterpret_cast<const uint4*>(src);
+                const uint4 hi4 = *reinterpret_cast<const uint4*>(src + 8);
+                bf[tau][0] = lo4.x; bf[tau][1] = lo4.y; bf[tau][2] = lo4.z; bf[tau][3] = lo4.w;
+                bf[tau][4] = hi4.x; bf[tau][5] = hi4.y; bf[tau][6] = hi4.z; bf[tau][7] = hi4.w;
+            }
+            // ---- 3. correction tile: rows 0..PER-1 = z of slot i, rows 8..8+PER-1 = the offsets
+            {
+                uint32_t zf[8];
+                const __half* src = zz_w + (g < PER ? g : 0) * ROW + 16 * t;
+                const uint4 lo4 = *reinterpret_cast<const uint4*>(src);
+                const uint4 hi4 = *reinterpret_cast<const uint4*>(src + 8);
+                zf[0] = lo4.x & keep; zf[1] = lo4.y & keep; zf[2] = lo4.z & keep; zf[3] = lo4.w & keep;
+                zf[4] = hi4.x & keep; zf[5] = hi4.y & keep; zf[6] = hi4.z & keep; zf[7] = hi4.w & keep;
+#pragma unroll
+                for (int wd = 0; wd < 4; ++wd)
+#pragma unroll
+                    for (int tau = 0; tau < NT; ++tau)
+                        mma_f16(accc[tau], zf[2 * wd], olo, zf[2 * wd + 1], ohi, bf[tau][2 * wd], bf[tau][2 * wd + 1]);
+            }
+            // ---- 4. the weights
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                const uint32_t r0[4] = {q0[b].x, q0[b].y, q0[b].z, q0[b].w};
+                const uint32_t r1[4] = {q1[b].x, q1[b].y, q1[b].z, q1[b].w};
+#pragma unroll
+                for (int wd = 0; wd < 4; ++wd) {
+                    const F f0(prmt(r0[wd], 0u, 0x3120u)), f1(prmt(r1[wd], 0u, 0x3120u));
+#pragma unroll
+                    for (int tau = 0; tau < NT; ++tau) {
+                        const uint32_t b0 = bf[tau][2 * wd], b1 = bf[tau][2 * wd + 1];
+                        mma_f16(acc[b][tau][0], f0.template lo<0>(), f1.template lo<0>(), f0.template hi<0>(),
+                                f1.template hi<0>(), b0, b1);
+                        mma_f16(acc[b][tau][1], f0.template lo<1>(), f1.template lo<1>(), f0.template hi<1>(),
+                                f1.template hi<1>(), b0, b1);
+                        if constexpr (PER == 4) {
+                            mma_f16(acc[b][tau][PER - 2], f0.template lo<2>(), f1.template lo<2>(),
+                                    f0.template hi<2>(), f1.template hi<2>(), b0, b1);
+                            mma_f16(acc[b][tau][PER - 1], f0.template lo<3>(), f1.template lo<3>(),
+                                    f0.template hi<3>(), f1.template hi<3>(), b0, b1);
+                        }
                     }
-#pragma unroll
-                    for (int j = 0; j < DK / 2; ++j) xs2[j] = h2_bits(__hmul2(bf16pair_to_h2(xv[j]), bits_h2(s2[j])));
-                } else {
-#pragma unroll
-                    for (int j = 0; j < DK / 2; ++j) xs2[j] = 0u;
-                }
-                __half* dst = xs_w + (m * PER + sd) * ROW + kd;
-                if constexpr (DK == 8) {
-                    *reinterpret_cast<uint4*>(dst) = make_uint4(xs2[0], xs2[1], xs2[(DK / 2) - 2], xs2[(DK / 2) - 1]);
-                } else {
-                    *reinterpret_cast<uint2*>(dst) = make_uint2(xs2[0], xs2[1]);
                 }
             }
+            __syncwarp();   // the next pass overwrites this warp's shared memory
+        };
+
+        // ---- the warp's passes of this segment.  The decode inputs are dead once decoded, so the
+        // next pass's are requested into the same registers right away; the next weight rows go to
+        // a second register set.  Both are in flight while the tensor-core phase of this pass runs.
+        PR d;
+        uint4 qa0[NB], qa1[NB], qb0[NB], qb1[NB];
+        int p = pa + wi;
+        if (p < pb) {
+            load_rows(qa0, qa1, p);
+            load_meta(d, p);
         }
-        __syncwarp();
-        // ---- 2. B fragments: xs of (token mB, slot sB) at this lane's 16 columns
-        uint32_t bf[NT][8];
+        while (p < pb) {
+            decode_pass(d);
+            const int pn = p + NW;
+            if (pn < pb) {
+                load_meta(d, pn);
+                load_rows(qb0, qb1, pn);
+            }
+            mma_pass(qa0, qa1);
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                qa0[b] = qb0[b];
+                qa1[b] = qb1[b];
+            }
+            p = pn;
+        }
+
+        // ---- segment epilogue: pick the valid columns, subtract the correction, add up the warps.
+        // Lane (g, t) holds columns 2t, 2t+1 of every tile: slots sa and sa + 1 of token (2t) / PER.
+        // Column n of the correction tile is valid in the lane whose row index equals the column's slot.
 #pragma unroll
         for (int tau = 0; tau < NT; ++tau) {
-            const __half* src = xs_w + ((tau * TPT + mB) * PER + sB) * ROW + 16 * t;
-            const uint4 lo4 = *reinterpret_cast<const uint4*>(src);
-            const uint4 hi4 = *reinterpret_cast<const uint4*>(src + 8);
-            bf[tau][0] = lo4.x; bf[tau][1] = lo4.y; bf[tau][2] = lo4.z; bf[tau][3] = lo4.w;
-            bf[tau][4] = hi4.x; bf[tau][5] = hi4.y; bf[tau][6] = hi4.z; bf[tau][7] = hi4.w;
-        }
-        // ---- 3. correction tile: rows 0..PER-1 = z of slot i, rows 8..8+PER-1 = the offsets
-        {
-            uint32_t zf[8];
-            const __half* src = zz_w + (g < PER ? g : 0) * ROW + 16 * t;
-            const uint4 lo4 = *reinterpret_cast<const uint4*>(src);
-            const uint4 hi4 = *reinterpret_cast<const uint4*>(src + 8);
-            const uint32_t keep = (g < PER) ? 0xffffffffu : 0u;
-            zf[0] = lo4.x & keep; zf[1] = lo4.y & keep; zf[2] = lo4.z & keep; zf[3] = lo4.w & keep;
-            zf[4] = hi4.x & keep; zf[5] = hi4.y & keep; zf[6] = hi4.z & keep; zf[7] = hi4.w & keep;
-            const uint32_t olo = ((g & 1) ? F::off_lo(1) : F::off_lo(0)) * 0x00010001u & keep;
-            const uint32_t ohi = ((g & 1) ? F::off_hi(1) : F::off_hi(0)) * 0x00010001u & keep;
+            const float mine = (sa == g) ? accc[tau][0] + accc[tau][2] : accc[tau][1] + accc[tau][3];
+            const float ca = __shfl_sync(0xffffffffu, mine, sa * 4 + t);
+            const float cb = __shfl_sync(0xffffffffu, mine, (sa + 1) * 4 + t);
 #pragma unroll
-            for (int wd = 0; wd < 4; ++wd)
+            for (int b = 0; b < NB; ++b) {
+                float va0 = 0.f, va1 = 0.f, vb0 = 0.f, vb1 = 0.f;
 #pragma unroll
-                for (int tau = 0; tau < NT; ++tau)
-                    mma_f16(accc[tau], zf[2 * wd], olo, zf[2 * wd + 1], ohi, bf[tau][2 * wd], bf[tau][2 * wd + 1]);
-        }
-        // ---- 4. the weights
-#pragma unroll
-        for (int b = 0; b < NB; ++b) {
-            const uint32_t r0[4] = {q0[b].x, q0[b].y, q0[b].z, q0[b].w};
-            const uint32_t r1[4] = {q1[b].x, q1[b].y, q1[b].z, q1[b].w};
-#pragma unroll
-            for (int wd = 0; wd < 4; ++wd) {
-                const F f0(prmt(r0[wd], 0u, 0x3120u)), f1(prmt(r1[wd], 0u, 0x3120u));
-#pragma unroll
-                for (int tau = 0; tau < NT; ++tau) {
-                    const uint32_t b0 = bf[tau][2 * wd], b1 = bf[tau][2 * wd + 1];
-                    mma_f16(acc[b][tau][0], f0.template lo<0>(), f1.template lo<0>(), f0.template hi<0>(),
-                            f1.template hi<0>(), b0, b1);
-                    mma_f16(acc[b][tau][1], f0.template lo<1>(), f1.template lo<1>(), f0.template hi<1>(),
-                            f1.template hi<1>(), b0, b1);
-                    if constexpr (PER == 4) {
-                        mma_f16(acc[b][tau][PER - 2], f0.template lo<2>(), f1.template lo<2>(), f0.template hi<2>(),
-                                f1.template hi<2>(), b0, b1);
-                        mma_f16(acc[b][tau][PER - 1], f0.template lo<3>(), f1.template lo<3>(), f0.template hi<3>(),
-                                f1.template hi<3>(), b0, b1);
+                for (int s = 0; s < PER; s += 2) {
+                    if (s == sa) {
+                        va0 = acc[b][tau][s][0];      // row g,     column 2t
+                        va1 = acc[b][tau][s][2];      // row g + 8, column 2t
+                        vb0 = acc[b][tau][s + 1][1];  // row g,     column 2t + 1
+                        vb1 = acc[b][tau][s + 1][3];  // row g + 8, column 2t + 1
                     }
                 }
+                float* dst = red + wi * RED_PER_WARP + (b * NT + tau) * 128 + lane;
+                dst[0] = va0 - ca;
+                dst[32] = vb0 - cb;
+                dst[64] = va1 - ca;
+                dst[96] = vb1 - cb;
             }
         }
-        __syncwarp();   // the next pass overwrites this warp's shared memory
-    }
-
-    // ---- epilogue: pick the valid columns, subtract the correction, add up the warps
-    // Lane (g, t) holds columns 2t, 2t+1 of every tile: slots sa = (2t) % PER and sa + 1
-    // of token (2t) / PER.  Column n of the correction tile is valid in the lane whose
-    // row index equals the column's slot.
-    const int sa = (2 * t) % PER;
-    constexpr int RED_PER_WARP = NB * NT * 4 * 32;
+        __syncthreads();
+        const int slot_idx = blockIdx.x - sp.owner((uint32_t)rho * (uint32_t)PT);
+        for (int e = threadIdx.x; e < RED_PER_WARP; e += blockDim.x) {
+            float sum = 0.f;
 #pragma unroll
-    for (int tau = 0; tau < NT; ++tau) {
-        const float mine = (sa == g) ? accc[tau][0] + accc[tau][2] : accc[tau][1] + accc[tau][3];
-        const float ca = __shfl_sync(0xffffffffu, mine, sa * 4 + t);
-        const float cb = __shfl_sync(0xffffffffu, mine, (sa + 1) * 4 + t);
-#pragma unroll
-        for (int b = 0; b < NB; ++b) {
-            float va0 = 0.f, va1 = 0.f, vb0 = 0.f, vb1 = 0.f;
-#pragma unroll
-            for (int s = 0; s < PER; s += 2) {
-                if (s == sa) {
-                    va0 = acc[b][tau][s][0];      // row g,     column 2t
-                    va1 = acc[b][tau][s][2];      // row g + 8, column 2t
-                    vb0 = acc[b][tau][s + 1][1];  // row g,     column 2t + 1
-                    vb1 = acc[b][tau][s + 1][3];  // row g + 8, column 2t + 1
-                }
+            for (int wv = 0; wv < NW; ++wv) sum += red[wv * RED_PER_WARP + e];
+            const int le = e & 31, v = (e >> 5) & 3, bt = e >> 7;
+            const int tau = bt % NT, b = bt / NT;
+            const int ge = le >> 2, te = le & 3;
+            const int slot = (2 * te) % PER + (v & 1);
+            const int m = tau * TPT + (2 * te) / PER;
+            const int member = 16 * b + ge + 8 * (v >> 1);
+            if (m < M) {
+                const int64_t n = (int64_t)member * G + PER * rho + slot;
+                partial[((int64_t)slot_idx * M_total + m_base + m) * w.N + n] = sum;
             }
-            float* dst = red + wi * RED_PER_WARP + (b * NT + tau) * 128 + lane;
-            dst[0] = va0 - ca;
-            dst[32] = vb0 - cb;
-            dst[64] = va1 - ca;
-            dst[96] = vb1 - cb;
         }
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < RED_PER_WARP; e += blockDim.x) {
-        float sum = 0.f;
-        for (int wv = 0; wv < NW; ++wv) sum += red[wv * RED_PER_WARP + e];
-        const int le = e & 31, v = (e >> 5) & 3, bt = e >> 7;
-        const int tau = bt % NT, b = bt / NT;
-        const int ge = le >> 2, te = le & 3;
-        const int slot = (2 * te) % PER + (v & 1);
-        const int m = tau * TPT + (2 * te) / PER;
-        const int member = 16 * b + ge + 8 * (v >> 1);
-        if (m < M) {
-            const int64_t n = (int64_t)member * G + PER * rho + slot;
-            partial[((int64_t)ks * M_total + m_base + m) * w.N + n] = sum;
-        }
+        __syncthreads();   // `red` is reused by the next segment
     }
 }
 
-// y = bf16( sum_ks partial[ks] + bias )
+// y = bf16( sum over the CTAs that hold a piece of row n's residue + bias )
 __global__ void finalize_linear_kernel(uint16_t* __restrict__ y, const float* __restrict__ partial,
-                                       const uint16_t* __restrict__ bias, int64_t MN, int N, int SK) {
+                                       const uint16_t* __restrict__ bias, int64_t MN, int N, int G, int per, Split sp) {
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < MN; i += (int64_t)gridDim.x * blockDim.x) {
+        const int n = (int)(i % N);
+        const int rho = (n % G) / per;
+        const int first = sp.owner((uint32_t)rho * sp.PT), last = sp.owner((uint32_t)rho * sp.PT + sp.PT - 1);
         float v = 0.f;
-        for (int s = 0; s < SK; ++s) v += partial[s * MN + i];
-        if (bias) v += bf16_bits_to_float(bias[i % N]);
+        for (int s = 0; s <= last - first; ++s) v += partial[s * MN + i];
+        if (bias) v += bf16_bits_to_float(bias[n]);
         y[i] = float_to_bf16_bits(v);
     }
 }
 
 // --------------------------------------------------------------------------- host side
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <int NBITS, int NB, int NT>
+static size_t smem_bytes() {
+    constexpr int PER = codes_per_word(NBITS);
+    constexpr int MTOK = NT * (8 / PER);
+    return 8 * ((size_t)(MTOK + 1) * PER * 72 * sizeof(__half) + (size_t)NB * NT * 4 * 32 * sizeof(float));
+}
+
+// Resident CTAs per SM of an instantiation (queried once), times the SM count.
+template <int NBITS, int NB, int NT>
+static int resident_grid() {
+    static int cached = 0;
+    if (cached == 0) {
+        auto kern = gemv_stream_kernel<NBITS, NB, NT>;
+        const size_t smem = smem_bytes<NBITS, NB, NT>();
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        int per_sm = 0, dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 256, smem) != cudaSuccess || per_sm < 1)
+            per_sm = 1;
+        cached = per_sm * sms;
+    }
+    return cached;
+}
+
+// The instantiation that serves `tokens` rows of a layer in one launch.
+static int tiles_for(int nbits, int nb, int tokens) {
+    const int tpt = 8 / codes_per_word(nbits);
+    const int nt_max = ((nbits == 2 && nb == 1) || (nbits == 4 && nb == 2)) ? 4 : 2;
+    int nt = 1;
+    while (nt < nt_max && nt * tpt < tokens) nt *= 2;
+    return nt;
+}
+
+template <typename Fn>
+static int dispatch(int nbits, int nb, int nt, Fn&& fn) {
+#define HQM_CASE(B, NBK, T) if (nbits == B && nb == NBK && nt == T) return fn(std::integral_constant<int, B>(), std::integral_constant<int, NBK>(), std::integral_constant<int, T>());
+    HQM_CASE(2, 1, 1) HQM_CASE(2, 1, 2) HQM_CASE(2, 1, 4)
+    HQM_CASE(2, 2, 1) HQM_CASE(2, 2, 2)
+    HQM_CASE(4, 2, 1) HQM_CASE(4, 2, 2) HQM_CASE(4, 2, 4)
+    HQM_CASE(4, 4, 1) HQM_CASE(4, 4, 2)
+#undef HQM_CASE
+    return -1;
+}
 
 bool gemv_stream_plan(const hqm_weight* w, int G, int C, int64_t M, StreamPlan* plan) {
     if (w->nbits != 2 && w->nbits != 4) return false;
@@ -358,81 +478,65 @@ bool gemv_stream_plan(const hqm_weight* w, int G, int C, int64_t M, StreamPlan* 
     const bool group_ok = (w->nbits == 2) ? (g == 16 || g == 32) : (g == 32 || g == 64);
     if (!group_ok || G % per != 0 || w->K % 64 != 0 || C % dk != 0) return false;
     if (M < 1 || M > 16) return false;
+    if ((int64_t)G * w->K >= (int64_t)1 << 31 || (int64_t)(w->N / per) * w->K >= (int64_t)1 << 31) return false;
     if (!aligned16(w->W_q) || !aligned16(w->scale_q) || !aligned16(w->zero_q) || !aligned16(w->ms_scale) ||
         !aligned16(w->mz_scale) || !aligned16(w->ms_zero) || !aligned16(w->mz_zero))
         return false;
+    const int nb = g / 16;
+    // the grid of the widest instantiation any chunk of these M rows uses decides the split
+    const int tpt = 8 / per;
+    const int nt = tiles_for(w->nbits, nb, (int)M);
+    int grid = dispatch(w->nbits, nb, nt, [](auto b, auto k, auto t) {
+        return resident_grid<decltype(b)::value, decltype(k)::value, decltype(t)::value>();
+    });
+    if (grid <= 0) return false;
     plan->P = G / per;
-    plan->passes_total = w->K / 64;
-    // enough CTAs for ~3 per SM, but never less than one pass per CTA
-    int sk = (3 * 148 + plan->P - 1) / plan->P;
-    if (sk > plan->passes_total) sk = plan->passes_total;
-    if (sk < 1) sk = 1;
-    plan->ppu = (plan->passes_total + sk - 1) / sk;
-    plan->SK = (plan->passes_total + plan->ppu - 1) / plan->ppu;
-    plan->warps = plan->ppu < 8 ? plan->ppu : 8;
+    plan->PT = w->K / 64;
+    const int64_t total = (int64_t)plan->P * plan->PT;
+    if (grid > total) grid = (int)total;
+    if (total * grid >= ((int64_t)1 << 31)) return false;
+    plan->grid = grid;
+    plan->nt = nt;
+    plan->chunk = nt * tpt;
+    const int64_t min_range = total / grid;                   // >= 1
+    plan->slots = (int)((plan->PT + min_range - 1) / min_range) + 1;
     return true;
 }
 
 size_t gemv_stream_scratch_bytes(const StreamPlan& plan, int64_t M, int N) {
-    return (size_t)plan.SK * (size_t)M * (size_t)N * sizeof(float);
-}
-
-template <int NBITS, int NB, int NT>
-static int launch_one(float* partial, const uint16_t* x, const int32_t* x_idx, int M, int m_base, int M_total,
-                      const hqm_weight* w, int G, int C, const StreamPlan& plan, cudaStream_t st) {
-    constexpr int PER = codes_per_word(NBITS);
-    constexpr int MTOK = NT * (8 / PER);
-    const size_t smem = (size_t)plan.warps * ((MTOK + 1) * PER * 72 * sizeof(__half) + NB * NT * 4 * 32 * sizeof(float));
-    auto kern = gemv_stream_kernel<NBITS, NB, NT>;
-    if (smem > 48 * 1024) HQM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<plan.P * plan.SK, 32 * plan.warps, smem, st>>>(partial, x, x_idx, M, m_base, M_total, *w, G, C, plan.P,
-                                                          plan.passes_total, plan.ppu);
-    HQM_LAUNCH_CHECK();
-    return HQM_OK;
-}
-
-// Tokens are processed in chunks of at most NT_MAX column tiles per launch.
-template <int NBITS, int NB, int NT_MAX>
-static int launch_chunks(float* partial, const uint16_t* x, const int32_t* x_idx, int M, const hqm_weight* w, int G,
-                         int C, const StreamPlan& plan, cudaStream_t st) {
-    constexpr int TPT = 8 / codes_per_word(NBITS);
-    for (int m0 = 0; m0 < M;) {
-        const int left = M - m0;
-        int rc;
-        if (left <= TPT) {
-            rc = launch_one<NBITS, NB, 1>(partial, x, x_idx, left, m0, M, w, G, C, plan, st);
-            m0 += left;
-        } else if (left <= 2 * TPT || NT_MAX < 4) {
-            const int take = left < 2 * TPT ? left : 2 * TPT;
-            rc = launch_one<NBITS, NB, 2>(partial, x, x_idx, take, m0, M, w, G, C, plan, st);
-            m0 += take;
-        } else {
-            const int take = left < 4 * TPT ? left : 4 * TPT;
-            rc = launch_one<NBITS, NB, (NT_MAX >= 4 ? 4 : 2)>(partial, x, x_idx, take, m0, M, w, G, C, plan, st);
-            m0 += take;
-        }
-        if (rc != HQM_OK) return rc;
-    }
-    return HQM_OK;
+    return (size_t)plan.slots * (size_t)M * (size_t)N * sizeof(float);
 }
 
 int launch_gemv_stream_partials(float* partial, const uint16_t* x, const int32_t* x_idx, int64_t M,
                                 const hqm_weight* w, int G, int C, const StreamPlan& plan, cudaStream_t st) {
     const int nb = w->group_size / 16;
-    if (w->nbits == 2 && nb == 1) return launch_chunks<2, 1, 4>(partial, x, x_idx, (int)M, w, G, C, plan, st);
-    if (w->nbits == 2 && nb == 2) return launch_chunks<2, 2, 2>(partial, x, x_idx, (int)M, w, G, C, plan, st);
-    if (w->nbits == 4 && nb == 2) return launch_chunks<4, 2, 4>(partial, x, x_idx, (int)M, w, G, C, plan, st);
-    if (w->nbits == 4 && nb == 4) return launch_chunks<4, 4, 2>(partial, x, x_idx, (int)M, w, G, C, plan, st);
-    set_error("gemv_stream: no instantiation for nbits=%d group_size=%d", w->nbits, w->group_size);
-    return HQM_ERR_ARG;
+    const Split sp{plan.P, plan.PT, plan.grid};
+    // rows beyond one launch's column tiles go in further launches over the same split
+    for (int m0 = 0; m0 < (int)M; m0 += plan.chunk) {
+        const int take = ((int)M - m0 < plan.chunk) ? (int)M - m0 : plan.chunk;
+        const int rc = dispatch(w->nbits, nb, plan.nt, [&](auto b, auto k, auto t) {
+            constexpr int B = decltype(b)::value, NBK = decltype(k)::value, T = decltype(t)::value;
+            resident_grid<B, NBK, T>();     // sets the shared-memory attribute on first use
+            gemv_stream_kernel<B, NBK, T><<<plan.grid, 256, smem_bytes<B, NBK, T>(), st>>>(
+                partial, x, x_idx, take, m0, (int)M, *w, G, C, sp);
+            return 0;
+        });
+        if (rc != 0) {
+            set_error("gemv_stream: no instantiation for nbits=%d group_size=%d", w->nbits, w->group_size);
+            return HQM_ERR_ARG;
+        }
+        HQM_LAUNCH_CHECK();
+    }
+    return HQM_OK;
 }
 
-int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bias, int64_t M, int N, int SK,
-                           cudaStream_t st) {
-    const int64_t MN = M * N;
+int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bias, int64_t M, const hqm_weight* w,
+                           int G, const StreamPlan& plan, cudaStream_t st) {
+    const int64_t MN = M * w->N;
     int64_t blocks = (MN + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
-    finalize_linear_kernel<<<(int)blocks, 256, 0, st>>>(y, partial, bias, MN, N, SK);
+    finalize_linear_kernel<<<(int)blocks, 256, 0, st>>>(y, partial, bias, MN, w->N, G, codes_per_word(w->nbits),
+                                                       Split{plan.P, plan.PT, plan.grid});
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }

@@ -10,19 +10,20 @@ int launch_linear_generic(uint16_t* y, const uint16_t* x, const int32_t* x_idx, 
 
 // gemv_stream.cu — the weight-streaming path for small row counts.
 struct StreamPlan {
-    int P;             // storage-row residues = CTAs along the output rows
-    int passes_total;  // K / 64
-    int SK;            // K splits (CTAs along K); fp32 partials [SK][M][N]
-    int ppu;           // 64-column passes per CTA
-    int warps;         // warps per CTA
+    int P;       // storage-row residues
+    int PT;      // 64-column passes per residue (K / 64)
+    int grid;    // CTAs of the single-wave persistent grid
+    int nt;      // column tiles of the instantiation used
+    int chunk;   // rows of x served per launch
+    int slots;   // upper bound on the CTAs contributing to one residue: fp32 partials [slots][M][N]
 };
 // False when the layer / row count is outside what the streaming kernels cover.
 bool gemv_stream_plan(const hqm_weight* w, int G, int C, int64_t M, StreamPlan* plan);
 size_t gemv_stream_scratch_bytes(const StreamPlan& plan, int64_t M, int N);
 int launch_gemv_stream_partials(float* partial, const uint16_t* x, const int32_t* x_idx, int64_t M,
                                 const hqm_weight* w, int G, int C, const StreamPlan& plan, cudaStream_t st);
-int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bias, int64_t M, int N, int SK,
-                           cudaStream_t st);
+int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bias, int64_t M, const hqm_weight* w,
+                           int G, const StreamPlan& plan, cudaStream_t st);
 
 // Dispatcher used by hqm_linear and by the expert FFN: picks the streaming
 // kernel when the layer's shape allows it, the generic one otherwise.
