@@ -36,12 +36,41 @@ __global__ void scale_scatter_kernel(uint16_t* __restrict__ out, const uint16_t*
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+static bool same_format(const hqm_weight* a, const hqm_weight* b) {
+    return a->N == b->N && a->K == b->K && a->nbits == b->nbits && a->group_size == b->group_size &&
+           a->meta_group == b->meta_group;
+}
+
+// The streaming path for a whole expert: w1 and w3 in one launch, then w2.
+struct FusedPlan {
+    StreamPlan up, down;
+    int G1, C1, G2, C2;
+    size_t up_bytes, h_bytes, down_bytes;
+};
+static bool fused_plan(int64_t M, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3, const void* x,
+                       FusedPlan* fp) {
+    if (force_generic() || !same_format(w1, w3)) return false;
+    if (check_weight(w1, &fp->G1, &fp->C1) != HQM_OK || check_weight(w3, &fp->G1, &fp->C1) != HQM_OK ||
+        check_weight(w2, &fp->G2, &fp->C2) != HQM_OK)
+        return false;
+    if (x && (reinterpret_cast<uintptr_t>(x) & 15u) != 0) return false;
+    if (!gemv_stream_plan(w1, 2, fp->G1, fp->C1, M, &fp->up) || !gemv_stream_plan(w3, 2, fp->G1, fp->C1, M, &fp->up) ||
+        !gemv_stream_plan(w2, 1, fp->G2, fp->C2, M, &fp->down))
+        return false;
+    fp->up_bytes = align_up(gemv_stream_scratch_bytes(fp->up, M, w1->N), 256);
+    fp->h_bytes = align_up((size_t)M * w1->N * 2, 256);
+    fp->down_bytes = align_up(gemv_stream_scratch_bytes(fp->down, M, w2->N), 256);
+    return true;
+}
+
 }  // namespace hqm
 
 extern "C" {
 
 size_t hqm_expert_ffn_scratch_bytes(int64_t M, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3) {
     if (!w1 || !w2 || !w3 || M <= 0) return 0;
+    hqm::FusedPlan fp;
+    if (hqm::fused_plan(M, w1, w2, w3, nullptr, &fp)) return fp.up_bytes + fp.h_bytes + fp.down_bytes;
     const size_t a = hqm::align_up((size_t)M * (size_t)w1->N * 2, 256);
     const size_t b = hqm::align_up((size_t)M * (size_t)w3->N * 2, 256);
     const size_t c = hqm::align_up((size_t)M * (size_t)w2->N * 2, 256);
@@ -71,6 +100,20 @@ int hqm_expert_ffn(uint16_t* out, const uint16_t* x, int64_t M, const int32_t* t
     cudaStream_t st = (cudaStream_t)stream;
     const int F = w1->N, H = w2->N;
     uint8_t* p = (uint8_t*)scratch;
+    FusedPlan fp;
+    if (fused_plan(M, w1, w2, w3, x, &fp)) {
+        // 4 launches: [w1;w3] partials -> h = silu(a) * b -> w2 partials -> scale / accumulate into out
+        float* up = (float*)p;
+        uint16_t* h = (uint16_t*)(p + fp.up_bytes);
+        float* down = (float*)(p + fp.up_bytes + fp.h_bytes);
+        int rc = launch_gemv_stream_partials(up, x, token_idx, M, w1, w3, fp.G1, fp.C1, fp.up, st);
+        if (rc != HQM_OK) return rc;
+        rc = launch_finalize_silu_mul(h, up, M, w1, fp.G1, fp.up, st);
+        if (rc != HQM_OK) return rc;
+        rc = launch_gemv_stream_partials(down, h, nullptr, M, w2, nullptr, fp.G2, fp.C2, fp.down, st);
+        if (rc != HQM_OK) return rc;
+        return launch_finalize_scatter(out, down, token_idx, route_w, accumulate, M, w2, fp.G2, fp.down, st);
+    }
     uint16_t* a = (uint16_t*)p;
     p += align_up((size_t)M * F * 2, 256);
     uint16_t* b = (uint16_t*)p;

@@ -36,6 +36,7 @@
 //
 // HBM traffic per launch is the packed codes + scale_q + zero_q once (the meta and x
 // stay in L1/L2), which is the algorithmic minimum.
+#include <map>
 #include <type_traits>
 
 #include "common.cuh"
@@ -76,23 +77,42 @@ __device__ __forceinline__ __half2 meta_decode(uint32_t two_bytes_as_h2, __half2
 // (B0,B2,B1,B3), so in each 16-bit half the low byte belongs to columns k0 / k1 and
 // the high byte to k2 / k3.  lo(s) / hi(s) return the fp16 pair OFFSET + code of slot s
 // for (k0,k1) / (k2,k3).  OFF_LO / OFF_HI are those offsets as fp16 bit patterns.
+// (field & mask) | magic with mask and magic in registers: one LOP3.  Written as a literal
+// expression the two 32-bit immediates do not fit one instruction and it becomes two.
+__device__ __forceinline__ uint32_t and_or(uint32_t v, uint32_t mask, uint32_t magic) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(v), "r"(mask), "r"(magic));
+    return d;
+}
+
+// Masks and fp16 magic numbers of the extraction, passed as a kernel parameter so that
+// they live in (uniform) registers instead of being re-materialised as immediates.
+struct FieldConsts {
+    uint32_t mask_a, mask_b, mask_c;     // 2-bit: bits 7-6, 5-4, 9-8 of each half;  4-bit: bits 7-4
+    uint32_t magic_a, magic_b, magic_c;  // 16.0, 64.0, 4.0 in both halves
+};
+static inline FieldConsts field_consts(int nbits) {
+    if (nbits == 2) return FieldConsts{0x00C000C0u, 0x00300030u, 0x03000300u, 0x4C004C00u, 0x54005400u, 0x44004400u};
+    return FieldConsts{0x00F000F0u, 0u, 0u, 0x54005400u, 0u, 0u};
+}
+
 template <int NBITS> struct Fields;
 
 template <> struct Fields<2> {
     static constexpr int PER = 4;
     uint32_t v0, v1, v2, v3;
     __device__ __forceinline__ explicit Fields(uint32_t u) : v0(u), v1(u << 4), v2(u >> 4), v3(u >> 8) {}
-    template <int S> __device__ __forceinline__ uint32_t lo() const {
-        if (S == 0) return (v0 & 0x00C000C0u) | 0x4C004C00u;     // bits 7-6            -> 16 + c
-        if (S == 1) return (v0 & 0x00300030u) | 0x54005400u;     // bits 5-4            -> 64 + c
-        if (S == 2) return (v1 & 0x00C000C0u) | 0x4C004C00u;     // bits 3-2 moved to 7-6
-        return (v1 & 0x00300030u) | 0x54005400u;                 // bits 1-0 moved to 5-4
+    template <int S> __device__ __forceinline__ uint32_t lo(const FieldConsts& c) const {
+        if (S == 0) return and_or(v0, c.mask_a, c.magic_a);     // bits 7-6            -> 16 + code
+        if (S == 1) return and_or(v0, c.mask_b, c.magic_b);     // bits 5-4            -> 64 + code
+        if (S == 2) return and_or(v1, c.mask_a, c.magic_a);     // bits 3-2 moved to 7-6
+        return and_or(v1, c.mask_b, c.magic_b);                 // bits 1-0 moved to 5-4
     }
-    template <int S> __device__ __forceinline__ uint32_t hi() const {
-        if (S == 0) return (v3 & 0x00C000C0u) | 0x4C004C00u;     // bits 15-14 moved to 7-6
-        if (S == 1) return (v2 & 0x03000300u) | 0x44004400u;     // bits 13-12 moved to 9-8 -> 4 + c
-        if (S == 2) return (v2 & 0x00C000C0u) | 0x4C004C00u;     // bits 11-10 moved to 7-6
-        return (v0 & 0x03000300u) | 0x44004400u;                 // bits 9-8
+    template <int S> __device__ __forceinline__ uint32_t hi(const FieldConsts& c) const {
+        if (S == 0) return and_or(v3, c.mask_a, c.magic_a);     // bits 15-14 moved to 7-6
+        if (S == 1) return and_or(v2, c.mask_c, c.magic_c);     // bits 13-12 moved to 9-8 -> 4 + code
+        if (S == 2) return and_or(v2, c.mask_a, c.magic_a);     // bits 11-10 moved to 7-6
+        return and_or(v0, c.mask_c, c.magic_c);                 // bits 9-8
     }
     __host__ __device__ static constexpr uint32_t off_lo(int s) { return (s & 1) ? 0x5400u : 0x4C00u; }
     __host__ __device__ static constexpr uint32_t off_hi(int s) { return (s & 1) ? 0x4400u : 0x4C00u; }
@@ -102,11 +122,11 @@ template <> struct Fields<4> {
     static constexpr int PER = 2;
     uint32_t v0, v1, v2, v3;
     __device__ __forceinline__ explicit Fields(uint32_t u) : v0(u), v1(u << 4), v2(u >> 4), v3(u >> 8) {}
-    template <int S> __device__ __forceinline__ uint32_t lo() const {
-        return ((S == 0 ? v0 : v1) & 0x00F000F0u) | 0x54005400u;  // nibble at bits 7-4 -> 64 + c
+    template <int S> __device__ __forceinline__ uint32_t lo(const FieldConsts& c) const {
+        return and_or(S == 0 ? v0 : v1, c.mask_a, c.magic_a);   // nibble at bits 7-4 -> 64 + code
     }
-    template <int S> __device__ __forceinline__ uint32_t hi() const {
-        return ((S == 0 ? v3 : v2) & 0x00F000F0u) | 0x54005400u;
+    template <int S> __device__ __forceinline__ uint32_t hi(const FieldConsts& c) const {
+        return and_or(S == 0 ? v3 : v2, c.mask_a, c.magic_a);
     }
     __host__ __device__ static constexpr uint32_t off_lo(int) { return 0x5400u; }
     __host__ __device__ static constexpr uint32_t off_hi(int) { return 0x5400u; }
@@ -114,7 +134,7 @@ template <> struct Fields<4> {
 
 // --------------------------------------------------------------------------- kernel
 // Work split shared by the kernel and the finalize step: passes are numbered
-// L = rho * PT + p (PT = K / 64 passes per residue); CTA c owns [c*Ltot/grid, (c+1)*Ltot/grid).
+// L = rho * PT + p (PT passes per residue); CTA c owns [c*Ltot/grid, (c+1)*Ltot/grid).
 // (32-bit arithmetic throughout: the planner rejects layers with total() * grid >= 2^31.)
 struct Split {
     int P, PT, grid;
@@ -129,15 +149,28 @@ struct Split {
     }
 };
 
-// NB: blocks of 16 group members (group_size = 16*NB).  NT: column tiles of 8/PER tokens.
-template <int NBITS, int NB, int NT>
-struct Pass {
+// Compile-time shape of an instantiation.
+//   NB   blocks of 16 group members (group_size = 16 * NB)
+//   TOKS rows of x decoded per launch (1, 2, 4, 8, 16)
+template <int NBITS, int NB, int TOKS>
+struct Shape {
     static constexpr int PER = codes_per_word(NBITS);
-    static constexpr int MTOK = NT * (8 / PER);
-    static constexpr int DK = 64 / (32 / PER);     // decode columns per lane (8 or 4)
-    uint32_t sq[DK / 4], zq[DK / 4];
-    uint32_t mss[DK / 2], mzs[DK / 2], msz[DK / 2], mzz[DK / 2];
-    uint32_t xv[MTOK][DK / 2];
+    static constexpr int TPT = 8 / PER;                         // tokens per column tile
+    static constexpr int NT = (TOKS + TPT - 1) / TPT;           // column tiles
+    static constexpr int MTOK = NT * TPT;                       // token rows kept in shared memory
+    static constexpr int LPS = 32 / PER;                        // decode lanes per slot
+    static constexpr int DK = 64 / LPS;                         // decode columns per lane (8 or 4)
+    static constexpr int SUB = (NB == 1) ? 2 : 1;               // 64-column sub-passes per pass
+    static constexpr int PW = 64 * SUB;                         // pass width in columns
+    static constexpr bool STAGE_X = TOKS <= 2;                  // x converted to fp16 in shared memory per segment
+    static constexpr int ROW = 72;                              // 64 columns + padding against bank conflicts
+    static constexpr int WARP_HALFS = SUB * (MTOK + 1) * PER * ROW;
+    static constexpr int NW = 8;
+    static constexpr int RED_PER_WARP = NB * NT * 4 * 32;
+    static size_t smem_bytes(int K) {
+        return (size_t)NW * WARP_HALFS * sizeof(__half) + (size_t)NW * RED_PER_WARP * sizeof(float) +
+               (STAGE_X ? (size_t)TOKS * K * sizeof(__half) : 0);
+    }
 };
 
 template <int N> __device__ __forceinline__ void ld_words(uint32_t (&dst)[N], const void* p) {
@@ -159,57 +192,74 @@ template <int N> __device__ __forceinline__ void st_words(void* p, const uint32_
     }
 }
 
-template <int NBITS, int NB, int NT>
-__global__ void __launch_bounds__(256)
+// Up to two layers of identical shape share one launch (the expert's w1 and w3): their
+// residues are numbered one after the other and the output columns of layer 1 follow
+// those of layer 0.
+struct Layers {
+    hqm_weight w[2];
+    int count;
+};
+
+template <int NBITS, int NB, int TOKS>
+__global__ void __launch_bounds__(256, (NB == 1 && TOKS <= 2) ? 2 : 1)
 gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, const int32_t* __restrict__ x_idx,
-                   int M, int m_base, int M_total, hqm_weight w, int G, int C, Split sp) {
+                   int M, int m_base, int M_total, Layers ly, int G, int C, int P, Split sp, FieldConsts fc) {
     using F = Fields<NBITS>;
-    using PR = Pass<NBITS, NB, NT>;
-    constexpr int PER = F::PER;
-    constexpr int TPT = 8 / PER;            // tokens per column tile
-    constexpr int MTOK = NT * TPT;          // tokens this instantiation handles
-    constexpr int LPS = 32 / PER;           // decode lanes per slot
-    constexpr int DK = PR::DK;
-    constexpr int ROW = 72;                 // 64 columns + padding: rows of different slots hit different banks
-    constexpr int WARP_HALFS = (MTOK + 1) * PER * ROW;
-    constexpr int NW = 8;
-    constexpr int RED_PER_WARP = NB * NT * 4 * 32;
+    using S = Shape<NBITS, NB, TOKS>;
+    constexpr int PER = S::PER, TPT = S::TPT, NT = S::NT, MTOK = S::MTOK, LPS = S::LPS, DK = S::DK, SUB = S::SUB,
+                  PW = S::PW, ROW = S::ROW, NW = S::NW, RED_PER_WARP = S::RED_PER_WARP;
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int K = w.K, P = sp.P, PT = sp.PT;
-    __half* xs_w = reinterpret_cast<__half*>(smem_raw) + wi * WARP_HALFS;
-    __half* zz_w = xs_w + MTOK * PER * ROW;
-    float* red = reinterpret_cast<float*>(smem_raw + (size_t)NW * WARP_HALFS * sizeof(__half));
+    const int K = ly.w[0].K, N = ly.w[0].N, PT = sp.PT;
+    const int N_total = N * ly.count;
+    __half* xs_w = reinterpret_cast<__half*>(smem_raw) + wi * S::WARP_HALFS;      // [SUB][MTOK][PER][ROW]
+    __half* zz_w = xs_w + SUB * MTOK * PER * ROW;                                  // [SUB][PER][ROW]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)NW * S::WARP_HALFS * sizeof(__half));
+    __half* xh = reinterpret_cast<__half*>(red + NW * RED_PER_WARP);               // [TOKS][segment columns]
 
-    // rows of x this launch works on
-    const uint16_t* xr[MTOK];
+    // token rows that exist only to fill a column tile stay zero for the whole kernel
+    for (int i = lane; i < SUB * MTOK * PER * ROW / 2; i += 32) reinterpret_cast<uint32_t*>(xs_w)[i] = 0u;
+    __syncwarp();
+
+    const uint16_t* xr[TOKS];
 #pragma unroll
-    for (int m = 0; m < MTOK; ++m) {
+    for (int m = 0; m < TOKS; ++m) {
         const int mm = (m < M) ? (m_base + m) : m_base;
         xr[m] = x + (int64_t)(x_idx ? x_idx[mm] : mm) * K;
     }
-    const uint8_t* Wq = reinterpret_cast<const uint8_t*>(w.W_q);
     const int sd = lane / LPS;                      // slot this lane decodes
-    const int kd = (lane % LPS) * DK;               // its first column inside the pass
+    const int kd = (lane % LPS) * DK;               // its first column inside a sub-pass
     const int sB = g % PER, mB = g / PER;           // slot / token of this lane's B column
     const int sa = (2 * t) % PER;                   // first of the two slots whose columns this lane reads back
     const uint32_t keep = (g < PER) ? 0xffffffffu : 0u;
     const uint32_t olo = ((g & 1) ? F::off_lo(1) : F::off_lo(0)) * 0x00010001u & keep;
     const uint32_t ohi = ((g & 1) ? F::off_hi(1) : F::off_hi(0)) * 0x00010001u & keep;
-    // offsets of this lane's weight rows (bytes from W_q + rho*K + k0) and of its decode element
-    uint32_t qoff[NB];
+    uint32_t qoff[NB];                              // this lane's weight rows, bytes from W_q + rho*K + k0
 #pragma unroll
     for (int b = 0; b < NB; ++b) qoff[b] = (uint32_t)(16 * b + g) * (uint32_t)P * (uint32_t)K + 16u * t;
     const uint32_t qoff8 = 8u * (uint32_t)P * (uint32_t)K;
 
     const uint32_t L_begin = sp.begin(blockIdx.x), L_end = sp.begin(blockIdx.x + 1);
     for (uint32_t L = L_begin; L < L_end;) {
-        // ---- one segment: passes [pa, pb) of residue rho
-        const int rho = (int)(L / (uint32_t)PT), pa = (int)(L - (uint32_t)rho * (uint32_t)PT);
+        // ---- one segment: passes [pa, pb) of residue rho of layer `layer`
+        const int rho_g = (int)(L / (uint32_t)PT), pa = (int)(L - (uint32_t)rho_g * (uint32_t)PT);
         const int pb = min(PT, pa + (int)(L_end - L));
         L += (uint32_t)(pb - pa);
+        const int layer = rho_g / P, rho = rho_g - layer * P;
+        const hqm_weight& w = ly.w[layer];
+
+        if constexpr (S::STAGE_X) {
+            // the segment's columns of x, converted to fp16 once for all warps
+            const int c0 = pa * PW, nc = (pb - pa) * PW;
+#pragma unroll
+            for (int m = 0; m < TOKS; ++m)
+                for (int i = threadIdx.x * 2; i < nc; i += 2 * blockDim.x)
+                    *reinterpret_cast<__half2*>(xh + m * K + i) =
+                        bf16pair_to_h2(*reinterpret_cast<const uint32_t*>(xr[m] + c0 + i));
+            __syncthreads();
+        }
 
         float acc[NB][NT][PER][4];
         float accc[NT][4];
@@ -226,107 +276,142 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
 #pragma unroll
             for (int v = 0; v < 4; ++v) accc[tau][v] = 0.f;
 
-        const uint8_t* wrow = Wq + (size_t)rho * K;
+        const uint8_t* wrow = reinterpret_cast<const uint8_t*>(w.W_q) + (size_t)rho * K;
         const uint32_t dbase = (uint32_t)(PER * rho + sd) * (uint32_t)K + kd;     // flat scale/zero index at k0 = 0
-
         // meta column of a flat scale/zero index: the residue-row part is reduced once per segment,
-        // a pass then adds k0 < K and wraps with compares instead of a division
+        // each pass then adds its k0 (tracked modulo C) and wraps with a compare
         const uint32_t dcol0 = dbase % (uint32_t)C;
-        uint32_t kcol = (uint32_t)((pa + wi) * 64) % (uint32_t)C;     // (k0 % C) of the pass loaded next
-        auto col_of = [&](uint32_t) {
-            const uint32_t c = dcol0 + kcol;
-            kcol += 64u * NW;
-            while (kcol >= (uint32_t)C) kcol -= (uint32_t)C;
-            return c >= (uint32_t)C ? c - (uint32_t)C : c;
+        uint32_t kcol = (uint32_t)((pa + wi) * PW) % (uint32_t)C;     // (k0 % C) of the pass loaded next
+        const uint32_t kstep = (uint32_t)(PW * NW) % (uint32_t)C;
+        const uint32_t ustep = 64u % (uint32_t)C;
+
+        struct Meta {
+            uint32_t sq[SUB][DK / 4], zq[SUB][DK / 4];
+            uint32_t mss[SUB][DK / 2], mzs[SUB][DK / 2], msz[SUB][DK / 2], mzz[SUB][DK / 2];
+            uint32_t xv[S::STAGE_X ? 1 : TOKS][SUB][DK / 2];
         };
-        auto load_rows = [&](uint4 (&q0)[NB], uint4 (&q1)[NB], int p) {
-            const int k0 = p * 64;
-#pragma unroll
-            for (int b = 0; b < NB; ++b) {
-                q0[b] = ld_stream_16(wrow + k0 + qoff[b]);
-                q1[b] = ld_stream_16(wrow + k0 + qoff[b] + qoff8);
-            }
-        };
-        auto load_meta = [&](PR& r, int p) {
-            const int k0 = p * 64;
-            const uint32_t idx = dbase + k0;
-            const uint32_t col = col_of(idx);
-            ld_words(r.sq, w.scale_q + idx);
-            ld_words(r.zq, w.zero_q + idx);
-            ld_words(r.mss, w.ms_scale + col);
-            ld_words(r.mzs, w.mz_scale + col);
-            ld_words(r.msz, w.ms_zero + col);
-            ld_words(r.mzz, w.mz_zero + col);
-#pragma unroll
-            for (int m = 0; m < MTOK; ++m)
-                if (m < M) ld_words(r.xv[m], xr[m] + k0 + kd);
+        struct Rows {
+            uint4 q0[SUB][NB], q1[SUB][NB];
         };
 
-        auto decode_pass = [&](const PR& r) {
-            // ---- 1. decode scale / zero of (slot sd, DK columns) and fold into x
-            uint32_t s2[DK / 2], z2[DK / 2];
+        auto load_rows = [&](Rows& r, int p) {
+            const uint8_t* base = wrow + p * PW;
 #pragma unroll
-            for (int j = 0; j < DK / 2; ++j) {
-                const uint32_t sel = (j & 1) ? 0x4342u : 0x4140u;      // bytes (2j, 2j+1) of the word -> two fp16
-                s2[j] = h2_bits(meta_decode(prmt(r.sq[j / 2], 0x64646464u, sel), bits_h2(r.mzs[j]), bits_h2(r.mss[j])));
-                z2[j] = h2_bits(meta_decode(prmt(r.zq[j / 2], 0x64646464u, sel), bits_h2(r.mzz[j]), bits_h2(r.msz[j])));
+            for (int u = 0; u < SUB; ++u)
+#pragma unroll
+                for (int b = 0; b < NB; ++b) {
+                    r.q0[u][b] = ld_stream_16(base + qoff[b] + 64 * u);
+                    r.q1[u][b] = ld_stream_16(base + qoff[b] + qoff8 + 64 * u);
+                }
+        };
+        auto load_meta = [&](Meta& r, int p) {
+            const int k0 = p * PW;
+            const uint32_t idx = dbase + k0;
+#pragma unroll
+            for (int u = 0; u < SUB; ++u) {
+                uint32_t col = dcol0 + kcol;                      // < 2C
+                col = col >= (uint32_t)C ? col - (uint32_t)C : col;
+                if (u == 1) {
+                    col += ustep;
+                    col = col >= (uint32_t)C ? col - (uint32_t)C : col;
+                }
+                ld_words(r.sq[u], w.scale_q + idx + 64 * u);
+                ld_words(r.zq[u], w.zero_q + idx + 64 * u);
+                ld_words(r.mss[u], w.ms_scale + col);
+                ld_words(r.mzs[u], w.mz_scale + col);
+                ld_words(r.msz[u], w.ms_zero + col);
+                ld_words(r.mzz[u], w.mz_zero + col);
+                if constexpr (!S::STAGE_X) {
+#pragma unroll
+                    for (int m = 0; m < TOKS; ++m) ld_words(r.xv[m][u], xr[m] + k0 + 64 * u + kd);
+                }
             }
-            st_words(zz_w + sd * ROW + kd, z2);
+            kcol += kstep;
+            kcol = kcol >= (uint32_t)C ? kcol - (uint32_t)C : kcol;
+        };
+
+        // 1. decode scale / zero of (slot sd, DK columns per sub-pass), fold into x, publish to the warp
+        auto decode_pass = [&](const Meta& r, int p) {
 #pragma unroll
-            for (int m = 0; m < MTOK; ++m) {
-                uint32_t xs2[DK / 2];
+            for (int u = 0; u < SUB; ++u) {
+                uint32_t s2[DK / 2], z2[DK / 2];
 #pragma unroll
-                for (int j = 0; j < DK / 2; ++j)
-                    xs2[j] = (m < M) ? h2_bits(__hmul2(bf16pair_to_h2(r.xv[m][j]), bits_h2(s2[j]))) : 0u;
-                st_words(xs_w + (m * PER + sd) * ROW + kd, xs2);
+                for (int j = 0; j < DK / 2; ++j) {
+                    const uint32_t sel = (j & 1) ? 0x4342u : 0x4140u;      // bytes (2j, 2j+1) of the word -> two fp16
+                    s2[j] = h2_bits(meta_decode(prmt(r.sq[u][j / 2], 0x64646464u, sel), bits_h2(r.mzs[u][j]),
+                                                bits_h2(r.mss[u][j])));
+                    z2[j] = h2_bits(meta_decode(prmt(r.zq[u][j / 2], 0x64646464u, sel), bits_h2(r.mzz[u][j]),
+                                                bits_h2(r.msz[u][j])));
+                }
+                st_words(zz_w + (u * PER + sd) * ROW + kd, z2);
+#pragma unroll
+                for (int m = 0; m < TOKS; ++m) {
+                    uint32_t xs2[DK / 2];
+                    if constexpr (S::STAGE_X) {
+                        uint32_t xf[DK / 2];
+                        ld_words(xf, xh + m * K + (p - pa) * PW + 64 * u + kd);
+#pragma unroll
+                        for (int j = 0; j < DK / 2; ++j) xs2[j] = h2_bits(__hmul2(bits_h2(xf[j]), bits_h2(s2[j])));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < DK / 2; ++j)
+                            xs2[j] = h2_bits(__hmul2(bf16pair_to_h2(r.xv[m][u][j]), bits_h2(s2[j])));
+                    }
+                    st_words(xs_w + ((u * MTOK + m) * PER + sd) * ROW + kd, xs2);
+                }
             }
             __syncwarp();
         };
-        auto mma_pass = [&](const uint4 (&q0)[NB], const uint4 (&q1)[NB]) {
-            // ---- 2. B fragments: xs of (token mB, slot sB) at this lane's 16 columns
-            uint32_t bf[NT][8];
+
+        auto mma_pass = [&](const Rows& r) {
 #pragma unroll
-            for (int tau = 0; tau < NT; ++tau) {
-                const __half* src = xs_w + ((tau * TPT + mB) * PER + sB) * ROW + 16 * t;
-                const uint4 lo4 = *reinterpret_cast<const uint4*>(src);
-                const uint4 hi4 = *reinterpret_cast<const uint4*>(src + 8);
-                bf[tau][0] = lo4.x; bf[tau][1] = lo4.y; bf[tau][2] = lo4.z; bf[tau][3] = lo4.w;
-                bf[tau][4] = hi4.x; bf[tau][5] = hi4.y; bf[tau][6] = hi4.z; bf[tau][7] = hi4.w;
-            }
-            // ---- 3. correction tile: rows 0..PER-1 = z of slot i, rows 8..8+PER-1 = the offsets
-            {
-                uint32_t zf[8];
-                const __half* src = zz_w + (g < PER ? g : 0) * ROW + 16 * t;
-                const uint4 lo4 = *reinterpret_cast<const uint4*>(src);
-                const uint4 hi4 = *reinterpret_cast<const uint4*>(src + 8);
-                zf[0] = lo4.x & keep; zf[1] = lo4.y & keep; zf[2] = lo4.z & keep; zf[3] = lo4.w & keep;
-                zf[4] = hi4.x & keep; zf[5] = hi4.y & keep; zf[6] = hi4.z & keep; zf[7] = hi4.w & keep;
+            for (int u = 0; u < SUB; ++u) {
+                // 2. B fragments: xs of (token, slot sB) at this lane's 16 columns
+                uint32_t bf[NT][8];
 #pragma unroll
-                for (int wd = 0; wd < 4; ++wd)
+                for (int tau = 0; tau < NT; ++tau) {
+                    const __half* src = xs_w + ((u * MTOK + tau * TPT + mB) * PER + sB) * ROW + 16 * t;
+                    const uint4 lo4 = *reinterpret_cast<const uint4*>(src);
+                    const uint4 hi4 = *reinterpret_cast<const uint4*>(src + 8);
+                    bf[tau][0] = lo4.x; bf[tau][1] = lo4.y; bf[tau][2] = lo4.z; bf[tau][3] = lo4.w;
+                    bf[tau][4] = hi4.x; bf[tau][5] = hi4.y; bf[tau][6] = hi4.z; bf[tau][7] = hi4.w;
+                }
+                // 3. correction tile: rows 0..PER-1 = z of slot i, rows 8..8+PER-1 = the offsets
+                {
+                    uint32_t zf[8];
+                    const __half* src = zz_w + (u * PER + (g < PER ? g : 0)) * ROW + 16 * t;
+                    const uint4 lo4 = *reinterpret_cast<const uint4*>(src);
+                    const uint4 hi4 = *reinterpret_cast<const uint4*>(src + 8);
+                    zf[0] = lo4.x & keep; zf[1] = lo4.y & keep; zf[2] = lo4.z & keep; zf[3] = lo4.w & keep;
+                    zf[4] = hi4.x & keep; zf[5] = hi4.y & keep; zf[6] = hi4.z & keep; zf[7] = hi4.w & keep;
 #pragma unroll
-                    for (int tau = 0; tau < NT; ++tau)
-                        mma_f16(accc[tau], zf[2 * wd], olo, zf[2 * wd + 1], ohi, bf[tau][2 * wd], bf[tau][2 * wd + 1]);
-            }
-            // ---- 4. the weights
+                    for (int wd = 0; wd < 4; ++wd)
 #pragma unroll
-            for (int b = 0; b < NB; ++b) {
-                const uint32_t r0[4] = {q0[b].x, q0[b].y, q0[b].z, q0[b].w};
-                const uint32_t r1[4] = {q1[b].x, q1[b].y, q1[b].z, q1[b].w};
+                        for (int tau = 0; tau < NT; ++tau)
+                            mma_f16(accc[tau], zf[2 * wd], olo, zf[2 * wd + 1], ohi, bf[tau][2 * wd],
+                                    bf[tau][2 * wd + 1]);
+                }
+                // 4. the weights
 #pragma unroll
-                for (int wd = 0; wd < 4; ++wd) {
-                    const F f0(prmt(r0[wd], 0u, 0x3120u)), f1(prmt(r1[wd], 0u, 0x3120u));
+                for (int b = 0; b < NB; ++b) {
+                    const uint32_t r0[4] = {r.q0[u][b].x, r.q0[u][b].y, r.q0[u][b].z, r.q0[u][b].w};
+                    const uint32_t r1[4] = {r.q1[u][b].x, r.q1[u][b].y, r.q1[u][b].z, r.q1[u][b].w};
 #pragma unroll
-                    for (int tau = 0; tau < NT; ++tau) {
-                        const uint32_t b0 = bf[tau][2 * wd], b1 = bf[tau][2 * wd + 1];
-                        mma_f16(acc[b][tau][0], f0.template lo<0>(), f1.template lo<0>(), f0.template hi<0>(),
-                                f1.template hi<0>(), b0, b1);
-                        mma_f16(acc[b][tau][1], f0.template lo<1>(), f1.template lo<1>(), f0.template hi<1>(),
-                                f1.template hi<1>(), b0, b1);
-                        if constexpr (PER == 4) {
-                            mma_f16(acc[b][tau][PER - 2], f0.template lo<2>(), f1.template lo<2>(),
-                                    f0.template hi<2>(), f1.template hi<2>(), b0, b1);
-                            mma_f16(acc[b][tau][PER - 1], f0.template lo<3>(), f1.template lo<3>(),
-                                    f0.template hi<3>(), f1.template hi<3>(), b0, b1);
+                    for (int wd = 0; wd < 4; ++wd) {
+                        const F f0(prmt(r0[wd], 0u, 0x3120u)), f1(prmt(r1[wd], 0u, 0x3120u));
+#pragma unroll
+                        for (int tau = 0; tau < NT; ++tau) {
+                            const uint32_t b0 = bf[tau][2 * wd], b1 = bf[tau][2 * wd + 1];
+                            mma_f16(acc[b][tau][0], f0.template lo<0>(fc), f1.template lo<0>(fc), f0.template hi<0>(fc),
+                                    f1.template hi<0>(fc), b0, b1);
+                            mma_f16(acc[b][tau][1], f0.template lo<1>(fc), f1.template lo<1>(fc), f0.template hi<1>(fc),
+                                    f1.template hi<1>(fc), b0, b1);
+                            if constexpr (PER == 4) {
+                                mma_f16(acc[b][tau][PER - 2], f0.template lo<2>(fc), f1.template lo<2>(fc),
+                                        f0.template hi<2>(fc), f1.template hi<2>(fc), b0, b1);
+                                mma_f16(acc[b][tau][PER - 1], f0.template lo<3>(fc), f1.template lo<3>(fc),
+                                        f0.template hi<3>(fc), f1.template hi<3>(fc), b0, b1);
+                            }
                         }
                     }
                 }
@@ -335,28 +420,32 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
         };
 
         // ---- the warp's passes of this segment.  The decode inputs are dead once decoded, so the
-        // next pass's are requested into the same registers right away; the next weight rows go to
-        // a second register set.  Both are in flight while the tensor-core phase of this pass runs.
-        PR d;
-        uint4 qa0[NB], qa1[NB], qb0[NB], qb1[NB];
+        // next pass's are requested into the same registers right away; the weight rows alternate
+        // between two register sets.  Both are in flight while the tensor-core phase of a pass runs.
+        Meta d;
+        Rows ra, rb;
         int p = pa + wi;
         if (p < pb) {
-            load_rows(qa0, qa1, p);
+            load_rows(ra, p);
             load_meta(d, p);
         }
         while (p < pb) {
-            decode_pass(d);
-            const int pn = p + NW;
+            decode_pass(d, p);
+            int pn = p + NW;
             if (pn < pb) {
                 load_meta(d, pn);
-                load_rows(qb0, qb1, pn);
+                load_rows(rb, pn);
             }
-            mma_pass(qa0, qa1);
-#pragma unroll
-            for (int b = 0; b < NB; ++b) {
-                qa0[b] = qb0[b];
-                qa1[b] = qb1[b];
+            mma_pass(ra);
+            p = pn;
+            if (p >= pb) break;
+            decode_pass(d, p);
+            pn = p + NW;
+            if (pn < pb) {
+                load_meta(d, pn);
+                load_rows(ra, pn);
             }
+            mma_pass(rb);
             p = pn;
         }
 
@@ -388,7 +477,7 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
             }
         }
         __syncthreads();
-        const int slot_idx = blockIdx.x - sp.owner((uint32_t)rho * (uint32_t)PT);
+        const int slot_idx = blockIdx.x - sp.owner((uint32_t)rho_g * (uint32_t)PT);
         for (int e = threadIdx.x; e < RED_PER_WARP; e += blockDim.x) {
             float sum = 0.f;
 #pragma unroll
@@ -400,129 +489,189 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
             const int m = tau * TPT + (2 * te) / PER;
             const int member = 16 * b + ge + 8 * (v >> 1);
             if (m < M) {
-                const int64_t n = (int64_t)member * G + PER * rho + slot;
-                partial[((int64_t)slot_idx * M_total + m_base + m) * w.N + n] = sum;
+                const int64_t n = (int64_t)layer * N + (int64_t)member * G + PER * rho + slot;
+                partial[((int64_t)slot_idx * M_total + m_base + m) * N_total + n] = sum;
             }
         }
-        __syncthreads();   // `red` is reused by the next segment
+        __syncthreads();   // `red` and the staged x are reused by the next segment
     }
 }
 
-// y = bf16( sum over the CTAs that hold a piece of row n's residue + bias )
+// Number of partial row-sets that hold a piece of output column n (of N_total = layers * N).
+__device__ __forceinline__ int partial_count(const Split& sp, int n, int N, int G, int per, int P) {
+    const int layer = n / N, nn = n - layer * N;
+    const uint32_t rho_g = (uint32_t)(layer * P + (nn % G) / per);
+    return sp.owner(rho_g * sp.PT + sp.PT - 1) - sp.owner(rho_g * sp.PT) + 1;
+}
+
+// y = bf16( sum of the partials + bias )
 __global__ void finalize_linear_kernel(uint16_t* __restrict__ y, const float* __restrict__ partial,
-                                       const uint16_t* __restrict__ bias, int64_t MN, int N, int G, int per, Split sp) {
+                                       const uint16_t* __restrict__ bias, int64_t MN, int N, int G, int per, int P,
+                                       Split sp) {
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < MN; i += (int64_t)gridDim.x * blockDim.x) {
         const int n = (int)(i % N);
-        const int rho = (n % G) / per;
-        const int first = sp.owner((uint32_t)rho * sp.PT), last = sp.owner((uint32_t)rho * sp.PT + sp.PT - 1);
+        const int cnt = partial_count(sp, n, N, G, per, P);
         float v = 0.f;
-        for (int s = 0; s <= last - first; ++s) v += partial[s * MN + i];
+        for (int s = 0; s < cnt; ++s) v += partial[s * MN + i];
         if (bias) v += bf16_bits_to_float(bias[n]);
         y[i] = float_to_bf16_bits(v);
+    }
+}
+
+// h[m, f] = bf16( bf16(silu(bf16(a))) * bf16(b) ) with a / b the summed partials of the
+// w1 / w3 halves of a two-layer launch (columns f and F + f).
+__global__ void finalize_silu_mul_kernel(uint16_t* __restrict__ h, const float* __restrict__ partial, int64_t M,
+                                         int F, int G, int per, int P, Split sp) {
+    const int64_t MF = M * F, M2F = 2 * MF;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < MF; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / F;
+        const int f = (int)(i - m * F);
+        const int cnt = partial_count(sp, f, F, G, per, P);      // same split position for both halves? no: count each
+        const int cnt3 = partial_count(sp, F + f, F, G, per, P);
+        float a = 0.f, b = 0.f;
+        for (int s = 0; s < cnt; ++s) a += partial[s * M2F + m * 2 * F + f];
+        for (int s = 0; s < cnt3; ++s) b += partial[s * M2F + m * 2 * F + F + f];
+        a = round_bf16(a);
+        b = round_bf16(b);
+        const float act = round_bf16(a / (1.f + __expf(-a)));
+        h[i] = float_to_bf16_bits(act * b);
+    }
+}
+
+// out[t] = (accumulate ? out[t] : 0) + bf16(w_i * bf16(sum of the partials)), t = token_idx[i]
+__global__ void finalize_scatter_kernel(uint16_t* __restrict__ out, const float* __restrict__ partial,
+                                        const int32_t* __restrict__ token_idx, const float* __restrict__ route_w,
+                                        int64_t M, int H, int G, int per, int P, int accumulate, Split sp) {
+    const int64_t MH = M * H;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < MH; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / H;
+        const int n = (int)(i - m * H);
+        const int cnt = partial_count(sp, n, H, G, per, P);
+        float v = 0.f;
+        for (int s = 0; s < cnt; ++s) v += partial[s * MH + i];
+        const int64_t tk = token_idx ? token_idx[m] : m;
+        const float wgt = route_w ? route_w[m] : 1.f;
+        v = round_bf16(round_bf16(v) * wgt);
+        uint16_t* dst = out + tk * H + n;
+        *dst = float_to_bf16_bits(accumulate ? bf16_bits_to_float(*dst) + v : v);
     }
 }
 
 // --------------------------------------------------------------------------- host side
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-template <int NBITS, int NB, int NT>
-static size_t smem_bytes() {
-    constexpr int PER = codes_per_word(NBITS);
-    constexpr int MTOK = NT * (8 / PER);
-    return 8 * ((size_t)(MTOK + 1) * PER * 72 * sizeof(__half) + (size_t)NB * NT * 4 * 32 * sizeof(float));
-}
-
-// Resident CTAs per SM of an instantiation (queried once), times the SM count.
-template <int NBITS, int NB, int NT>
-static int resident_grid() {
-    static int cached = 0;
-    if (cached == 0) {
-        auto kern = gemv_stream_kernel<NBITS, NB, NT>;
-        const size_t smem = smem_bytes<NBITS, NB, NT>();
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+// Resident CTAs per SM of an instantiation for a given K, times the SM count.
+template <int NBITS, int NB, int TOKS>
+static int resident_grid(int K) {
+    using S = Shape<NBITS, NB, TOKS>;
+    static std::map<int, int> cache;                 // K -> grid (host-side, one entry per layer width seen)
+    static size_t max_smem = 0;
+    auto it = cache.find(K);
+    if (it != cache.end()) return it->second;
+    int cached = 0;
+    {
+        auto kern = gemv_stream_kernel<NBITS, NB, TOKS>;
+        const size_t smem = S::smem_bytes(K);
+        if (smem > 227 * 1024) return 0;
+        if (smem > max_smem) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+                cudaGetLastError();
+                return 0;
+            }
+            max_smem = smem;
+        }
         int per_sm = 0, dev = 0, sms = 148;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 256, smem) != cudaSuccess || per_sm < 1)
-            per_sm = 1;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 256, smem) != cudaSuccess || per_sm < 1) {
+            cudaGetLastError();
+            return 0;
+        }
         cached = per_sm * sms;
+        cache[K] = cached;
     }
     return cached;
 }
 
-// The instantiation that serves `tokens` rows of a layer in one launch.
-static int tiles_for(int nbits, int nb, int tokens) {
-    const int tpt = 8 / codes_per_word(nbits);
-    const int nt_max = ((nbits == 2 && nb == 1) || (nbits == 4 && nb == 2)) ? 4 : 2;
-    int nt = 1;
-    while (nt < nt_max && nt * tpt < tokens) nt *= 2;
-    return nt;
+// Rows of x one launch decodes for `tokens` pending rows.
+static int toks_for(int nbits, int nb, int tokens) {
+    const int max_toks = (nbits == 2) ? (nb == 1 ? 8 : 4) : (nb == 2 ? 16 : 8);
+    int tk = 1;
+    while (tk < max_toks && tk < tokens) tk *= 2;
+    if (nbits == 4 && tk == 2) tk = 4;           // a 4-bit column tile holds 4 tokens anyway
+    return tk;
 }
 
 template <typename Fn>
-static int dispatch(int nbits, int nb, int nt, Fn&& fn) {
-#define HQM_CASE(B, NBK, T) if (nbits == B && nb == NBK && nt == T) return fn(std::integral_constant<int, B>(), std::integral_constant<int, NBK>(), std::integral_constant<int, T>());
-    HQM_CASE(2, 1, 1) HQM_CASE(2, 1, 2) HQM_CASE(2, 1, 4)
-    HQM_CASE(2, 2, 1) HQM_CASE(2, 2, 2)
-    HQM_CASE(4, 2, 1) HQM_CASE(4, 2, 2) HQM_CASE(4, 2, 4)
-    HQM_CASE(4, 4, 1) HQM_CASE(4, 4, 2)
+static int dispatch(int nbits, int nb, int toks, Fn&& fn) {
+#define HQM_CASE(B, NBK, T) \
+    if (nbits == B && nb == NBK && toks == T) \
+        return fn(std::integral_constant<int, B>(), std::integral_constant<int, NBK>(), std::integral_constant<int, T>());
+    HQM_CASE(2, 1, 1) HQM_CASE(2, 1, 2) HQM_CASE(2, 1, 4) HQM_CASE(2, 1, 8)
+    HQM_CASE(2, 2, 1) HQM_CASE(2, 2, 2) HQM_CASE(2, 2, 4)
+    HQM_CASE(4, 2, 1) HQM_CASE(4, 2, 4) HQM_CASE(4, 2, 8) HQM_CASE(4, 2, 16)
+    HQM_CASE(4, 4, 1) HQM_CASE(4, 4, 4) HQM_CASE(4, 4, 8)
 #undef HQM_CASE
     return -1;
 }
 
-bool gemv_stream_plan(const hqm_weight* w, int G, int C, int64_t M, StreamPlan* plan) {
+bool gemv_stream_plan(const hqm_weight* w, int layers, int G, int C, int64_t M, StreamPlan* plan) {
     if (w->nbits != 2 && w->nbits != 4) return false;
     const int per = codes_per_word(w->nbits);
     const int dk = w->nbits == 2 ? 8 : 4;
     const int g = w->group_size;
     const bool group_ok = (w->nbits == 2) ? (g == 16 || g == 32) : (g == 32 || g == 64);
-    if (!group_ok || G % per != 0 || w->K % 64 != 0 || C % dk != 0) return false;
+    const int nb = g / 16;
+    const int pw = nb == 1 ? 128 : 64;
+    if (!group_ok || G % per != 0 || w->K % pw != 0 || C % dk != 0) return false;
     if (M < 1 || M > 16) return false;
     if ((int64_t)G * w->K >= (int64_t)1 << 31 || (int64_t)(w->N / per) * w->K >= (int64_t)1 << 31) return false;
     if (!aligned16(w->W_q) || !aligned16(w->scale_q) || !aligned16(w->zero_q) || !aligned16(w->ms_scale) ||
         !aligned16(w->mz_scale) || !aligned16(w->ms_zero) || !aligned16(w->mz_zero))
         return false;
-    const int nb = g / 16;
-    // the grid of the widest instantiation any chunk of these M rows uses decides the split
-    const int tpt = 8 / per;
-    const int nt = tiles_for(w->nbits, nb, (int)M);
-    int grid = dispatch(w->nbits, nb, nt, [](auto b, auto k, auto t) {
-        return resident_grid<decltype(b)::value, decltype(k)::value, decltype(t)::value>();
+    const int toks = toks_for(w->nbits, nb, (int)M);
+    const int K = w->K;
+    int grid = dispatch(w->nbits, nb, toks, [K](auto b, auto k, auto t) {
+        return resident_grid<decltype(b)::value, decltype(k)::value, decltype(t)::value>(K);
     });
     if (grid <= 0) return false;
     plan->P = G / per;
-    plan->PT = w->K / 64;
-    const int64_t total = (int64_t)plan->P * plan->PT;
+    plan->layers = layers;
+    plan->PT = w->K / pw;
+    const int64_t total = (int64_t)plan->P * layers * plan->PT;
     if (grid > total) grid = (int)total;
     if (total * grid >= ((int64_t)1 << 31)) return false;
     plan->grid = grid;
-    plan->nt = nt;
-    plan->chunk = nt * tpt;
+    plan->toks = toks;
     const int64_t min_range = total / grid;                   // >= 1
     plan->slots = (int)((plan->PT + min_range - 1) / min_range) + 1;
     return true;
 }
 
 size_t gemv_stream_scratch_bytes(const StreamPlan& plan, int64_t M, int N) {
-    return (size_t)plan.slots * (size_t)M * (size_t)N * sizeof(float);
+    return (size_t)plan.slots * (size_t)M * (size_t)N * (size_t)plan.layers * sizeof(float);
 }
 
 int launch_gemv_stream_partials(float* partial, const uint16_t* x, const int32_t* x_idx, int64_t M,
-                                const hqm_weight* w, int G, int C, const StreamPlan& plan, cudaStream_t st) {
-    const int nb = w->group_size / 16;
-    const Split sp{plan.P, plan.PT, plan.grid};
-    // rows beyond one launch's column tiles go in further launches over the same split
-    for (int m0 = 0; m0 < (int)M; m0 += plan.chunk) {
-        const int take = ((int)M - m0 < plan.chunk) ? (int)M - m0 : plan.chunk;
-        const int rc = dispatch(w->nbits, nb, plan.nt, [&](auto b, auto k, auto t) {
+                                const hqm_weight* w0, const hqm_weight* w1, int G, int C, const StreamPlan& plan,
+                                cudaStream_t st) {
+    const int nb = w0->group_size / 16;
+    const Split sp{plan.P * plan.layers, plan.PT, plan.grid};
+    Layers ly;
+    ly.w[0] = *w0;
+    ly.w[1] = w1 ? *w1 : *w0;
+    ly.count = plan.layers;
+    // rows beyond one launch's tokens go in further launches over the same split
+    for (int m0 = 0; m0 < (int)M; m0 += plan.toks) {
+        const int take = ((int)M - m0 < plan.toks) ? (int)M - m0 : plan.toks;
+        const int rc = dispatch(w0->nbits, nb, plan.toks, [&](auto b, auto k, auto t) {
             constexpr int B = decltype(b)::value, NBK = decltype(k)::value, T = decltype(t)::value;
-            resident_grid<B, NBK, T>();     // sets the shared-memory attribute on first use
-            gemv_stream_kernel<B, NBK, T><<<plan.grid, 256, smem_bytes<B, NBK, T>(), st>>>(
-                partial, x, x_idx, take, m0, (int)M, *w, G, C, sp);
+            gemv_stream_kernel<B, NBK, T><<<plan.grid, 256, Shape<B, NBK, T>::smem_bytes(w0->K), st>>>(
+                partial, x, x_idx, take, m0, (int)M, ly, G, C, plan.P, sp, field_consts(w0->nbits));
             return 0;
         });
         if (rc != 0) {
-            set_error("gemv_stream: no instantiation for nbits=%d group_size=%d", w->nbits, w->group_size);
+            set_error("gemv_stream: no instantiation for nbits=%d group_size=%d", w0->nbits, w0->group_size);
             return HQM_ERR_ARG;
         }
         HQM_LAUNCH_CHECK();
@@ -530,13 +679,35 @@ int launch_gemv_stream_partials(float* partial, const uint16_t* x, const int32_t
     return HQM_OK;
 }
 
+static inline int blocks_for(int64_t n) {
+    int64_t blocks = (n + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    return (int)(blocks < 1 ? 1 : blocks);
+}
+
 int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bias, int64_t M, const hqm_weight* w,
                            int G, const StreamPlan& plan, cudaStream_t st) {
     const int64_t MN = M * w->N;
-    int64_t blocks = (MN + 255) / 256;
-    if (blocks > 148 * 8) blocks = 148 * 8;
-    finalize_linear_kernel<<<(int)blocks, 256, 0, st>>>(y, partial, bias, MN, w->N, G, codes_per_word(w->nbits),
-                                                       Split{plan.P, plan.PT, plan.grid});
+    finalize_linear_kernel<<<blocks_for(MN), 256, 0, st>>>(y, partial, bias, MN, w->N, G, codes_per_word(w->nbits),
+                                                           plan.P, Split{plan.P * plan.layers, plan.PT, plan.grid});
+    HQM_LAUNCH_CHECK();
+    return HQM_OK;
+}
+
+int launch_finalize_silu_mul(uint16_t* h, const float* partial, int64_t M, const hqm_weight* w1, int G,
+                             const StreamPlan& plan, cudaStream_t st) {
+    finalize_silu_mul_kernel<<<blocks_for(M * w1->N), 256, 0, st>>>(
+        h, partial, M, w1->N, G, codes_per_word(w1->nbits), plan.P, Split{plan.P * plan.layers, plan.PT, plan.grid});
+    HQM_LAUNCH_CHECK();
+    return HQM_OK;
+}
+
+int launch_finalize_scatter(uint16_t* out, const float* partial, const int32_t* token_idx, const float* route_w,
+                            int accumulate, int64_t M, const hqm_weight* w2, int G, const StreamPlan& plan,
+                            cudaStream_t st) {
+    finalize_scatter_kernel<<<blocks_for(M * w2->N), 256, 0, st>>>(
+        out, partial, token_idx, route_w, M, w2->N, G, codes_per_word(w2->nbits), plan.P, accumulate,
+        Split{plan.P * plan.layers, plan.PT, plan.grid});
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }

@@ -10,20 +10,27 @@ int launch_linear_generic(uint16_t* y, const uint16_t* x, const int32_t* x_idx, 
 
 // gemv_stream.cu — the weight-streaming path for small row counts.
 struct StreamPlan {
-    int P;       // storage-row residues
-    int PT;      // 64-column passes per residue (K / 64)
+    int P;       // storage-row residues of one layer
+    int layers;  // 1, or 2 when an expert's w1 and w3 share the launch
+    int PT;      // passes per residue (K / pass width)
     int grid;    // CTAs of the single-wave persistent grid
-    int nt;      // column tiles of the instantiation used
-    int chunk;   // rows of x served per launch
-    int slots;   // upper bound on the CTAs contributing to one residue: fp32 partials [slots][M][N]
+    int toks;    // rows of x decoded per launch
+    int slots;   // upper bound on the CTAs contributing to one residue: fp32 partials [slots][M][layers*N]
 };
 // False when the layer / row count is outside what the streaming kernels cover.
-bool gemv_stream_plan(const hqm_weight* w, int G, int C, int64_t M, StreamPlan* plan);
+bool gemv_stream_plan(const hqm_weight* w, int layers, int G, int C, int64_t M, StreamPlan* plan);
 size_t gemv_stream_scratch_bytes(const StreamPlan& plan, int64_t M, int N);
 int launch_gemv_stream_partials(float* partial, const uint16_t* x, const int32_t* x_idx, int64_t M,
-                                const hqm_weight* w, int G, int C, const StreamPlan& plan, cudaStream_t st);
+                                const hqm_weight* w0, const hqm_weight* w1, int G, int C, const StreamPlan& plan,
+                                cudaStream_t st);
 int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bias, int64_t M, const hqm_weight* w,
                            int G, const StreamPlan& plan, cudaStream_t st);
+int launch_finalize_silu_mul(uint16_t* h, const float* partial, int64_t M, const hqm_weight* w1, int G,
+                             const StreamPlan& plan, cudaStream_t st);
+int launch_finalize_scatter(uint16_t* out, const float* partial, const int32_t* token_idx, const float* route_w,
+                            int accumulate, int64_t M, const hqm_weight* w2, int G, const StreamPlan& plan,
+                            cudaStream_t st);
+bool force_generic();
 
 // Dispatcher used by hqm_linear and by the expert FFN: picks the streaming
 // kernel when the layer's shape allows it, the generic one otherwise.
