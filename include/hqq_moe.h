@@ -90,6 +90,21 @@ size_t hqm_linear_scratch_bytes(int64_t M, const hqm_weight* w);
 int hqm_linear(uint16_t* y, const uint16_t* x, int64_t M, const hqm_weight* w, const uint16_t* bias,
                void* scratch, size_t scratch_bytes, void* stream);
 
+/* Same result as hqm_linear, for callers that cannot hand over a scratch buffer: code
+ * running under CUDA stream capture (where allocating is not allowed), hosts that pass
+ * raw pointers but own no device allocator, loops whose memory plan is frozen.  It has
+ * no counterpart in the reference.  The partial sums go to a workspace built into the
+ * library image (hqm_static_scratch_capacity() bytes, 2 MiB, held on every GPU that
+ * loads the library until the process exits); the call allocates nothing.  A call that
+ * would need more returns HQM_ERR_SCRATCH and says how much.  The first call on each
+ * device looks up the workspace address (and, like hqm_linear, queries occupancy for a
+ * new layer width), so make one call per device before starting a stream capture.  All
+ * calls share the one workspace: calls that overlap on the GPU (different streams,
+ * different threads) race; serialise them.  Nothing needs to be cleared between calls. */
+size_t hqm_static_scratch_capacity(void);
+int hqm_linear_static_scratch(uint16_t* y, const uint16_t* x, int64_t M, const hqm_weight* w, const uint16_t* bias,
+                              void* stream);
+
 /* ---- expert FFN: src/custom_layers.py:243-256 and :297-312 --------------- */
 /* Bytes of scratch hqm_expert_ffn needs for M routed rows. */
 size_t hqm_expert_ffn_scratch_bytes(int64_t M, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3);

@@ -45,6 +45,8 @@ SIGNATURES = {
     "hqm_dequantize": (C.c_int, [_P, C.c_int, _WP, _P]),
     "hqm_linear_scratch_bytes": (C.c_size_t, [_I64, _WP]),
     "hqm_linear": (C.c_int, [_P, _P, _I64, _WP, _P, _P, C.c_size_t, _P]),
+    "hqm_static_scratch_capacity": (C.c_size_t, []),
+    "hqm_linear_static_scratch": (C.c_int, [_P, _P, _I64, _WP, _P, _P]),
     "hqm_expert_ffn_scratch_bytes": (C.c_size_t, [_I64, _WP, _WP, _WP]),
     "hqm_expert_ffn": (C.c_int, [_P, _P, _I64, _P, _P, C.c_int, _WP, _WP, _WP, _P, C.c_size_t, _P]),
     "hqm_router_top2": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),
