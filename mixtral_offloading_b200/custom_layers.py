@@ -286,7 +286,8 @@ class SparseMoeWrapper(nn.Module):
         E = self.num_experts
         logits, _, _, meta, token_idx, token_w = self.route(x2)
         if self._host_counts is None:
-            self._host_counts = torch.empty((2 * E + 1,), dtype=torch.int32).pin_memory()
+            with torch.inference_mode(False):     # a normal tensor: it is written from any mode later
+                self._host_counts = torch.empty((2 * E + 1,), dtype=torch.int32).pin_memory()
         self._host_counts.copy_(meta, non_blocking=True)
         torch.cuda.current_stream(x2.device).synchronize()
         host = self._host_counts.tolist()

@@ -227,10 +227,13 @@ def router_top2(x: torch.Tensor, gate_w: torch.Tensor, top_k: int = 2, round_to=
     return logits, w, idx
 
 
-def moe_forward(x: torch.Tensor, gate_w: torch.Tensor, experts: list, round_to=torch.bfloat16):
+def moe_forward(x: torch.Tensor, gate_w: torch.Tensor, experts: list, round_to=torch.bfloat16, routing=None):
     """SparseMoeWrapper.forward, custom_layers.py:272-314, with every expert resident.
-    `experts` is a list of (w1, w2, w3) layer dictionaries."""
+    `experts` is a list of (w1, w2, w3) layer dictionaries.  `routing` = (weights, indices)
+    replaces the router's decision (used to take near-ties of rounded logits out of a comparison)."""
     logits, w, idx = router_top2(x, gate_w, round_to=round_to)
+    if routing is not None:
+        w, idx = routing[0].to(torch.float32), routing[1].to(torch.int64)
     if round_to is not None:
         w = w.to(round_to).to(torch.float32)                              # custom_layers.py:282
     out = torch.zeros(x.shape[0], x.shape[1], dtype=torch.float32)

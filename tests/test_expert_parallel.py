@@ -1,0 +1,151 @@
+"""Expert-parallel MoE block: partition and combine logic on CPU ranks (gloo, world size 2), and the
+real thing on 2 GPUs when they are there."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from mixtral_offloading_b200.expert_parallel import ExpertParallelMoe, expert_owner, owner_layout
+from oracle import hqq_oracle as O
+from tests.helpers import random_layer
+
+
+class Cfg:
+    def __init__(self, hidden, ffn, n_exp):
+        self.hidden_size, self.intermediate_size, self.num_local_experts = hidden, ffn, n_exp
+        self.num_experts_per_tok, self.hidden_act = 2, "silu"
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _problem(hidden=128, ffn=256, n_exp=4, tokens=7):
+    experts = [tuple(random_layer(n, k, 2, 16, seed=10 * e + i) for i, (n, k) in
+                     enumerate(((ffn, hidden), (hidden, ffn), (ffn, hidden)))) for e in range(n_exp)]
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(tokens, hidden, generator=g).to(torch.bfloat16)
+    gate_w = (torch.randn(n_exp, hidden, generator=g) * 0.02).to(torch.bfloat16)
+    return hidden, ffn, n_exp, experts, x, gate_w
+
+
+def test_owner_layout_and_partition():
+    per, perm = owner_layout(7, 4)
+    assert per == 2 and sorted(perm.tolist()) == sorted(set(perm.tolist())) and int(perm.max()) < 8
+    for t in range(7):
+        assert perm[t] // per == t % 4                      # grouped by owner
+    assert [expert_owner(e, 8, 4) for e in range(8)] == [0, 0, 1, 1, 2, 2, 3, 3]
+    with pytest.raises(AssertionError):
+        expert_owner(0, 8, 3)
+
+
+class OracleRankMoe(ExpertParallelMoe):
+    """The same module with the device pieces replaced by the CPU oracle, so that the sharding and
+    the collectives can run as gloo ranks."""
+
+    def __init__(self, *a, experts=None, gate_w=None, **k):
+        super().__init__(*a, **k)
+        self._experts, self._gate_w = experts, gate_w
+
+    def route(self, x2d):
+        logits, w, idx = O.router_top2(x2d, self._gate_w, round_to=torch.bfloat16)
+        w = w.to(torch.bfloat16).float()
+        E = self.num_experts
+        counts, offsets, tok, tw = [], [0], [], []
+        for e in range(E):
+            t, slot = torch.where(idx == e)
+            order = torch.argsort(t)
+            tok += t[order].tolist()
+            tw += w[t[order], slot[order]].tolist()
+            counts.append(len(t))
+            offsets.append(offsets[-1] + len(t))
+        return logits.to(torch.bfloat16), counts, offsets, torch.tensor(tok, dtype=torch.int32), torch.tensor(tw)
+
+    def run_expert(self, e, x_rows, row_idx, row_w, out):
+        rows = row_idx.long()
+        y = O.expert_ffn(x_rows[rows], *self._experts[e]) * row_w[:, None].to(torch.bfloat16).float()
+        out[rows] = (out[rows].float() + y.to(torch.bfloat16).float()).to(out.dtype)
+
+
+def _cpu_rank(rank, world, port, combine, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        hidden, ffn, n_exp, experts, x, gate_w = _problem()
+        local = {e: None for e in range(n_exp) if expert_owner(e, n_exp, world) == rank}
+        moe = OracleRankMoe(Cfg(hidden, ffn, n_exp), 0, None, local, combine=combine, experts=experts, gate_w=gate_w)
+        y, logits = moe(x.reshape(1, -1, hidden))
+        want, want_logits = O.moe_forward(x, gate_w, experts)
+        err = O.rel_err(y.reshape(-1, hidden), want)
+        assert err < 1e-2, err
+        assert O.rel_err(logits, want_logits) < 1e-2
+        if rank == 0:
+            result.put(float(err))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("combine", ["all_reduce", "all_to_all"])
+def test_two_cpu_ranks_match_the_single_process_block(combine):
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_cpu_rank, args=(r, 2, port, combine, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert result.get(timeout=5) < 1e-2
+
+
+def _gpu_rank(rank, world, port, combine, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from tests.test_gpu_parity import make_expert
+        import tests.test_gpu_parity as tp
+        tp.DEV = dev
+        hidden, ffn, n_exp, experts, x, gate_w = _problem(hidden=256, ffn=512, n_exp=4, tokens=37)
+        local = {e: make_expert(hidden, ffn, experts[e]) for e in range(n_exp) if expert_owner(e, n_exp, world) == rank}
+        gate = torch.nn.Linear(hidden, n_exp, bias=False, dtype=torch.bfloat16, device=dev)
+        gate.weight.data = gate_w.to(dev)
+        moe = ExpertParallelMoe(Cfg(hidden, ffn, n_exp), 0, gate, local, combine=combine)
+        for tokens in (37, 1):
+            y, _ = moe(x[:tokens].to(dev).reshape(1, tokens, hidden))
+            # the device's own routing decision goes into the oracle: a near-tie of two bf16-rounded
+            # logits may legitimately be broken differently, and would swamp the comparison
+            _, tw, ti, _, _, _ = moe.router.route(x[:tokens].to(dev))
+            want, _ = O.moe_forward(x[:tokens], gate_w, experts, routing=(tw.cpu(), ti.cpu()))
+            err = O.rel_err(y.cpu().reshape(-1, hidden), want)
+            assert err < 1e-2, (tokens, err)
+        if rank == 0:
+            result.put(float(err))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("combine", ["all_reduce", "all_to_all"])
+def test_two_gpu_ranks_match_the_oracle(combine):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gpu_rank, args=(r, 2, port, combine, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    assert result.get(timeout=5) < 1e-2
