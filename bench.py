@@ -200,6 +200,91 @@ def build_pool(device, n_experts, seed0):
     return pool
 
 
+def run_moe(args):
+    """One Mixtral MoE block (router 4096 -> 8, top-2, eight 2-bit experts) per step; with N ranks the
+    experts are sharded N ways (expert-parallel) and the combine is a collective.  Strong scaling: the
+    same tokens on every rank count.  Steps rotate over `layers` distinct layers so weights come from HBM.
+    The block reads back the per-expert row counts every call, so steps are issued from Python (no graph)."""
+    from mixtral_offloading_b200 import _cabi
+    from mixtral_offloading_b200.expert_parallel import ExpertParallelMoe, expert_owner
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _cabi.lib()
+    E, layers, T = 8, 4, args.tokens
+
+    class ModelCfg:
+        hidden_size, intermediate_size, num_local_experts, num_experts_per_tok, hidden_act = HIDDEN, FFN, E, 2, "silu"
+    torch.manual_seed(1234 + rank)
+    mine = [e for e in range(E) if expert_owner(e, E, world) == rank]
+    blocks = []
+    for l in range(layers):
+        pool = build_pool(dev, len(mine), seed0=100 * l + 10 * rank + 1)
+        gate = torch.nn.Linear(HIDDEN, E, bias=False, dtype=torch.bfloat16, device=dev)
+        g = torch.Generator().manual_seed(500 + l)
+        gate.weight.data = (torch.randn(E, HIDDEN, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+        blocks.append(ExpertParallelMoe(ModelCfg, l, gate, dict(zip(mine, pool)), combine=args.combine))
+    x_host = torch.randn(1, T, HIDDEN, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).pin_memory()
+    x = x_host.to(dev)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for i in range(args.warmup):
+        blocks[i % layers](x)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    stream = torch.cuda.current_stream(dev)
+    launches0 = lib.hqm_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for i in range(args.steps):
+        y, _ = blocks[i % layers](x)
+    ev1.record(stream)
+    barrier()
+    launches = lib.hqm_launch_count() - launches0
+    ms = ev0.elapsed_time(ev1)
+    y_host = torch.empty_like(x_host)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(args.steps):
+        y, _ = blocks[i % layers](x_host.to(dev, non_blocking=True))
+        y_host.copy_(y, non_blocking=True)
+        stream.synchronize()
+    e1.record(stream)
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler is not None else None
+    if world > 1:
+        tt = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = tt.tolist()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    ms_step, e2e_step = ms / args.steps, ms_e2e / args.steps
+    print(json.dumps({
+        "metric": "decode_tokens_per_s_moe_block", "value": T / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"one Mixtral MoE block (router 4096->8, top-2, 8 experts 2-bit g16), tokens={T}, "
+                   f"experts sharded over {world} rank(s), combine={args.combine if world > 1 else 'local'}",
+                   "l2": f"steps rotate over {layers} distinct layers"},
+        "e2e": {"value": T / (e2e_step * 1e-3), "unit": UNIT, "ms_per_step": e2e_step,
+                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }))
+
+
 def profile_linear(args):
     """A few launches of the dominant kernel on HBM-cold weights, nothing else (for ncu)."""
     dev = torch.device("cuda", 0)
@@ -357,6 +442,10 @@ def main():
     ap.add_argument("--tokens", type=int, default=1)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="expert", choices=["expert", "moe"],
+                    help="expert: one expert FFN per step (the default, BASELINE configs[1]); moe: one MoE block "
+                         "per step, expert-parallel over the ranks")
+    ap.add_argument("--combine", default="all_reduce", choices=["all_reduce", "all_to_all"])
     ap.add_argument("--profile-linear", type=int, default=0, metavar="N",
                     help="only launch N quantized linears (w1 shape, rotating over 6 layers > L2) and exit; "
                          "the small case meant to be run under ncu")
@@ -367,6 +456,10 @@ def main():
         run_reference(args)
     elif args.profile_linear:
         profile_linear(args)
+    elif args.workload == "moe":
+        args.steps = 200 if args.steps is None else args.steps
+        args.warmup = max(3, 8 if args.warmup is None else args.warmup)
+        run_moe(args)
     else:
         args.steps = 200 if args.steps is None else args.steps
         args.warmup = max(3, 8 if args.warmup is None else args.warmup)
