@@ -59,6 +59,9 @@ const char* hqm_last_error(void);
 int hqm_version(void);
 /* Number of CUDA kernels this library has launched in the process so far (for benchmarks). */
 int64_t hqm_launch_count(void);
+/* 1 if a bounded wait inside a tensor-core GEMM launch ever ran out (that launch skipped its work),
+ * 0 otherwise, -1 on a CUDA error.  Synchronises the device; meant for tests and start-up checks. */
+int hqm_device_error(void);
 
 /* ---- bit packing: src/packing.py --------------------------------------- */
 /* pack_4bit_u8_common, packing.py:10-17.  codes (N, K) uint8 -> packed (N/2, K). */

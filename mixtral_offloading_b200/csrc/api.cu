@@ -57,7 +57,9 @@ size_t linear_scratch_bytes(int64_t M, const hqm_weight* w) {
     int G, C;
     StreamPlan plan;
     if (M <= 0 || check_weight(w, &G, &C) != HQM_OK) return 0;
-    if (force_generic() || !gemv_stream_plan(w, 1, G, C, M, &plan)) return 0;
+    if (force_generic()) return 0;
+    if (M >= TC_MIN_ROWS && gemm_tc_supported(w, G, C, M)) return ((size_t)M * w->N * sizeof(float) + 255) / 256 * 256;
+    if (!gemv_stream_plan(w, 1, G, C, M, &plan)) return 0;
     return (gemv_stream_scratch_bytes(plan, M, w->N) + 255) / 256 * 256;
 }
 
@@ -70,6 +72,17 @@ int launch_linear(uint16_t* y, const uint16_t* x, const int32_t* x_idx, int64_t 
     StreamPlan plan;
     const bool x_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
     if (!x_ok || force_generic()) return launch_linear_generic(y, x, x_idx, M, w, G, C, bias, st);
+    if (M >= TC_MIN_ROWS && gemm_tc_supported(w, G, C, M)) {
+        const size_t need = (size_t)M * w->N * sizeof(float);
+        if (scratch == nullptr || scratch_bytes < need) {
+            set_error("linear: scratch of %zu bytes given, %zu needed", scratch_bytes, need);
+            return HQM_ERR_SCRATCH;
+        }
+        HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 15u) == 0, "linear: scratch must be 16-byte aligned");
+        rc = launch_gemm_tc((float*)scratch, x, x_idx, M, w, nullptr, G, C, st);
+        if (rc != HQM_OK) return rc;
+        return launch_rows_from_sums(y, (const float*)scratch, bias, M, w->N, st);
+    }
     if (gemv_stream_plan(w, 1, G, C, M, &plan)) {
         const size_t need = gemv_stream_scratch_bytes(plan, M, w->N);
         if (scratch == nullptr || scratch_bytes < need) {

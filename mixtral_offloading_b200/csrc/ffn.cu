@@ -41,6 +41,27 @@ static bool same_format(const hqm_weight* a, const hqm_weight* b) {
            a->meta_group == b->meta_group;
 }
 
+// The tensor-core path for a whole expert (many rows): [w1; w3] GEMM -> silu * mul -> w2 GEMM -> scatter.
+struct TcPlan {
+    int G1, C1, G2, C2;
+    size_t up_bytes, h_bytes, down_bytes;
+};
+static bool tc_plan(int64_t M, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3, const void* x,
+                    TcPlan* tp) {
+    if (force_generic() || M < TC_MIN_ROWS || !same_format(w1, w3)) return false;
+    if (check_weight(w1, &tp->G1, &tp->C1) != HQM_OK || check_weight(w3, &tp->G1, &tp->C1) != HQM_OK ||
+        check_weight(w2, &tp->G2, &tp->C2) != HQM_OK)
+        return false;
+    if (x && (reinterpret_cast<uintptr_t>(x) & 15u) != 0) return false;
+    if (!gemm_tc_supported(w1, tp->G1, tp->C1, M) || !gemm_tc_supported(w3, tp->G1, tp->C1, M) ||
+        !gemm_tc_supported(w2, tp->G2, tp->C2, M))
+        return false;
+    tp->up_bytes = align_up((size_t)M * 2 * w1->N * sizeof(float), 256);
+    tp->h_bytes = align_up((size_t)M * w1->N * 2, 256);
+    tp->down_bytes = align_up((size_t)M * w2->N * sizeof(float), 256);
+    return true;
+}
+
 // The streaming path for a whole expert: w1 and w3 in one launch, then w2.
 struct FusedPlan {
     StreamPlan up, down;
@@ -69,6 +90,8 @@ extern "C" {
 
 size_t hqm_expert_ffn_scratch_bytes(int64_t M, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3) {
     if (!w1 || !w2 || !w3 || M <= 0) return 0;
+    hqm::TcPlan tp;
+    if (hqm::tc_plan(M, w1, w2, w3, nullptr, &tp)) return tp.up_bytes + tp.h_bytes + tp.down_bytes;
     hqm::FusedPlan fp;
     if (hqm::fused_plan(M, w1, w2, w3, nullptr, &fp)) return fp.up_bytes + fp.h_bytes + fp.down_bytes;
     const size_t a = hqm::align_up((size_t)M * (size_t)w1->N * 2, 256);
@@ -100,6 +123,19 @@ int hqm_expert_ffn(uint16_t* out, const uint16_t* x, int64_t M, const int32_t* t
     cudaStream_t st = (cudaStream_t)stream;
     const int F = w1->N, H = w2->N;
     uint8_t* p = (uint8_t*)scratch;
+    TcPlan tp;
+    if (tc_plan(M, w1, w2, w3, x, &tp)) {
+        float* up = (float*)p;
+        uint16_t* h = (uint16_t*)(p + tp.up_bytes);
+        float* down = (float*)(p + tp.up_bytes + tp.h_bytes);
+        int rc = launch_gemm_tc(up, x, token_idx, M, w1, w3, tp.G1, tp.C1, st);
+        if (rc != HQM_OK) return rc;
+        rc = launch_silu_mul_from_sums(h, up, M, F, st);
+        if (rc != HQM_OK) return rc;
+        rc = launch_gemm_tc(down, h, nullptr, M, w2, nullptr, tp.G2, tp.C2, st);
+        if (rc != HQM_OK) return rc;
+        return launch_scatter_from_sums(out, down, token_idx, route_w, accumulate, M, H, st);
+    }
     FusedPlan fp;
     if (fused_plan(M, w1, w2, w3, x, &fp)) {
         // 4 launches: [w1;w3] partials -> h = silu(a) * b -> w2 partials -> scale / accumulate into out

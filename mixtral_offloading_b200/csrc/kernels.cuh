@@ -32,6 +32,16 @@ int launch_finalize_scatter(uint16_t* out, const float* partial, const int32_t* 
                             cudaStream_t st);
 bool force_generic();
 
+// gemm_tc.cu — tcgen05 / TMEM path for many rows of x.
+bool gemm_tc_supported(const hqm_weight* w, int G, int C, int64_t M);
+int launch_gemm_tc(float* sums, const uint16_t* x, const int32_t* x_idx, int64_t M, const hqm_weight* w0,
+                   const hqm_weight* w1, int G, int C, cudaStream_t st);
+int launch_rows_from_sums(uint16_t* y, const float* sums, const uint16_t* bias, int64_t M, int N, cudaStream_t st);
+int launch_silu_mul_from_sums(uint16_t* h, const float* sums, int64_t M, int F, cudaStream_t st);
+int launch_scatter_from_sums(uint16_t* out, const float* sums, const int32_t* token_idx, const float* route_w,
+                             int accumulate, int64_t M, int H, cudaStream_t st);
+constexpr int64_t TC_MIN_ROWS = 17;   // fewer rows go to the streaming kernels
+
 // Dispatcher used by hqm_linear and by the expert FFN: picks the streaming
 // kernel when the layer's shape allows it, the generic one otherwise.
 size_t linear_scratch_bytes(int64_t M, const hqm_weight* w);

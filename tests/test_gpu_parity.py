@@ -146,6 +146,16 @@ def test_linear_oracle_small(nbits, group, N, K, M):
     assert O.rel_err(y, O.linear(x, od)) < TOL
 
 
+def test_tensor_core_path_reports_no_timeout():
+    """The tcgen05 GEMM bounds every wait; a wait that ran out would set this flag (and skip work)."""
+    od = random_layer(512, 1024, 4, 64, seed=9)
+    layer = layer_from_oracle(od, DEV)
+    for M in (17, 64, 100, 300):
+        x = torch.randn(M, 1024, generator=torch.Generator().manual_seed(M)).to(torch.bfloat16)
+        assert O.rel_err(layer(x.to(DEV)).cpu(), O.linear(x, od)) < TOL
+    assert _cabi.lib().hqm_device_error() == 0
+
+
 def test_linear_shapes_and_dtypes():
     od = random_layer(128, 256, 4, 64, seed=5)
     layer = layer_from_oracle(od, DEV)
@@ -167,8 +177,8 @@ def test_linear_shapes_and_dtypes():
     assert O.rel_err(yb.reshape(6, 128), want) < TOL
 
 
-FULL = [(4, 64, 4096, 4096, (1, 16)), (4, 64, 1024, 4096, (1,)), (2, 16, 14336, 4096, (1, 8)),
-        (2, 16, 4096, 14336, (1, 8)), (3, 64, 14336, 4096, (1, 16))]
+FULL = [(4, 64, 4096, 4096, (1, 16, 64)), (4, 64, 1024, 4096, (1,)), (2, 16, 14336, 4096, (1, 8, 64, 512)),
+        (2, 16, 4096, 14336, (1, 8, 64, 512)), (3, 64, 14336, 4096, (1, 16))]
 
 
 @pytest.mark.parametrize("nbits,group,N,K,Ms", FULL)
@@ -237,7 +247,7 @@ def test_expert_ffn_golden(golden_dir):
     assert O.rel_err(y, O.expert_ffn(x, *experts[0])) < TOL
 
 
-@pytest.mark.parametrize("M", [1, 8, 64])
+@pytest.mark.parametrize("M", [1, 8, 64, 200])
 def test_expert_ffn_mid_size(M):
     hidden, ffn = 1024, 3584
     ods = (random_layer(ffn, hidden, 2, 16, 1), random_layer(hidden, ffn, 2, 16, 2), random_layer(ffn, hidden, 2, 16, 3))
