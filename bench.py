@@ -285,6 +285,76 @@ def run_moe(args):
     }))
 
 
+def run_offload(args):
+    """BASELINE configs[4](a) reduced to the MoE blocks: per layer 8 experts, 4 resident on the device and 4
+    in pinned host memory, 4 spare slabs, LRU swap through ExpertCache; decode at batch `tokens`.  `layers`
+    layers are built (each with its own eviction group, as build_model.py:219-235 registers them) and a
+    step runs all of them once.  The path is bound by the host link, so the line reports the achieved
+    host->device bandwidth and the hit rate next to the time per layer."""
+    from mixtral_offloading_b200 import ExpertCache, MixtralExpertWrapper, SparseMoeWrapper, _cabi
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    E, L, T = 8, args.layers, args.tokens
+    per_layer_off = 4
+
+    class ModelCfg:
+        hidden_size, intermediate_size, num_local_experts, num_experts_per_tok, hidden_act = HIDDEN, FFN, E, 2, "silu"
+    torch.manual_seed(7)
+    template = build_pool(dev, 1, seed0=999)[0]
+    state = {"n": 0}
+
+    def make_module():
+        # every slab of the cache needs its own module object bound to its own storage
+        state["n"] += 1
+        return build_pool(dev, 1, seed0=1000 + state["n"])[0]
+    cache = ExpertCache(make_module, main_size=L * (E - per_layer_off), offload_size=L * per_layer_off, buffer_size=4)
+    blocks = []
+    for l in range(L):
+        for e, wrapped in enumerate(build_pool(dev, E, seed0=5000 + 16 * l)):
+            cache.add_expert((l, e), wrapped, eviction_group=l, offload=(e < per_layer_off))
+        gate = torch.nn.Linear(HIDDEN, E, bias=False, dtype=torch.bfloat16, device=dev)
+        gate.weight.data = (torch.randn(E, HIDDEN) * 0.02).to(torch.bfloat16).to(dev)
+        blocks.append(SparseMoeWrapper(ModelCfg, l, gate, cache))
+    del template
+    xs = [torch.randn(1, T, HIDDEN).to(torch.bfloat16).to(dev) for _ in range(64)]
+    torch.cuda.synchronize(dev)
+
+    def step(i):
+        x = xs[i % len(xs)]
+        for blk in blocks:
+            y, _ = blk(x)
+        return y
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize(dev)
+    hm0 = [(cache.group_infos[l].hits, cache.group_infos[l].misses) for l in range(L)]
+    bytes0, swaps0 = cache.stats()
+    stream = torch.cuda.current_stream(dev)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for i in range(args.steps):
+        step(args.warmup + i)
+    ev1.record(stream)
+    torch.cuda.synchronize(dev)
+    ms = ev0.elapsed_time(ev1)
+    bytes1, swaps1 = cache.stats()
+    hits = sum(cache.group_infos[l].hits - hm0[l][0] for l in range(L))
+    misses = sum(cache.group_infos[l].misses - hm0[l][1] for l in range(L))
+    ms_layer = ms / (args.steps * L)
+    print(json.dumps({
+        "metric": "decode_tokens_per_s_offload_32_layers", "value": T / (ms_layer * 32 * 1e-3), "unit": UNIT,
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"MoE blocks of {L} layers, 8 experts each (4 resident + 4 in pinned host memory), "
+                   f"4 spare slabs, LRU swap, tokens={T}; value extrapolates the measured time per layer to 32 layers "
+                   "(MoE blocks only)"},
+        "ms_per_layer": ms_layer, "hit_rate": hits / max(1, hits + misses), "misses_per_layer_step": misses / (args.steps * L),
+        "h2d_gbs": (bytes1 - bytes0) / (ms * 1e-3) / 1e9, "h2d_bytes_per_step": (bytes1 - bytes0) / args.steps,
+        "swaps": swaps1 - swaps0, "slab_mb": cache.module_size / 1e6,
+    }))
+
+
 def profile_linear(args):
     """A few launches of the dominant kernel on HBM-cold weights, nothing else (for ncu)."""
     dev = torch.device("cuda", 0)
@@ -442,7 +512,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=1)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="expert", choices=["expert", "moe"],
+    ap.add_argument("--layers", type=int, default=8, help="layers built by the offload workload")
+    ap.add_argument("--workload", default="expert", choices=["expert", "moe", "offload"],
                     help="expert: one expert FFN per step (the default, BASELINE configs[1]); moe: one MoE block "
                          "per step, expert-parallel over the ranks")
     ap.add_argument("--combine", default="all_reduce", choices=["all_reduce", "all_to_all"])
@@ -456,6 +527,10 @@ def main():
         run_reference(args)
     elif args.profile_linear:
         profile_linear(args)
+    elif args.workload == "offload":
+        args.steps = 50 if args.steps is None else args.steps
+        args.warmup = max(3, 5 if args.warmup is None else args.warmup)
+        run_offload(args)
     elif args.workload == "moe":
         args.steps = 200 if args.steps is None else args.steps
         args.warmup = max(3, 8 if args.warmup is None else args.warmup)
