@@ -201,7 +201,7 @@ struct Layers {
 };
 
 template <int NBITS, int NB, int TOKS>
-__global__ void __launch_bounds__(256, (NB == 1 && TOKS <= 2) ? 2 : 1)
+__global__ void __launch_bounds__(256, 1)
 gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, const int32_t* __restrict__ x_idx,
                    int M, int m_base, int M_total, Layers ly, int G, int C, int P, Split sp, FieldConsts fc) {
     using F = Fields<NBITS>;
