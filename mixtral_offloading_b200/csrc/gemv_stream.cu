@@ -167,9 +167,16 @@ struct Shape {
     static constexpr int WARP_HALFS = SUB * (MTOK + 1) * PER * ROW;
     static constexpr int NW = 8;
     static constexpr int RED_PER_WARP = NB * NT * 4 * 32;
+    // Asynchronous-copy ring: per warp DEPTH slots, each one pass of 16-byte cells per lane:
+    // per sub-pass 2*NB weight-row cells, 1 cell scale_q | zero_q, 4 cells of fp16 meta.  (x comes from the
+    // per-segment fp16 staging buffer, or straight from global memory when there are too many rows for that.)
+    static constexpr int DEPTH = 2;
+    static constexpr int CELLS_SUB = 2 * NB + 5;
+    static constexpr int CELLS = SUB * CELLS_SUB;
+    static constexpr int SLOT_BYTES = CELLS * 32 * 16;
     static size_t smem_bytes(int K) {
         return (size_t)NW * WARP_HALFS * sizeof(__half) + (size_t)NW * RED_PER_WARP * sizeof(float) +
-               (STAGE_X ? (size_t)TOKS * K * sizeof(__half) : 0);
+               (size_t)NW * DEPTH * SLOT_BYTES + (STAGE_X ? (size_t)TOKS * K * sizeof(__half) : 0);
     }
 };
 
@@ -190,6 +197,22 @@ template <int N> __device__ __forceinline__ void st_words(void* p, const uint32_
     } else {
         *reinterpret_cast<uint4*>(p) = make_uint4(src[0], src[1], src[2], src[3]);
     }
+}
+
+// Per-thread asynchronous global -> shared copies (the data goes to shared memory without
+// occupying registers while in flight, so a warp can have several passes outstanding).
+template <int BYTES>
+__device__ __forceinline__ void cp_async(void* smem_dst, const void* gmem_src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    if constexpr (BYTES == 16) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+    } else {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(d), "l"(gmem_src), "n"(BYTES) : "memory");
+    }
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // Up to two layers of identical shape share one launch (the expert's w1 and w3): their
@@ -217,7 +240,10 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
     __half* xs_w = reinterpret_cast<__half*>(smem_raw) + wi * S::WARP_HALFS;      // [SUB][MTOK][PER][ROW]
     __half* zz_w = xs_w + SUB * MTOK * PER * ROW;                                  // [SUB][PER][ROW]
     float* red = reinterpret_cast<float*>(smem_raw + (size_t)NW * S::WARP_HALFS * sizeof(__half));
-    __half* xh = reinterpret_cast<__half*>(red + NW * RED_PER_WARP);               // [TOKS][segment columns]
+    unsigned char* ring = reinterpret_cast<unsigned char*>(red + NW * RED_PER_WARP) +
+                          (size_t)wi * S::DEPTH * S::SLOT_BYTES + lane * 16;       // this lane's cell column
+    __half* xh = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(red + NW * RED_PER_WARP) +
+                                           (size_t)NW * S::DEPTH * S::SLOT_BYTES);  // [TOKS][segment columns]
 
     // token rows that exist only to fill a column tile stay zero for the whole kernel
     for (int i = lane; i < SUB * MTOK * PER * ROW / 2; i += 32) reinterpret_cast<uint32_t*>(xs_w)[i] = 0u;
@@ -249,17 +275,6 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
         L += (uint32_t)(pb - pa);
         const int layer = rho_g / P, rho = rho_g - layer * P;
         const hqm_weight& w = ly.w[layer];
-
-        if constexpr (S::STAGE_X) {
-            // the segment's columns of x, converted to fp16 once for all warps
-            const int c0 = pa * PW, nc = (pb - pa) * PW;
-#pragma unroll
-            for (int m = 0; m < TOKS; ++m)
-                for (int i = threadIdx.x * 2; i < nc; i += 2 * blockDim.x)
-                    *reinterpret_cast<__half2*>(xh + m * K + i) =
-                        bf16pair_to_h2(*reinterpret_cast<const uint32_t*>(xr[m] + c0 + i));
-            __syncthreads();
-        }
 
         float acc[NB][NT][PER][4];
         float accc[NT][4];
@@ -294,40 +309,59 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
             uint4 q0[SUB][NB], q1[SUB][NB];
         };
 
-        auto load_rows = [&](Rows& r, int p) {
+        // cell (c) of slot (sl): ring + sl * SLOT_BYTES + c * 512 (each lane owns 16 bytes of every cell)
+        auto issue = [&](int sl, int p) {
+            unsigned char* cell = ring + sl * S::SLOT_BYTES;
             const uint8_t* base = wrow + p * PW;
-#pragma unroll
-            for (int u = 0; u < SUB; ++u)
-#pragma unroll
-                for (int b = 0; b < NB; ++b) {
-                    r.q0[u][b] = ld_stream_16(base + qoff[b] + 64 * u);
-                    r.q1[u][b] = ld_stream_16(base + qoff[b] + qoff8 + 64 * u);
-                }
-        };
-        auto load_meta = [&](Meta& r, int p) {
             const int k0 = p * PW;
             const uint32_t idx = dbase + k0;
 #pragma unroll
             for (int u = 0; u < SUB; ++u) {
+                unsigned char* cu = cell + u * S::CELLS_SUB * 512;
+#pragma unroll
+                for (int b = 0; b < NB; ++b) {
+                    cp_async<16>(cu + (2 * b) * 512, base + qoff[b] + 64 * u);
+                    cp_async<16>(cu + (2 * b + 1) * 512, base + qoff[b] + qoff8 + 64 * u);
+                }
                 uint32_t col = dcol0 + kcol;                      // < 2C
                 col = col >= (uint32_t)C ? col - (uint32_t)C : col;
                 if (u == 1) {
                     col += ustep;
                     col = col >= (uint32_t)C ? col - (uint32_t)C : col;
                 }
-                ld_words(r.sq[u], w.scale_q + idx + 64 * u);
-                ld_words(r.zq[u], w.zero_q + idx + 64 * u);
-                ld_words(r.mss[u], w.ms_scale + col);
-                ld_words(r.mzs[u], w.mz_scale + col);
-                ld_words(r.msz[u], w.ms_zero + col);
-                ld_words(r.mzz[u], w.mz_zero + col);
-                if constexpr (!S::STAGE_X) {
-#pragma unroll
-                    for (int m = 0; m < TOKS; ++m) ld_words(r.xv[m][u], xr[m] + k0 + 64 * u + kd);
-                }
+                unsigned char* cm = cu + 2 * NB * 512;
+                cp_async<DK>(cm, w.scale_q + idx + 64 * u);
+                cp_async<DK>(cm + 8, w.zero_q + idx + 64 * u);
+                cp_async<2 * DK>(cm + 512, w.ms_scale + col);
+                cp_async<2 * DK>(cm + 2 * 512, w.mz_scale + col);
+                cp_async<2 * DK>(cm + 3 * 512, w.ms_zero + col);
+                cp_async<2 * DK>(cm + 4 * 512, w.mz_zero + col);
             }
             kcol += kstep;
             kcol = kcol >= (uint32_t)C ? kcol - (uint32_t)C : kcol;
+        };
+        auto fetch = [&](int sl, int p, Meta& r, Rows& q) {
+            const unsigned char* cell = ring + sl * S::SLOT_BYTES;
+#pragma unroll
+            for (int u = 0; u < SUB; ++u) {
+                const unsigned char* cu = cell + u * S::CELLS_SUB * 512;
+#pragma unroll
+                for (int b = 0; b < NB; ++b) {
+                    q.q0[u][b] = *reinterpret_cast<const uint4*>(cu + (2 * b) * 512);
+                    q.q1[u][b] = *reinterpret_cast<const uint4*>(cu + (2 * b + 1) * 512);
+                }
+                const unsigned char* cm = cu + 2 * NB * 512;
+                ld_words(r.sq[u], cm);
+                ld_words(r.zq[u], cm + 8);
+                ld_words(r.mss[u], cm + 512);
+                ld_words(r.mzs[u], cm + 2 * 512);
+                ld_words(r.msz[u], cm + 3 * 512);
+                ld_words(r.mzz[u], cm + 4 * 512);
+                if constexpr (!S::STAGE_X) {
+#pragma unroll
+                    for (int m = 0; m < TOKS; ++m) ld_words(r.xv[m][u], xr[m] + p * PW + 64 * u + kd);
+                }
+            }
         };
 
         // 1. decode scale / zero of (slot sd, DK columns per sub-pass), fold into x, publish to the warp
@@ -419,34 +453,45 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
             __syncwarp();   // the next pass overwrites this warp's shared memory
         };
 
-        // ---- the warp's passes of this segment.  The decode inputs are dead once decoded, so the
-        // next pass's are requested into the same registers right away; the weight rows alternate
-        // between two register sets.  Both are in flight while the tensor-core phase of a pass runs.
-        Meta d;
-        Rows ra, rb;
-        int p = pa + wi;
-        if (p < pb) {
-            load_rows(ra, p);
-            load_meta(d, p);
+        // ---- the warp's passes of this segment: DEPTH passes are requested with asynchronous copies
+        // before anything is computed, and a slot is refilled as soon as its pass has been moved to
+        // registers, so the copies of the next passes run under the arithmetic of the current one.
+        // (One commit group per pass, empty when the warp has no pass left, keeps the count uniform.)
+        {
+            int pi = pa + wi;
+#pragma unroll
+            for (int sl = 0; sl < S::DEPTH; ++sl) {
+                if (pi < pb) issue(sl, pi);
+                cp_async_commit();
+                pi += NW;
+            }
         }
-        while (p < pb) {
-            decode_pass(d, p);
-            int pn = p + NW;
-            if (pn < pb) {
-                load_meta(d, pn);
-                load_rows(rb, pn);
+        if constexpr (S::STAGE_X) {
+            // the segment's columns of x, converted to fp16 once for all warps
+            const int c0 = pa * PW, nc = (pb - pa) * PW;
+#pragma unroll
+            for (int m = 0; m < TOKS; ++m)
+                for (int i = threadIdx.x * 2; i < nc; i += 2 * blockDim.x)
+                    *reinterpret_cast<__half2*>(xh + m * K + i) =
+                        bf16pair_to_h2(*reinterpret_cast<const uint32_t*>(xr[m] + c0 + i));
+            __syncthreads();
+        }
+
+        {
+            Meta d;
+            Rows r;
+            int sl = 0;
+            for (int p = pa + wi; p < pb; p += NW) {
+                cp_async_wait<S::DEPTH - 1>();
+                fetch(sl, p, d, r);
+                const int pn = p + S::DEPTH * NW;
+                if (pn < pb) issue(sl, pn);
+                cp_async_commit();
+                decode_pass(d, p);
+                mma_pass(r);
+                sl = (sl + 1 == S::DEPTH) ? 0 : sl + 1;
             }
-            mma_pass(ra);
-            p = pn;
-            if (p >= pb) break;
-            decode_pass(d, p);
-            pn = p + NW;
-            if (pn < pb) {
-                load_meta(d, pn);
-                load_rows(ra, pn);
-            }
-            mma_pass(rb);
-            p = pn;
+            cp_async_wait<0>();
         }
 
         // ---- segment epilogue: pick the valid columns, subtract the correction, add up the warps.
