@@ -14,9 +14,10 @@
 // Mapping.  The unit of work is a "pass": one storage-row residue `rho` (PER adjacent
 // residues r, the rows packed into one byte) x 64 input columns.  Passes are numbered
 // rho-major and cut into equal contiguous ranges, one per CTA of a single-wave
-// persistent grid (148 SMs x resident CTAs), so every SM gets the same number of bytes
-// whatever the layer shape; inside a range the warps take passes round-robin and load
-// the next pass into registers before computing the current one.  In a pass a warp
+// persistent grid, one range per WARP (148 SMs x resident warps), so every SM gets the
+// same number of bytes whatever the layer shape and warps never wait for each other (no
+// CTA barrier anywhere); a warp keeps the next passes in flight with asynchronous copies
+// while it computes the current one.  In a pass a warp
 //   1. decodes s, z for its PER x 64 (r, k) pairs, 2*PER per lane, and writes
 //      xs (per token) and z to warp-private shared memory as fp16;
 //   2. streams the 16*NB storage rows rho + i*P (the group's members) with 128-bit
@@ -30,7 +31,7 @@
 //      cross-lane reduction, so no shuffles are needed on the way;
 //   4. one extra MMA per word with A = [z ; OFFSET] yields sum xs*z and OFFSET*sum xs,
 //      which are subtracted at the end.
-// A residue whose passes span several CTAs gets one fp32 partial row-set per CTA in a
+// A residue whose passes span several warps gets one fp32 partial row-set per warp in a
 // scratch buffer [slots][M][N]; a small finalize kernel adds them in fixed order
 // (deterministic), applies bias and rounds to bf16.
 //
@@ -134,13 +135,13 @@ template <> struct Fields<4> {
 
 // --------------------------------------------------------------------------- kernel
 // Work split shared by the kernel and the finalize step: passes are numbered
-// L = rho * PT + p (PT passes per residue); CTA c owns [c*Ltot/grid, (c+1)*Ltot/grid).
+// L = rho * PT + p (PT passes per residue); warp c of the grid owns [c*Ltot/grid, (c+1)*Ltot/grid).
 // (32-bit arithmetic throughout: the planner rejects layers with total() * grid >= 2^31.)
 struct Split {
     int P, PT, grid;
     __host__ __device__ uint32_t total() const { return (uint32_t)P * (uint32_t)PT; }
     __host__ __device__ uint32_t begin(int c) const { return (uint32_t)c * total() / (uint32_t)grid; }
-    // CTA whose range contains pass L
+    // warp whose range contains pass L
     __host__ __device__ int owner(uint32_t L) const {
         int c = (int)(L * (uint32_t)grid / total());
         while (c + 1 < grid && begin(c + 1) <= L) ++c;
@@ -166,18 +167,18 @@ struct Shape {
     static constexpr int ROW = 72;                              // 64 columns + padding against bank conflicts
     static constexpr int WARP_HALFS = SUB * (MTOK + 1) * PER * ROW;
     static constexpr int NW = 8;
-    static constexpr int RED_PER_WARP = NB * NT * 4 * 32;
+    static constexpr int XPASS = 8;                             // longest range (passes) a warp may be given
     // Asynchronous-copy ring: per warp DEPTH slots, each one pass of 16-byte cells per lane:
-    // per sub-pass 2*NB weight-row cells, 1 cell scale_q | zero_q, 4 cells of fp16 meta.  (x comes from the
-    // per-segment fp16 staging buffer, or straight from global memory when there are too many rows for that.)
+    // per sub-pass 2*NB weight-row cells and 1 cell scale_q | zero_q: the bytes that come from HBM.  The fp16
+    // meta of scale/zero (L2 resident) is loaded to registers one pass ahead; x comes from the per-segment
+    // fp16 staging buffer, or straight from global memory when there are too many rows for that.
     static constexpr int DEPTH = 2;
-    static constexpr int CELLS_SUB = 2 * NB + 5;
+    static constexpr int CELLS_SUB = 2 * NB + 1;
     static constexpr int CELLS = SUB * CELLS_SUB;
     static constexpr int SLOT_BYTES = CELLS * 32 * 16;
-    static size_t smem_bytes(int K) {
-        return (size_t)NW * WARP_HALFS * sizeof(__half) + (size_t)NW * RED_PER_WARP * sizeof(float) +
-               (size_t)NW * DEPTH * SLOT_BYTES + (STAGE_X ? (size_t)TOKS * K * sizeof(__half) : 0);
-    }
+    static constexpr int XH_HALFS = STAGE_X ? TOKS * XPASS * PW : 0;   // per warp: its range of x as fp16
+    static constexpr size_t WARP_BYTES = (size_t)WARP_HALFS * 2 + (size_t)DEPTH * SLOT_BYTES + (size_t)XH_HALFS * 2;
+    static constexpr size_t smem_bytes() { return (size_t)NW * WARP_BYTES; }
 };
 
 template <int N> __device__ __forceinline__ void ld_words(uint32_t (&dst)[N], const void* p) {
@@ -224,26 +225,25 @@ struct Layers {
 };
 
 template <int NBITS, int NB, int TOKS>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(256, (NB == 1 && TOKS <= 2) ? 2 : 1)
 gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, const int32_t* __restrict__ x_idx,
                    int M, int m_base, int M_total, Layers ly, int G, int C, int P, Split sp, FieldConsts fc) {
     using F = Fields<NBITS>;
     using S = Shape<NBITS, NB, TOKS>;
     constexpr int PER = S::PER, TPT = S::TPT, NT = S::NT, MTOK = S::MTOK, LPS = S::LPS, DK = S::DK, SUB = S::SUB,
-                  PW = S::PW, ROW = S::ROW, NW = S::NW, RED_PER_WARP = S::RED_PER_WARP;
+                  PW = S::PW, ROW = S::ROW, NW = S::NW;
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int K = ly.w[0].K, N = ly.w[0].N, PT = sp.PT;
     const int N_total = N * ly.count;
-    __half* xs_w = reinterpret_cast<__half*>(smem_raw) + wi * S::WARP_HALFS;      // [SUB][MTOK][PER][ROW]
+    unsigned char* warp_mem = smem_raw + (size_t)wi * S::WARP_BYTES;               // everything is warp-private
+    __half* xs_w = reinterpret_cast<__half*>(warp_mem);                             // [SUB][MTOK][PER][ROW]
     __half* zz_w = xs_w + SUB * MTOK * PER * ROW;                                  // [SUB][PER][ROW]
-    float* red = reinterpret_cast<float*>(smem_raw + (size_t)NW * S::WARP_HALFS * sizeof(__half));
-    unsigned char* ring = reinterpret_cast<unsigned char*>(red + NW * RED_PER_WARP) +
-                          (size_t)wi * S::DEPTH * S::SLOT_BYTES + lane * 16;       // this lane's cell column
-    __half* xh = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(red + NW * RED_PER_WARP) +
-                                           (size_t)NW * S::DEPTH * S::SLOT_BYTES);  // [TOKS][segment columns]
+    unsigned char* ring = warp_mem + (size_t)S::WARP_HALFS * 2 + lane * 16;        // this lane's cell column
+    __half* xh = reinterpret_cast<__half*>(warp_mem + (size_t)S::WARP_HALFS * 2 + (size_t)S::DEPTH * S::SLOT_BYTES);
+    constexpr int XCOLS = S::XPASS * PW;                                           // [TOKS][XCOLS]
 
     // token rows that exist only to fill a column tile stay zero for the whole kernel
     for (int i = lane; i < SUB * MTOK * PER * ROW / 2; i += 32) reinterpret_cast<uint32_t*>(xs_w)[i] = 0u;
@@ -267,7 +267,8 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
     for (int b = 0; b < NB; ++b) qoff[b] = (uint32_t)(16 * b + g) * (uint32_t)P * (uint32_t)K + 16u * t;
     const uint32_t qoff8 = 8u * (uint32_t)P * (uint32_t)K;
 
-    const uint32_t L_begin = sp.begin(blockIdx.x), L_end = sp.begin(blockIdx.x + 1);
+    const int gw = blockIdx.x * NW + wi;                                           // this warp in the grid
+    const uint32_t L_begin = sp.begin(gw), L_end = sp.begin(gw + 1);
     for (uint32_t L = L_begin; L < L_end;) {
         // ---- one segment: passes [pa, pb) of residue rho of layer `layer`
         const int rho_g = (int)(L / (uint32_t)PT), pa = (int)(L - (uint32_t)rho_g * (uint32_t)PT);
@@ -296,8 +297,8 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
         // meta column of a flat scale/zero index: the residue-row part is reduced once per segment,
         // each pass then adds its k0 (tracked modulo C) and wraps with a compare
         const uint32_t dcol0 = dbase % (uint32_t)C;
-        uint32_t kcol = (uint32_t)((pa + wi) * PW) % (uint32_t)C;     // (k0 % C) of the pass loaded next
-        const uint32_t kstep = (uint32_t)(PW * NW) % (uint32_t)C;
+        uint32_t kcol = (uint32_t)(pa * PW) % (uint32_t)C;            // (k0 % C) of the pass loaded next
+        const uint32_t kstep = (uint32_t)PW % (uint32_t)C;
         const uint32_t ustep = 64u % (uint32_t)C;
 
         struct Meta {
@@ -323,19 +324,24 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
                     cp_async<16>(cu + (2 * b) * 512, base + qoff[b] + 64 * u);
                     cp_async<16>(cu + (2 * b + 1) * 512, base + qoff[b] + qoff8 + 64 * u);
                 }
+                unsigned char* cm = cu + 2 * NB * 512;
+                cp_async<DK>(cm, w.scale_q + idx + 64 * u);
+                cp_async<DK>(cm + 8, w.zero_q + idx + 64 * u);
+            }
+        };
+        auto load_meta = [&](Meta& r) {                 // for the pass whose columns kcol points at
+#pragma unroll
+            for (int u = 0; u < SUB; ++u) {
                 uint32_t col = dcol0 + kcol;                      // < 2C
                 col = col >= (uint32_t)C ? col - (uint32_t)C : col;
                 if (u == 1) {
                     col += ustep;
                     col = col >= (uint32_t)C ? col - (uint32_t)C : col;
                 }
-                unsigned char* cm = cu + 2 * NB * 512;
-                cp_async<DK>(cm, w.scale_q + idx + 64 * u);
-                cp_async<DK>(cm + 8, w.zero_q + idx + 64 * u);
-                cp_async<2 * DK>(cm + 512, w.ms_scale + col);
-                cp_async<2 * DK>(cm + 2 * 512, w.mz_scale + col);
-                cp_async<2 * DK>(cm + 3 * 512, w.ms_zero + col);
-                cp_async<2 * DK>(cm + 4 * 512, w.mz_zero + col);
+                ld_words(r.mss[u], w.ms_scale + col);
+                ld_words(r.mzs[u], w.mz_scale + col);
+                ld_words(r.msz[u], w.ms_zero + col);
+                ld_words(r.mzz[u], w.mz_zero + col);
             }
             kcol += kstep;
             kcol = kcol >= (uint32_t)C ? kcol - (uint32_t)C : kcol;
@@ -353,10 +359,6 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
                 const unsigned char* cm = cu + 2 * NB * 512;
                 ld_words(r.sq[u], cm);
                 ld_words(r.zq[u], cm + 8);
-                ld_words(r.mss[u], cm + 512);
-                ld_words(r.mzs[u], cm + 2 * 512);
-                ld_words(r.msz[u], cm + 3 * 512);
-                ld_words(r.mzz[u], cm + 4 * 512);
                 if constexpr (!S::STAGE_X) {
 #pragma unroll
                     for (int m = 0; m < TOKS; ++m) ld_words(r.xv[m][u], xr[m] + p * PW + 64 * u + kd);
@@ -383,7 +385,7 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
                     uint32_t xs2[DK / 2];
                     if constexpr (S::STAGE_X) {
                         uint32_t xf[DK / 2];
-                        ld_words(xf, xh + m * K + (p - pa) * PW + 64 * u + kd);
+                        ld_words(xf, xh + m * XCOLS + (p - pa) * PW + 64 * u + kd);
 #pragma unroll
                         for (int j = 0; j < DK / 2; ++j) xs2[j] = h2_bits(__hmul2(bits_h2(xf[j]), bits_h2(s2[j])));
                     } else {
@@ -457,88 +459,75 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
         // before anything is computed, and a slot is refilled as soon as its pass has been moved to
         // registers, so the copies of the next passes run under the arithmetic of the current one.
         // (One commit group per pass, empty when the warp has no pass left, keeps the count uniform.)
-        {
-            int pi = pa + wi;
 #pragma unroll
-            for (int sl = 0; sl < S::DEPTH; ++sl) {
-                if (pi < pb) issue(sl, pi);
-                cp_async_commit();
-                pi += NW;
-            }
+        for (int sl = 0; sl < S::DEPTH; ++sl) {
+            if (pa + sl < pb) issue(sl, pa + sl);
+            cp_async_commit();
         }
         if constexpr (S::STAGE_X) {
-            // the segment's columns of x, converted to fp16 once for all warps
+            // the segment's columns of x, converted to fp16 once
             const int c0 = pa * PW, nc = (pb - pa) * PW;
 #pragma unroll
             for (int m = 0; m < TOKS; ++m)
-                for (int i = threadIdx.x * 2; i < nc; i += 2 * blockDim.x)
-                    *reinterpret_cast<__half2*>(xh + m * K + i) =
+                for (int i = lane * 2; i < nc; i += 64)
+                    *reinterpret_cast<__half2*>(xh + m * XCOLS + i) =
                         bf16pair_to_h2(*reinterpret_cast<const uint32_t*>(xr[m] + c0 + i));
-            __syncthreads();
+            __syncwarp();
         }
 
         {
             Meta d;
             Rows r;
             int sl = 0;
-            for (int p = pa + wi; p < pb; p += NW) {
+            load_meta(d);
+            for (int p = pa; p < pb; ++p) {
                 cp_async_wait<S::DEPTH - 1>();
                 fetch(sl, p, d, r);
-                const int pn = p + S::DEPTH * NW;
+                const int pn = p + S::DEPTH;
                 if (pn < pb) issue(sl, pn);
                 cp_async_commit();
                 decode_pass(d, p);
+                if (p + 1 < pb) load_meta(d);          // the meta registers are free again: next pass's
                 mma_pass(r);
                 sl = (sl + 1 == S::DEPTH) ? 0 : sl + 1;
             }
             cp_async_wait<0>();
         }
 
-        // ---- segment epilogue: pick the valid columns, subtract the correction, add up the warps.
-        // Lane (g, t) holds columns 2t, 2t+1 of every tile: slots sa and sa + 1 of token (2t) / PER.
-        // Column n of the correction tile is valid in the lane whose row index equals the column's slot.
+        // ---- segment epilogue: pick the valid columns, subtract the correction, store this warp's
+        // partial row-set.  Lane (g, t) holds columns 2t, 2t+1 of every tile: slots sa and sa + 1 of token
+        // (2t) / PER.  Column n of the correction tile is valid in the lane whose row index equals the
+        // column's slot.
+        const int slot_idx = gw - sp.owner((uint32_t)rho_g * (uint32_t)PT);
 #pragma unroll
         for (int tau = 0; tau < NT; ++tau) {
             const float mine = (sa == g) ? accc[tau][0] + accc[tau][2] : accc[tau][1] + accc[tau][3];
             const float ca = __shfl_sync(0xffffffffu, mine, sa * 4 + t);
             const float cb = __shfl_sync(0xffffffffu, mine, (sa + 1) * 4 + t);
-#pragma unroll
-            for (int b = 0; b < NB; ++b) {
-                float va0 = 0.f, va1 = 0.f, vb0 = 0.f, vb1 = 0.f;
-#pragma unroll
-                for (int s = 0; s < PER; s += 2) {
-                    if (s == sa) {
-                        va0 = acc[b][tau][s][0];      // row g,     column 2t
-                        va1 = acc[b][tau][s][2];      // row g + 8, column 2t
-                        vb0 = acc[b][tau][s + 1][1];  // row g,     column 2t + 1
-                        vb1 = acc[b][tau][s + 1][3];  // row g + 8, column 2t + 1
-                    }
-                }
-                float* dst = red + wi * RED_PER_WARP + (b * NT + tau) * 128 + lane;
-                dst[0] = va0 - ca;
-                dst[32] = vb0 - cb;
-                dst[64] = va1 - ca;
-                dst[96] = vb1 - cb;
-            }
-        }
-        __syncthreads();
-        const int slot_idx = blockIdx.x - sp.owner((uint32_t)rho_g * (uint32_t)PT);
-        for (int e = threadIdx.x; e < RED_PER_WARP; e += blockDim.x) {
-            float sum = 0.f;
-#pragma unroll
-            for (int wv = 0; wv < NW; ++wv) sum += red[wv * RED_PER_WARP + e];
-            const int le = e & 31, v = (e >> 5) & 3, bt = e >> 7;
-            const int tau = bt % NT, b = bt / NT;
-            const int ge = le >> 2, te = le & 3;
-            const int slot = (2 * te) % PER + (v & 1);
-            const int m = tau * TPT + (2 * te) / PER;
-            const int member = 16 * b + ge + 8 * (v >> 1);
+            const int m = tau * TPT + (2 * t) / PER;
             if (m < M) {
-                const int64_t n = (int64_t)layer * N + (int64_t)member * G + PER * rho + slot;
-                partial[((int64_t)slot_idx * M_total + m_base + m) * N_total + n] = sum;
+                float* dst = partial + ((int64_t)slot_idx * M_total + m_base + m) * N_total + (int64_t)layer * N +
+                             PER * rho + sa;
+#pragma unroll
+                for (int b = 0; b < NB; ++b) {
+                    float va0 = 0.f, va1 = 0.f, vb0 = 0.f, vb1 = 0.f;
+#pragma unroll
+                    for (int s = 0; s < PER; s += 2) {
+                        if (s == sa) {
+                            va0 = acc[b][tau][s][0];      // row g,     column 2t
+                            va1 = acc[b][tau][s][2];      // row g + 8, column 2t
+                            vb0 = acc[b][tau][s + 1][1];  // row g,     column 2t + 1
+                            vb1 = acc[b][tau][s + 1][3];  // row g + 8, column 2t + 1
+                        }
+                    }
+                    float* d0 = dst + (int64_t)(16 * b + g) * G;        // member 16b + g
+                    float* d1 = d0 + (int64_t)8 * G;                    // member 16b + g + 8
+                    *reinterpret_cast<float2*>(d0) = make_float2(va0 - ca, vb0 - cb);
+                    *reinterpret_cast<float2*>(d1) = make_float2(va1 - ca, vb1 - cb);
+                }
             }
         }
-        __syncthreads();   // `red` and the staged x are reused by the next segment
+        __syncwarp();   // the staged x is reused by the next segment
     }
 }
 
@@ -605,36 +594,28 @@ __global__ void finalize_scatter_kernel(uint16_t* __restrict__ out, const float*
 // --------------------------------------------------------------------------- host side
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Resident CTAs per SM of an instantiation for a given K, times the SM count.
+// Resident CTAs per SM of an instantiation, times the SM count (queried once).
 template <int NBITS, int NB, int TOKS>
-static int resident_grid(int K) {
+static int resident_grid() {
     using S = Shape<NBITS, NB, TOKS>;
-    static std::map<int, int> cache;                 // K -> grid (host-side, one entry per layer width seen)
-    static size_t max_smem = 0;
-    auto it = cache.find(K);
-    if (it != cache.end()) return it->second;
-    int cached = 0;
-    {
-        auto kern = gemv_stream_kernel<NBITS, NB, TOKS>;
-        const size_t smem = S::smem_bytes(K);
-        if (smem > 227 * 1024) return 0;
-        if (smem > max_smem) {
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-                cudaGetLastError();
-                return 0;
-            }
-            max_smem = smem;
-        }
-        int per_sm = 0, dev = 0, sms = 148;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 256, smem) != cudaSuccess || per_sm < 1) {
-            cudaGetLastError();
-            return 0;
-        }
-        cached = per_sm * sms;
-        cache[K] = cached;
+    static int cached = -1;
+    if (cached >= 0) return cached;
+    cached = 0;
+    auto kern = gemv_stream_kernel<NBITS, NB, TOKS>;
+    const size_t smem = S::smem_bytes();
+    if (smem > 227 * 1024) return 0;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
     }
+    int per_sm = 0, dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 256, smem) != cudaSuccess || per_sm < 1) {
+        cudaGetLastError();
+        return 0;
+    }
+    cached = per_sm * sms;
     return cached;
 }
 
@@ -675,20 +656,35 @@ bool gemv_stream_plan(const hqm_weight* w, int layers, int G, int C, int64_t M, 
         !aligned16(w->mz_scale) || !aligned16(w->ms_zero) || !aligned16(w->mz_zero))
         return false;
     const int toks = toks_for(w->nbits, nb, (int)M);
-    const int K = w->K;
-    int grid = dispatch(w->nbits, nb, toks, [K](auto b, auto k, auto t) {
-        return resident_grid<decltype(b)::value, decltype(k)::value, decltype(t)::value>(K);
+    int grid = dispatch(w->nbits, nb, toks, [](auto b, auto k, auto t) {
+        return resident_grid<decltype(b)::value, decltype(k)::value, decltype(t)::value>();
     });
     if (grid <= 0) return false;
     plan->P = G / per;
     plan->layers = layers;
     plan->PT = w->K / pw;
     const int64_t total = (int64_t)plan->P * layers * plan->PT;
-    if (grid > total) grid = (int)total;
-    if (total * grid >= ((int64_t)1 << 31)) return false;
+    // Whole CTAs per SM, so that every SM carries the same load; fewer of them (and, for small layers,
+    // fewer SMs) rather than ranges shorter than ~3 passes, each of which costs a partial row-set.
+    {
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        int per_sm = grid / sms;
+        const int64_t want = total / ((int64_t)sms * 8 * 3);
+        if (per_sm > want) per_sm = (int)(want < 1 ? 1 : want);
+        grid = per_sm * sms;
+        if ((int64_t)grid * 8 * 3 > total) grid = (int)(total / (8 * 3));
+        if (grid < 1) grid = 1;
+        if ((int64_t)grid * 8 > total) return false;
+    }
+    const int64_t warps = (int64_t)grid * 8;
+    if (total * warps >= ((int64_t)1 << 31)) return false;
+    if (toks <= 2 && (total + warps - 1) / warps + 1 > 8) return false;   // a range must fit the x staging buffer
     plan->grid = grid;
+    plan->warps = (int)warps;
     plan->toks = toks;
-    const int64_t min_range = total / grid;                   // >= 1
+    const int64_t min_range = total / warps;                  // >= 1
     plan->slots = (int)((plan->PT + min_range - 1) / min_range) + 1;
     return true;
 }
@@ -701,7 +697,7 @@ int launch_gemv_stream_partials(float* partial, const uint16_t* x, const int32_t
                                 const hqm_weight* w0, const hqm_weight* w1, int G, int C, const StreamPlan& plan,
                                 cudaStream_t st) {
     const int nb = w0->group_size / 16;
-    const Split sp{plan.P * plan.layers, plan.PT, plan.grid};
+    const Split sp{plan.P * plan.layers, plan.PT, plan.warps};
     Layers ly;
     ly.w[0] = *w0;
     ly.w[1] = w1 ? *w1 : *w0;
@@ -711,7 +707,7 @@ int launch_gemv_stream_partials(float* partial, const uint16_t* x, const int32_t
         const int take = ((int)M - m0 < plan.toks) ? (int)M - m0 : plan.toks;
         const int rc = dispatch(w0->nbits, nb, plan.toks, [&](auto b, auto k, auto t) {
             constexpr int B = decltype(b)::value, NBK = decltype(k)::value, T = decltype(t)::value;
-            gemv_stream_kernel<B, NBK, T><<<plan.grid, 256, Shape<B, NBK, T>::smem_bytes(w0->K), st>>>(
+            gemv_stream_kernel<B, NBK, T><<<plan.grid, 256, Shape<B, NBK, T>::smem_bytes(), st>>>(
                 partial, x, x_idx, take, m0, (int)M, ly, G, C, plan.P, sp, field_consts(w0->nbits));
             return 0;
         });
@@ -734,7 +730,7 @@ int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bi
                            int G, const StreamPlan& plan, cudaStream_t st) {
     const int64_t MN = M * w->N;
     finalize_linear_kernel<<<blocks_for(MN), 256, 0, st>>>(y, partial, bias, MN, w->N, G, codes_per_word(w->nbits),
-                                                           plan.P, Split{plan.P * plan.layers, plan.PT, plan.grid});
+                                                           plan.P, Split{plan.P * plan.layers, plan.PT, plan.warps});
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }
@@ -742,7 +738,7 @@ int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bi
 int launch_finalize_silu_mul(uint16_t* h, const float* partial, int64_t M, const hqm_weight* w1, int G,
                              const StreamPlan& plan, cudaStream_t st) {
     finalize_silu_mul_kernel<<<blocks_for(M * w1->N), 256, 0, st>>>(
-        h, partial, M, w1->N, G, codes_per_word(w1->nbits), plan.P, Split{plan.P * plan.layers, plan.PT, plan.grid});
+        h, partial, M, w1->N, G, codes_per_word(w1->nbits), plan.P, Split{plan.P * plan.layers, plan.PT, plan.warps});
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }
@@ -752,7 +748,7 @@ int launch_finalize_scatter(uint16_t* out, const float* partial, const int32_t* 
                             cudaStream_t st) {
     finalize_scatter_kernel<<<blocks_for(M * w2->N), 256, 0, st>>>(
         out, partial, token_idx, route_w, M, w2->N, G, codes_per_word(w2->nbits), plan.P, accumulate,
-        Split{plan.P * plan.layers, plan.PT, plan.grid});
+        Split{plan.P * plan.layers, plan.PT, plan.warps});
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }

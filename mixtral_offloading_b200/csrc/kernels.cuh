@@ -14,8 +14,9 @@ struct StreamPlan {
     int layers;  // 1, or 2 when an expert's w1 and w3 share the launch
     int PT;      // passes per residue (K / pass width)
     int grid;    // CTAs of the single-wave persistent grid
+    int warps;   // warps of that grid: the units the passes are split over
     int toks;    // rows of x decoded per launch
-    int slots;   // upper bound on the CTAs contributing to one residue: fp32 partials [slots][M][layers*N]
+    int slots;   // upper bound on the warps contributing to one residue: fp32 partials [slots][M][layers*N]
 };
 // False when the layer / row count is outside what the streaming kernels cover.
 bool gemv_stream_plan(const hqm_weight* w, int layers, int G, int C, int64_t M, StreamPlan* plan);
