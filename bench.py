@@ -285,6 +285,135 @@ def run_moe(args):
     }))
 
 
+def run_decode(args):
+    """BASELINE configs[4](b) on one GPU: a Mixtral-8x7B-shaped decoder (32 layers unless --layers says
+    otherwise, hidden 4096, 32 query / 8 KV heads of 128, RoPE theta 1e6, RMSNorm eps 1e-5, vocab 32000,
+    bf16 embeddings and lm_head) with random-initialised weights, every expert resident.  The quantized
+    linears (attention 4-bit g64, experts 2-bit g16) and the MoE block are this library; norms, RoPE and
+    the attention core over the KV cache are plain torch ops (they are not part of the rebuilt path).
+    One greedy decode step at batch 1 is captured in a CUDA graph and replayed; the KV cache holds
+    `--context` positions before the first measured token."""
+    from mixtral_offloading_b200 import BaseQuantizeConfig, HQQLinearTritonSavable, ResidentMoe
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    L, H, NH, NKV, HD, E, V = args.layers, HIDDEN, 32, 8, 128, 8, 32000
+    max_len = args.context + args.steps + args.warmup + 8
+    attn_cfg = BaseQuantizeConfig(nbits=4, group_size=64, quant_zero=True, quant_scale=True)
+    torch.manual_seed(0)
+
+    class ModelCfg:
+        hidden_size, intermediate_size, num_local_experts, num_experts_per_tok, hidden_act = H, FFN, E, 2, "silu"
+
+    def qlinear(n_out, n_in):
+        lin = torch.nn.Linear(n_in, n_out, bias=False, device=dev, dtype=torch.float32)
+        lin.weight.data.normal_(0, 0.02)
+        return HQQLinearTritonSavable(lin, attn_cfg)
+
+    layers = []
+    for l in range(L):
+        gate = torch.nn.Linear(H, E, bias=False, dtype=torch.bfloat16, device=dev)
+        gate.weight.data.normal_(0, 0.02)
+        layers.append(dict(
+            q=qlinear(NH * HD, H), k=qlinear(NKV * HD, H), v=qlinear(NKV * HD, H), o=qlinear(H, NH * HD),
+            ln1=torch.ones(H, dtype=torch.bfloat16, device=dev), ln2=torch.ones(H, dtype=torch.bfloat16, device=dev),
+            moe=ResidentMoe(ModelCfg, l, gate, build_pool(dev, E, seed0=1000 * l)),
+            kc=torch.zeros(NKV, max_len, HD, dtype=torch.bfloat16, device=dev).normal_(0, 1),
+            vc=torch.zeros(NKV, max_len, HD, dtype=torch.bfloat16, device=dev).normal_(0, 1)))
+    embed = torch.randn(V, H, device=dev).mul_(0.02).to(torch.bfloat16)
+    lm_head = torch.randn(V, H, device=dev).mul_(0.02).to(torch.bfloat16)
+    ln_f = torch.ones(H, dtype=torch.bfloat16, device=dev)
+    inv_freq = 1.0 / (1e6 ** (torch.arange(0, HD, 2, device=dev, dtype=torch.float32) / HD))
+    pos = torch.full((1,), args.context, dtype=torch.int64, device=dev)     # position of the token being decoded
+    tok = torch.zeros((1,), dtype=torch.int64, device=dev)
+    positions = torch.arange(max_len, device=dev)
+
+    def rms(x, w):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5)).to(torch.bfloat16) * w
+
+    def rope(t):                                                           # t: (heads, HD)
+        ang = pos.float() * inv_freq
+        cos, sin = torch.cat([ang.cos(), ang.cos()]), torch.cat([ang.sin(), ang.sin()])
+        t1, t2 = t[..., :HD // 2], t[..., HD // 2:]
+        return (t.float() * cos + torch.cat([-t2, t1], -1).float() * sin).to(torch.bfloat16)
+
+    def step():
+        h = embed[tok]                                                     # (1, H)
+        for ly in layers:
+            x = rms(h, ly["ln1"])
+            q = rope(ly["q"](x).view(NH, HD))
+            k = rope(ly["k"](x).view(NKV, HD))
+            v = ly["v"](x).view(NKV, HD)
+            ly["kc"].index_copy_(1, pos, k.unsqueeze(1))
+            ly["vc"].index_copy_(1, pos, v.unsqueeze(1))
+            qg = q.view(NKV, NH // NKV, HD).float()
+            scores = torch.matmul(qg, ly["kc"].float().transpose(1, 2)) * (HD ** -0.5)     # (NKV, 4, max_len)
+            scores = scores.masked_fill(positions > pos, float("-inf"))
+            ctx = torch.matmul(torch.softmax(scores, -1), ly["vc"].float()).to(torch.bfloat16).view(1, NH * HD)
+            h = h + ly["o"](ctx)
+            y, _ = ly["moe"](rms(h, ly["ln2"]).view(1, 1, H))
+            h = h + y.view(1, H)
+        logits = torch.matmul(rms(h, ln_f), lm_head.t())
+        tok.copy_(logits.argmax(-1))
+        pos.add_(1)
+        return logits
+
+    lib = __import__("mixtral_offloading_b200")._cabi.lib()
+    with torch.inference_mode():
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize(dev)
+        launches0 = lib.hqm_launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        launches_per_step = lib.hqm_launch_count() - launches0
+        for _ in range(args.warmup):
+            graph.replay()
+        torch.cuda.synchronize(dev)
+        sampler = ClockSampler(0)
+        stream = torch.cuda.current_stream(dev)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        ev1.record(stream)
+        torch.cuda.synchronize(dev)
+        ms = ev0.elapsed_time(ev1) / args.steps
+        # end to end: the caller feeds the token from the host and reads the chosen token back, every step
+        tok_host = torch.zeros(1, dtype=torch.int64).pin_memory()
+        pos.fill_(args.context)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            tok.copy_(tok_host, non_blocking=True)
+            graph.replay()
+            tok_host.copy_(tok, non_blocking=True)
+            stream.synchronize()
+        e1.record(stream)
+        torch.cuda.synchronize(dev)
+        ms_e2e = e0.elapsed_time(e1) / args.steps
+        clocks = sampler.stop()
+    attn_bytes = 2 * layer_bytes(4096, 4096, 4, 64) + 2 * layer_bytes(1024, 4096, 4, 64)
+    kv_bytes = 2 * NKV * args.context * HD * 2
+    step_bytes = L * (attn_bytes + 2 * EXPERT_BYTES + kv_bytes) + V * H * 2
+    scale = 32.0 / L
+    print(json.dumps({
+        "metric": "decode_tokens_per_s_bs1", "value": 1e3 / (ms * scale), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"Mixtral-8x7B-shaped greedy decode, batch 1, {L} of 32 layers built, all experts "
+                   f"resident, KV cache of {args.context} positions"
+                   + ("" if L == 32 else f"; value scales the measured step time by 32/{L}"),
+                   "l2": "a step touches 5.3 GB of weights at 32 layers"},
+        "hbm_gbs": step_bytes / (ms * 1e-3) / 1e9, "algorithmic_bytes_per_step": step_bytes,
+        "e2e": {"value": 1e3 / (ms_e2e * scale), "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": 8,
+                "d2h_bytes_per_step": 8},
+        "gpu_launches": int(launches_per_step * args.steps), "clocks": clocks,
+    }))
+
+
 def run_offload(args):
     """BASELINE configs[4](a) reduced to the MoE blocks: per layer 8 experts, 4 resident on the device and 4
     in pinned host memory, 4 spare slabs, LRU swap through ExpertCache; decode at batch `tokens`.  `layers`
@@ -512,8 +641,9 @@ def main():
     ap.add_argument("--tokens", type=int, default=1)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--layers", type=int, default=8, help="layers built by the offload workload")
-    ap.add_argument("--workload", default="expert", choices=["expert", "moe", "offload"],
+    ap.add_argument("--layers", type=int, default=8, help="layers built by the offload / decode workloads")
+    ap.add_argument("--context", type=int, default=512, help="KV-cache positions before the first decoded token")
+    ap.add_argument("--workload", default="expert", choices=["expert", "moe", "offload", "decode"],
                     help="expert: one expert FFN per step (the default, BASELINE configs[1]); moe: one MoE block "
                          "per step, expert-parallel over the ranks")
     ap.add_argument("--combine", default="all_reduce", choices=["all_reduce", "all_to_all"])
@@ -527,6 +657,10 @@ def main():
         run_reference(args)
     elif args.profile_linear:
         profile_linear(args)
+    elif args.workload == "decode":
+        args.steps = 64 if args.steps is None else args.steps
+        args.warmup = max(3, 5 if args.warmup is None else args.warmup)
+        run_decode(args)
     elif args.workload == "offload":
         args.steps = 50 if args.steps is None else args.steps
         args.warmup = max(3, 5 if args.warmup is None else args.warmup)

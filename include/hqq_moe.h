@@ -136,6 +136,17 @@ int hqm_router_top2(uint16_t* router_logits, float* topk_w, int32_t* topk_idx, i
                     int32_t* token_idx, float* token_w, const uint16_t* x, const uint16_t* gate_w, int64_t M,
                     int64_t K, int32_t E, void* stream);
 
+/* The whole of SparseMoeWrapper.forward (custom_layers.py:272-314) for ONE token when every expert is
+ * resident on the device: router, then the two chosen experts' FFNs, weighted and summed into out (1, hidden).
+ * Which experts run is decided on the device (the FFN kernels read the router's choice and fetch that
+ * expert's descriptors from `table`), so nothing is copied back to the host and the call can be captured in a
+ * CUDA graph.  table: 3*E descriptors in DEVICE memory, expert e at [3e] = w1, [3e+1] = w2, [3e+2] = w3.
+ * w1 / w2 / w3: host descriptors giving the (common) shapes and format.  router_logits: (1, E) bf16. */
+size_t hqm_moe_decode_scratch_bytes(int32_t E, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3);
+int hqm_moe_decode(uint16_t* out, uint16_t* router_logits, const uint16_t* x, const uint16_t* gate_w, int32_t E,
+                   const hqm_weight* table, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3,
+                   void* scratch, size_t scratch_bytes, void* stream);
+
 /* ---- expert residency: src/expert_cache.py -------------------------------- */
 /* ExpertCache (expert_cache.py:55-201).  The handle owns the bookkeeping of
  * ExpertInfo / EvictionGroupInfo (expert_cache.py:12-52), a side copy stream and

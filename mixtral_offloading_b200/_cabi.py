@@ -50,6 +50,8 @@ SIGNATURES = {
     "hqm_linear_static_scratch": (C.c_int, [_P, _P, _I64, _WP, _P, _P]),
     "hqm_expert_ffn_scratch_bytes": (C.c_size_t, [_I64, _WP, _WP, _WP]),
     "hqm_expert_ffn": (C.c_int, [_P, _P, _I64, _P, _P, C.c_int, _WP, _WP, _WP, _P, C.c_size_t, _P]),
+    "hqm_moe_decode_scratch_bytes": (C.c_size_t, [_I32, _WP, _WP, _WP]),
+    "hqm_moe_decode": (C.c_int, [_P, _P, _P, _P, _I32, _P, _WP, _WP, _WP, _P, C.c_size_t, _P]),
     "hqm_router_top2": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),
     "hqm_cache_create": (C.c_int, [C.POINTER(_P), _I32, _I32, _I32, C.c_size_t, C.POINTER(_P), _I32]),
     "hqm_cache_destroy": (None, [_P]),

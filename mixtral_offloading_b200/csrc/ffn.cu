@@ -175,4 +175,59 @@ int hqm_expert_ffn(uint16_t* out, const uint16_t* x, int64_t M, const int32_t* t
     return HQM_OK;
 }
 
+// ---- single-token MoE block with every expert resident: the host never learns the routing ----------
+static size_t moe_decode_router_bytes(int E) { return hqm::align_up((size_t)(4 + 4 + 2 * E + 1 + 4) * 4, 256); }
+
+size_t hqm_moe_decode_scratch_bytes(int32_t E, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3) {
+    if (!w1 || !w2 || !w3 || E < 2) return 0;
+    hqm::FusedPlan fp;
+    if (!hqm::fused_plan(1, w1, w2, w3, nullptr, &fp)) return 0;
+    return moe_decode_router_bytes(E) + fp.up_bytes + fp.h_bytes + fp.down_bytes;
+}
+
+int hqm_moe_decode(uint16_t* out, uint16_t* router_logits, const uint16_t* x, const uint16_t* gate_w, int32_t E,
+                   const hqm_weight* table, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3,
+                   void* scratch, size_t scratch_bytes, void* stream) {
+    using namespace hqm;
+    HQM_CHECK_ARG(out && router_logits && x && gate_w && table && w1 && w2 && w3, "moe_decode: null pointer");
+    HQM_CHECK_ARG(E >= 2 && E <= 32, "moe_decode: %d experts not supported (2..32)", E);
+    FusedPlan fp;
+    HQM_CHECK_ARG(fused_plan(1, w1, w2, w3, x, &fp), "moe_decode: these expert shapes are outside the streaming path");
+    const size_t need = hqm_moe_decode_scratch_bytes(E, w1, w2, w3);
+    if (scratch == nullptr || scratch_bytes < need) {
+        set_error("moe_decode: scratch of %zu bytes given, %zu needed", scratch_bytes, need);
+        return HQM_ERR_SCRATCH;
+    }
+    HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "moe_decode: scratch must be 256-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    // router outputs live at the head of the scratch buffer
+    float* topk_w = (float*)scratch;                    // [2] (+2 pad)
+    int32_t* topk_idx = (int32_t*)(topk_w + 4);         // [2] (+2 pad)
+    int32_t* counts = topk_idx + 4;                     // [E]
+    int32_t* offsets = counts + E;                      // [E + 1]
+    int32_t* tok_idx = offsets + E + 1;                 // [2]
+    float* tok_w = (float*)(tok_idx + 2);               // [2]
+    int rc = hqm_router_top2(router_logits, topk_w, topk_idx, counts, offsets, tok_idx, tok_w, x, gate_w, 1, w1->K, E,
+                             stream);
+    if (rc != HQM_OK) return rc;
+    uint8_t* p = (uint8_t*)scratch + moe_decode_router_bytes(E);
+    float* up = (float*)p;
+    uint16_t* h = (uint16_t*)(p + fp.up_bytes);
+    float* down = (float*)(p + fp.up_bytes + fp.h_bytes);
+    for (int slot = 0; slot < 2; ++slot) {
+        // the expert is whatever the router wrote to topk_idx[slot]; its descriptors come from the table
+        const ExpertPick gate_up{table, topk_idx + slot, {0, 2}};
+        const ExpertPick down_proj{table, topk_idx + slot, {1, 1}};
+        rc = launch_gemv_stream_partials(up, x, nullptr, 1, w1, w3, fp.G1, fp.C1, fp.up, st, &gate_up);
+        if (rc != HQM_OK) return rc;
+        rc = launch_finalize_silu_mul(h, up, 1, w1, fp.G1, fp.up, st);
+        if (rc != HQM_OK) return rc;
+        rc = launch_gemv_stream_partials(down, h, nullptr, 1, w2, nullptr, fp.G2, fp.C2, fp.down, st, &down_proj);
+        if (rc != HQM_OK) return rc;
+        rc = launch_finalize_scatter(out, down, nullptr, topk_w + slot, /*accumulate=*/slot, 1, w2, fp.G2, fp.down, st);
+        if (rc != HQM_OK) return rc;
+    }
+    return HQM_OK;
+}
+
 }  // extern "C"

@@ -165,7 +165,7 @@ struct Shape {
     static constexpr int PW = 64 * SUB;                         // pass width in columns
     static constexpr bool STAGE_X = TOKS <= 2;                  // x converted to fp16 in shared memory per segment
     static constexpr int ROW = 72;                              // 64 columns + padding against bank conflicts
-    static constexpr int WARP_HALFS = SUB * (MTOK + 1) * PER * ROW;
+    static constexpr int WARP_HALFS = SUB * (MTOK * PER + PER + 1) * ROW;   // xs rows, z rows, one zero row
     static constexpr int NW = 8;
     static constexpr int XPASS = 8;                             // longest range (passes) a warp may be given
     // Asynchronous-copy ring: per warp DEPTH slots, each one pass of 16-byte cells per lane:
@@ -219,9 +219,16 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 // Up to two layers of identical shape share one launch (the expert's w1 and w3): their
 // residues are numbered one after the other and the output columns of layer 1 follow
 // those of layer 0.
+// With `table` set the layers are not the descriptors passed by value but entries of a descriptor table in
+// device memory, picked by an index that is itself in device memory (the router's choice): layer l is
+// table[3 * *sel + pick[l]].  w[0] then only carries the common shape.  This keeps the host out of the
+// loop when all experts are resident.
 struct Layers {
     hqm_weight w[2];
     int count;
+    const hqm_weight* table;
+    const int32_t* sel;
+    int pick[2];
 };
 
 template <int NBITS, int NB, int TOKS>
@@ -240,13 +247,13 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
     const int N_total = N * ly.count;
     unsigned char* warp_mem = smem_raw + (size_t)wi * S::WARP_BYTES;               // everything is warp-private
     __half* xs_w = reinterpret_cast<__half*>(warp_mem);                             // [SUB][MTOK][PER][ROW]
-    __half* zz_w = xs_w + SUB * MTOK * PER * ROW;                                  // [SUB][PER][ROW]
+    __half* zz_w = xs_w + SUB * MTOK * PER * ROW;                                  // [SUB][PER + 1][ROW], last row zero
     unsigned char* ring = warp_mem + (size_t)S::WARP_HALFS * 2 + lane * 16;        // this lane's cell column
     __half* xh = reinterpret_cast<__half*>(warp_mem + (size_t)S::WARP_HALFS * 2 + (size_t)S::DEPTH * S::SLOT_BYTES);
     constexpr int XCOLS = S::XPASS * PW;                                           // [TOKS][XCOLS]
 
-    // token rows that exist only to fill a column tile stay zero for the whole kernel
-    for (int i = lane; i < SUB * MTOK * PER * ROW / 2; i += 32) reinterpret_cast<uint32_t*>(xs_w)[i] = 0u;
+    // token rows that exist only to fill a column tile, and the extra z row, stay zero for the whole kernel
+    for (int i = lane; i < S::WARP_HALFS / 2; i += 32) reinterpret_cast<uint32_t*>(xs_w)[i] = 0u;
     __syncwarp();
 
     const uint16_t* xr[TOKS];
@@ -260,6 +267,7 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
     const int sB = g % PER, mB = g / PER;           // slot / token of this lane's B column
     const int sa = (2 * t) % PER;                   // first of the two slots whose columns this lane reads back
     const uint32_t keep = (g < PER) ? 0xffffffffu : 0u;
+    const int zrow = (g < PER ? g : PER) * ROW + 16 * t;      // this lane's row of the z tile (row PER is zero)
     const uint32_t olo = ((g & 1) ? F::off_lo(1) : F::off_lo(0)) * 0x00010001u & keep;
     const uint32_t ohi = ((g & 1) ? F::off_hi(1) : F::off_hi(0)) * 0x00010001u & keep;
     uint32_t qoff[NB];                              // this lane's weight rows, bytes from W_q + rho*K + k0
@@ -275,7 +283,7 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
         const int pb = min(PT, pa + (int)(L_end - L));
         L += (uint32_t)(pb - pa);
         const int layer = rho_g / P, rho = rho_g - layer * P;
-        const hqm_weight& w = ly.w[layer];
+        const hqm_weight w = ly.table ? ly.table[3 * ly.sel[0] + ly.pick[layer]] : ly.w[layer];
 
         float acc[NB][NT][PER][4];
         float accc[NT][4];
@@ -379,7 +387,7 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
                     z2[j] = h2_bits(meta_decode(prmt(r.zq[u][j / 2], 0x64646464u, sel), bits_h2(r.mzz[u][j]),
                                                 bits_h2(r.msz[u][j])));
                 }
-                st_words(zz_w + (u * PER + sd) * ROW + kd, z2);
+                st_words(zz_w + (u * (PER + 1) + sd) * ROW + kd, z2);
 #pragma unroll
                 for (int m = 0; m < TOKS; ++m) {
                     uint32_t xs2[DK / 2];
@@ -415,11 +423,11 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
                 // 3. correction tile: rows 0..PER-1 = z of slot i, rows 8..8+PER-1 = the offsets
                 {
                     uint32_t zf[8];
-                    const __half* src = zz_w + (u * PER + (g < PER ? g : 0)) * ROW + 16 * t;
+                    const __half* src = zz_w + u * (PER + 1) * ROW + zrow;      // lanes without a slot read zeros
                     const uint4 lo4 = *reinterpret_cast<const uint4*>(src);
                     const uint4 hi4 = *reinterpret_cast<const uint4*>(src + 8);
-                    zf[0] = lo4.x & keep; zf[1] = lo4.y & keep; zf[2] = lo4.z & keep; zf[3] = lo4.w & keep;
-                    zf[4] = hi4.x & keep; zf[5] = hi4.y & keep; zf[6] = hi4.z & keep; zf[7] = hi4.w & keep;
+                    zf[0] = lo4.x; zf[1] = lo4.y; zf[2] = lo4.z; zf[3] = lo4.w;
+                    zf[4] = hi4.x; zf[5] = hi4.y; zf[6] = hi4.z; zf[7] = hi4.w;
 #pragma unroll
                     for (int wd = 0; wd < 4; ++wd)
 #pragma unroll
@@ -695,13 +703,17 @@ size_t gemv_stream_scratch_bytes(const StreamPlan& plan, int64_t M, int N) {
 
 int launch_gemv_stream_partials(float* partial, const uint16_t* x, const int32_t* x_idx, int64_t M,
                                 const hqm_weight* w0, const hqm_weight* w1, int G, int C, const StreamPlan& plan,
-                                cudaStream_t st) {
+                                cudaStream_t st, const ExpertPick* pick) {
     const int nb = w0->group_size / 16;
     const Split sp{plan.P * plan.layers, plan.PT, plan.warps};
     Layers ly;
     ly.w[0] = *w0;
     ly.w[1] = w1 ? *w1 : *w0;
     ly.count = plan.layers;
+    ly.table = pick ? pick->table : nullptr;
+    ly.sel = pick ? pick->sel : nullptr;
+    ly.pick[0] = pick ? pick->which[0] : 0;
+    ly.pick[1] = pick ? pick->which[1] : 0;
     // rows beyond one launch's tokens go in further launches over the same split
     for (int m0 = 0; m0 < (int)M; m0 += plan.toks) {
         const int take = ((int)M - m0 < plan.toks) ? (int)M - m0 : plan.toks;

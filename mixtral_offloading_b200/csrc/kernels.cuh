@@ -21,9 +21,16 @@ struct StreamPlan {
 // False when the layer / row count is outside what the streaming kernels cover.
 bool gemv_stream_plan(const hqm_weight* w, int layers, int G, int C, int64_t M, StreamPlan* plan);
 size_t gemv_stream_scratch_bytes(const StreamPlan& plan, int64_t M, int N);
+// Device-side choice of the expert whose layers a streaming launch reads: descriptor table (3 per expert:
+// w1, w2, w3), pointer to the expert index, and which of the three each of the (up to 2) layers is.
+struct ExpertPick {
+    const hqm_weight* table;
+    const int32_t* sel;
+    int which[2];
+};
 int launch_gemv_stream_partials(float* partial, const uint16_t* x, const int32_t* x_idx, int64_t M,
                                 const hqm_weight* w0, const hqm_weight* w1, int G, int C, const StreamPlan& plan,
-                                cudaStream_t st);
+                                cudaStream_t st, const ExpertPick* pick = nullptr);
 int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bias, int64_t M, const hqm_weight* w,
                            int G, const StreamPlan& plan, cudaStream_t st);
 int launch_finalize_silu_mul(uint16_t* h, const float* partial, int64_t M, const hqm_weight* w1, int G,

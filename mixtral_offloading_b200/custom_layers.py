@@ -301,3 +301,83 @@ class SparseMoeWrapper(nn.Module):
         if hidden_states.dtype != torch.bfloat16:
             final, logits = final.to(hidden_states.dtype), logits.to(hidden_states.dtype)
         return final, logits
+
+
+class ResidentMoe(nn.Module):
+    """SparseMoeWrapper.forward for a layer whose experts ALL live on the device (no ExpertCache).
+
+    With nothing to swap, the host does not need to know the routing: for a single token the whole block —
+    router, the two chosen experts, weighted sum — runs as one chain of launches that pick the experts on
+    the device (hqm_moe_decode), so it can be captured in a CUDA graph.  More tokens take the same
+    per-expert loop as SparseMoeWrapper (one read-back of the row counts).
+    `experts` is a list of MixtralBLockSparseTop2MLP_HQQ / MixtralExpertWrapper, index = expert id.
+    """
+
+    def __init__(self, config, layer_id, gate, experts):
+        super().__init__()
+        self.hidden_dim = config.hidden_size
+        self.num_experts = config.num_local_experts
+        assert config.num_experts_per_tok == 2 and len(experts) == self.num_experts
+        self.layer_id = layer_id
+        self.gate = gate
+        self._experts = list(experts)              # kept out of the module registry like the wrapper does
+        self._router = SparseMoeWrapper(config, layer_id, gate, expert_cache=None)
+        self._table = None
+        self._host_counts = None
+
+    @staticmethod
+    def _ffn(expert):
+        return expert._expert if hasattr(expert, "_expert") else expert
+
+    def _descriptor_table(self, device):
+        """3 * E struct hqm_weight in device memory: (w1, w2, w3) of expert 0, 1, ..."""
+        if self._table is None:
+            raw = bytearray()
+            for ex in self._experts:
+                f = self._ffn(ex)
+                for lyr in (f.w1, f.w2, f.w3):
+                    raw += bytes(lyr.descriptor())
+            with torch.inference_mode(False):
+                self._table = torch.frombuffer(raw, dtype=torch.uint8).clone().to(device)
+        return self._table
+
+    @torch.inference_mode()
+    def forward(self, hidden_states: torch.Tensor):
+        batch, seq, hidden = hidden_states.shape
+        x2 = _as_bf16_2d(hidden_states, hidden)
+        T, E = x2.shape[0], self.num_experts
+        dev = x2.device
+        if T == 1:
+            f0 = self._ffn(self._experts[0])
+            d1, d2, d3 = f0.w1.descriptor(), f0.w2.descriptor(), f0.w3.descriptor()
+            lib = _cabi.lib()
+            need = lib.hqm_moe_decode_scratch_bytes(E, C.byref(d1), C.byref(d2), C.byref(d3))
+            if need:
+                gate_w = self.gate.weight if self.gate.weight.dtype == torch.bfloat16 else self.gate.weight.to(torch.bfloat16)
+                out = torch.empty((1, hidden), dtype=torch.bfloat16, device=dev)
+                logits = torch.empty((1, E), dtype=torch.bfloat16, device=dev)
+                ws = _scratch(dev, need)
+                _cabi.check(lib.hqm_moe_decode(_cabi.ptr(out), _cabi.ptr(logits), _cabi.ptr(x2), _cabi.ptr(gate_w), E,
+                                               _cabi.ptr(self._descriptor_table(dev)), C.byref(d1), C.byref(d2),
+                                               C.byref(d3), _cabi.ptr(ws), ws.numel(), _cabi.stream_ptr(dev)))
+                out = out.reshape(batch, seq, hidden)
+                if hidden_states.dtype != torch.bfloat16:
+                    out, logits = out.to(hidden_states.dtype), logits.to(hidden_states.dtype)
+                return out, logits
+        logits, _, _, meta, token_idx, token_w = self._router.route(x2)
+        if self._host_counts is None:
+            with torch.inference_mode(False):
+                self._host_counts = torch.empty((2 * E + 1,), dtype=torch.int32).pin_memory()
+        self._host_counts.copy_(meta, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+        host = self._host_counts.tolist()
+        counts, offsets = host[:E], host[E:]
+        final = torch.zeros((T, hidden), dtype=torch.bfloat16, device=dev)
+        for e in range(E):
+            if counts[e] > 0:
+                lo, hi = offsets[e], offsets[e + 1]
+                self._experts[e].forward_routed(x2, token_idx[lo:hi], token_w[lo:hi], final, accumulate=True)
+        final = final.reshape(batch, seq, hidden)
+        if hidden_states.dtype != torch.bfloat16:
+            final, logits = final.to(hidden_states.dtype), logits.to(hidden_states.dtype)
+        return final, logits

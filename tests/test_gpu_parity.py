@@ -332,6 +332,49 @@ def test_moe_block_golden(golden_dir):
     assert gi.misses > 0
 
 
+def test_resident_moe_device_side_routing():
+    """All experts resident: the single-token block never tells the host which experts ran, and can be
+    replayed from a CUDA graph; several tokens fall back to the per-expert loop.  Both match the oracle."""
+    from mixtral_offloading_b200 import ResidentMoe
+    hidden, ffn, n_exp = 256, 512, 8
+    experts = [tuple(random_layer(n, k, 2, 16, seed=20 * e + i) for i, (n, k) in
+                     enumerate(((ffn, hidden), (hidden, ffn), (ffn, hidden)))) for e in range(n_exp)]
+    g = torch.Generator().manual_seed(11)
+    gate_w = (torch.randn(n_exp, hidden, generator=g) * 0.05).to(torch.bfloat16)
+    gate = torch.nn.Linear(hidden, n_exp, bias=False, dtype=torch.bfloat16, device=DEV)
+    gate.weight.data = gate_w.to(DEV)
+    moe = ResidentMoe(Cfg(hidden, ffn, n_exp), 0, gate, [make_expert(hidden, ffn, ods) for ods in experts])
+    router = SparseMoeWrapper(Cfg(hidden, ffn, n_exp), 0, gate, None)
+    xs = torch.randn(6, hidden, generator=g).to(torch.bfloat16)
+    seen = set()
+    for t in range(6):
+        x = xs[t:t + 1]
+        y, logits = moe(x.to(DEV).reshape(1, 1, hidden))
+        _, tw, ti, _, _, _ = router.route(x.to(DEV))
+        seen.update(ti.cpu().flatten().tolist())
+        want, want_logits = O.moe_forward(x, gate_w, experts, routing=(tw.cpu(), ti.cpu()))
+        assert O.rel_err(y.cpu().reshape(1, hidden), want) < TOL
+        assert O.rel_err(logits.cpu(), want_logits) < TOL
+    assert len(seen) > 2                                  # different tokens really picked different experts
+    y, _ = moe(xs.to(DEV).reshape(1, 6, hidden))          # several tokens: host-driven loop
+    _, tw, ti, _, _, _ = router.route(xs.to(DEV))
+    want, _ = O.moe_forward(xs, gate_w, experts, routing=(tw.cpu(), ti.cpu()))
+    assert O.rel_err(y.cpu().reshape(6, hidden), want) < TOL
+    # graph replay with a new input: the routing changes inside the graph
+    x_static = xs[0:1].to(DEV).reshape(1, 1, hidden).clone()
+    moe(x_static)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y_static, _ = moe(x_static)
+    for t in (3, 5):
+        x_static.copy_(xs[t:t + 1].to(DEV).reshape(1, 1, hidden))
+        graph.replay()
+        _, tw, ti, _, _, _ = router.route(xs[t:t + 1].to(DEV))
+        want, _ = O.moe_forward(xs[t:t + 1], gate_w, experts, routing=(tw.cpu(), ti.cpu()))
+        assert O.rel_err(y_static.cpu().reshape(1, hidden), want) < TOL
+
+
 def test_expert_cache_moves_the_right_bytes(golden_dir):
     """Replay the reference's recorded requests on real slabs: every yielded module must hold
     its expert's bytes, and residency / hits / misses must follow the reference."""
