@@ -328,30 +328,31 @@ def run_decode(args):
     tok = torch.zeros((1,), dtype=torch.int64, device=dev)
     positions = torch.arange(max_len, device=dev)
 
-    def rms(x, w):
-        xf = x.float()
-        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5)).to(torch.bfloat16) * w
+    F = torch.nn.functional
+    ang = positions.float()[:, None] * inv_freq[None, :]
+    cos_tab = torch.cat([ang.cos(), ang.cos()], -1)                        # (max_len, HD) fp32
+    sin_tab = torch.cat([ang.sin(), ang.sin()], -1)
 
-    def rope(t):                                                           # t: (heads, HD)
-        ang = pos.float() * inv_freq
-        cos, sin = torch.cat([ang.cos(), ang.cos()]), torch.cat([ang.sin(), ang.sin()])
-        t1, t2 = t[..., :HD // 2], t[..., HD // 2:]
-        return (t.float() * cos + torch.cat([-t2, t1], -1).float() * sin).to(torch.bfloat16)
+    def rms(x, w):
+        return F.rms_norm(x, (H,), w, 1e-5)
+
+    def rope(t):                                                           # t: (heads, HD), rotate_half form
+        cos, sin = cos_tab[pos], sin_tab[pos]
+        rot = torch.cat([-t[..., HD // 2:], t[..., :HD // 2]], -1)
+        return (t.float() * cos + rot.float() * sin).to(torch.bfloat16)
 
     def step():
         h = embed[tok]                                                     # (1, H)
+        mask = (positions <= pos).view(1, 1, 1, max_len)
         for ly in layers:
             x = rms(h, ly["ln1"])
-            q = rope(ly["q"](x).view(NH, HD))
-            k = rope(ly["k"](x).view(NKV, HD))
+            qk = rope(torch.cat([ly["q"](x).view(NH, HD), ly["k"](x).view(NKV, HD)], 0))
             v = ly["v"](x).view(NKV, HD)
-            ly["kc"].index_copy_(1, pos, k.unsqueeze(1))
+            ly["kc"].index_copy_(1, pos, qk[NH:].unsqueeze(1))
             ly["vc"].index_copy_(1, pos, v.unsqueeze(1))
-            qg = q.view(NKV, NH // NKV, HD).float()
-            scores = torch.matmul(qg, ly["kc"].float().transpose(1, 2)) * (HD ** -0.5)     # (NKV, 4, max_len)
-            scores = scores.masked_fill(positions > pos, float("-inf"))
-            ctx = torch.matmul(torch.softmax(scores, -1), ly["vc"].float()).to(torch.bfloat16).view(1, NH * HD)
-            h = h + ly["o"](ctx)
+            ctx = F.scaled_dot_product_attention(qk[:NH].view(1, NH, 1, HD), ly["kc"].unsqueeze(0), ly["vc"].unsqueeze(0),
+                                                 attn_mask=mask, enable_gqa=True)
+            h = h + ly["o"](ctx.view(1, NH * HD))
             y, _ = ly["moe"](rms(h, ly["ln2"]).view(1, 1, H))
             h = h + y.view(1, H)
         logits = torch.matmul(rms(h, ln_f), lm_head.t())
