@@ -59,6 +59,8 @@ size_t linear_scratch_bytes(int64_t M, const hqm_weight* w) {
     if (M <= 0 || check_weight(w, &G, &C) != HQM_OK) return 0;
     if (force_generic()) return 0;
     if (M >= TC_MIN_ROWS && gemm_tc_supported(w, G, C, M)) return ((size_t)M * w->N * sizeof(float) + 255) / 256 * 256;
+    Stream3Plan plan3;
+    if (gemv_stream3_plan(w, G, C, M, &plan3)) return gemv_stream3_scratch_bytes(plan3, M, w->N);
     if (!gemv_stream_plan(w, 1, G, C, M, &plan)) return 0;
     return (gemv_stream_scratch_bytes(plan, M, w->N) + 255) / 256 * 256;
 }
@@ -82,6 +84,15 @@ int launch_linear(uint16_t* y, const uint16_t* x, const int32_t* x_idx, int64_t 
         rc = launch_gemm_tc((float*)scratch, x, x_idx, M, w, nullptr, G, C, st);
         if (rc != HQM_OK) return rc;
         return launch_rows_from_sums(y, (const float*)scratch, bias, M, w->N, st);
+    }
+    Stream3Plan plan3;
+    if (gemv_stream3_plan(w, G, C, M, &plan3)) {
+        const size_t need = gemv_stream3_scratch_bytes(plan3, M, w->N);
+        if (scratch == nullptr || scratch_bytes < need) {
+            set_error("linear: scratch of %zu bytes given, %zu needed", scratch_bytes, need);
+            return HQM_ERR_SCRATCH;
+        }
+        return launch_gemv_stream3(y, (float*)scratch, x, x_idx, M, w, bias, G, C, plan3, st);
     }
     if (gemv_stream_plan(w, 1, G, C, M, &plan)) {
         const size_t need = gemv_stream_scratch_bytes(plan, M, w->N);

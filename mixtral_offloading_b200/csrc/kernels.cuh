@@ -40,6 +40,19 @@ int launch_finalize_scatter(uint16_t* out, const float* partial, const int32_t* 
                             cudaStream_t st);
 bool force_generic();
 
+// gemv_stream3.cu — the weight-streaming path for 3-bit layers.
+struct Stream3Plan {
+    int P3;      // storage-row classes (rows R and R + P3 hold the same residues in the same slots)
+    int PT;      // 64-column passes per class
+    int rows;    // storage rows, ceil(N / 10)
+    int grid, warps, slots;
+};
+bool gemv_stream3_plan(const hqm_weight* w, int G, int C, int64_t M, Stream3Plan* plan);
+size_t gemv_stream3_scratch_bytes(const Stream3Plan& plan, int64_t M, int N);
+int launch_gemv_stream3(uint16_t* y, float* partial, const uint16_t* x, const int32_t* x_idx, int64_t M,
+                        const hqm_weight* w, const uint16_t* bias, int G, int C, const Stream3Plan& plan,
+                        cudaStream_t st);
+
 // gemm_tc.cu — tcgen05 / TMEM path for many rows of x.
 bool gemm_tc_supported(const hqm_weight* w, int G, int C, int64_t M);
 int launch_gemm_tc(float* sums, const uint16_t* x, const int32_t* x_idx, int64_t M, const hqm_weight* w0,
