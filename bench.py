@@ -486,16 +486,46 @@ def run_offload(args):
 
 
 def profile_linear(args):
-    """A few launches of the dominant kernel on HBM-cold weights, nothing else (for ncu)."""
+    """N launches of one quantized linear on HBM-cold weights, nothing else: the small case meant for ncu.
+    --layer NxK:nbits:group picks the layer (default: the expert's w1, 14336x4096:2:16); enough distinct
+    copies are built to exceed L2.  Also prints the time per call measured over a CUDA graph."""
+    from mixtral_offloading_b200 import BaseQuantizeConfig, HQQLinearTritonSavable
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    pool = build_pool(dev, 2, seed0=0)                      # 2 experts = 6 layers = 133 MB > 126 MB L2
-    layers = [getattr(w._expert, n) for w in pool for n in ("w1", "w3")]
-    x = torch.randn(args.tokens, HIDDEN, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(dev)
+    shape, nbits, group = args.layer.split(":")
+    N, K = (int(v) for v in shape.split("x"))
+    nbits, group = int(nbits), int(group)
+    cfg = BaseQuantizeConfig(nbits=nbits, group_size=group, quant_zero=True, quant_scale=True)
+    one = layer_bytes(N, K, nbits, group)
+    copies = max(2, int(140e6 // one) + 1)
+    layers = []
+    for i in range(copies):
+        lin = torch.nn.Linear(K, N, bias=False, device=dev)
+        lin.weight.data.normal_(0, 0.02)
+        layers.append(HQQLinearTritonSavable(lin, cfg))
+        del lin
+    x = torch.randn(args.tokens, K, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(dev)
     for i in range(args.profile_linear):
-        layers[i % len(layers)](x)
+        layers[i % copies](x)
     torch.cuda.synchronize(dev)
-    print(json.dumps({"profile_linear": args.profile_linear, "tokens": args.tokens}))
+    reps = 100
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(reps):
+            layers[i % copies](x)
+    graph.replay()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    nbytes = one + 2 * args.tokens * (N + K)
+    peak, _ = measured_peak()
+    print(json.dumps({"profile_linear": args.profile_linear, "layer": args.layer, "tokens": args.tokens, "copies": copies,
+                      "us_per_call": us, "algorithmic_bytes": nbytes, "gbs": nbytes / us / 1e3,
+                      "frac_of_measured_hbm": nbytes / us / 1e3 / peak}))
 
 
 def run_b200(args):
@@ -648,6 +678,7 @@ def main():
                     help="expert: one expert FFN per step (the default, BASELINE configs[1]); moe: one MoE block "
                          "per step, expert-parallel over the ranks")
     ap.add_argument("--combine", default="all_reduce", choices=["all_reduce", "all_to_all"])
+    ap.add_argument("--layer", default="14336x4096:2:16", help="NxK:nbits:group for --profile-linear")
     ap.add_argument("--profile-linear", type=int, default=0, metavar="N",
                     help="only launch N quantized linears (w1 shape, rotating over 6 layers > L2) and exit; "
                          "the small case meant to be run under ncu")
