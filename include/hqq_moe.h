@@ -62,6 +62,16 @@ int64_t hqm_launch_count(void);
 /* 1 if a bounded wait inside a tensor-core GEMM launch ever ran out (that launch skipped its work),
  * 0 otherwise, -1 on a CUDA error.  Synchronises the device; meant for tests and start-up checks. */
 int hqm_device_error(void);
+/* No counterpart in the reference.  The streaming kernels and their reductions are launched so that a
+ * kernel may become resident, set itself up and start requesting WEIGHT bytes while the kernel in front of
+ * it on the stream is still finishing (programmatic dependent launch); activations, indices, outputs and
+ * scratch are touched only after everything in front has completed.  The consequence for the caller: the
+ * weight tensors of a call (W_q, scale_q, zero_q and the fp16 meta) must not be written by the work that
+ * immediately precedes the call on the same stream; order such writes with an event, a copy or a
+ * synchronisation, as a cache swap does.  hqm_set_overlap(0) switches to plain launches (so does
+ * HQM_NO_OVERLAP=1 in the environment at load time), hqm_set_overlap(1) switches back; returns the previous
+ * setting.  Process wide. */
+int hqm_set_overlap(int on);
 
 /* ---- bit packing: src/packing.py --------------------------------------- */
 /* pack_4bit_u8_common, packing.py:10-17.  codes (N, K) uint8 -> packed (N/2, K). */

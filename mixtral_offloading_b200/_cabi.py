@@ -37,6 +37,7 @@ SIGNATURES = {
     "hqm_version": (C.c_int, []),
     "hqm_launch_count": (C.c_int64, []),
     "hqm_device_error": (C.c_int, []),
+    "hqm_set_overlap": (C.c_int, [C.c_int]),
     "hqm_pack_4bit_u8": (C.c_int, [_P, _P, _I64, _I64, _P]),
     "hqm_unpack_4bit_u8": (C.c_int, [_P, _P, _I64, _I64, _P]),
     "hqm_pack_2bit_u8": (C.c_int, [_P, _P, _I64, _I64, _P]),

@@ -53,12 +53,29 @@ bool force_generic() {
     return on;
 }
 
+static std::atomic<int> g_overlap{-1};
+bool overlap_enabled() {
+    int v = g_overlap.load(std::memory_order_relaxed);
+    if (v < 0) {
+        const char* e = getenv("HQM_NO_OVERLAP");
+        v = (e && e[0] == '1') ? 0 : 1;
+        g_overlap.store(v, std::memory_order_relaxed);
+    }
+    return v != 0;
+}
+int set_overlap(int on) {
+    const int prev = overlap_enabled() ? 1 : 0;
+    g_overlap.store(on ? 1 : 0, std::memory_order_relaxed);
+    return prev;
+}
+
 size_t linear_scratch_bytes(int64_t M, const hqm_weight* w) {
     int G, C;
     StreamPlan plan;
     if (M <= 0 || check_weight(w, &G, &C) != HQM_OK) return 0;
     if (force_generic()) return 0;
     if (M >= TC_MIN_ROWS && gemm_tc_supported(w, G, C, M)) return ((size_t)M * w->N * sizeof(float) + 255) / 256 * 256;
+    if (gemm_tc3_supported(w, G, C, M)) return gemm_tc3_scratch_bytes(w, G, M);
     Stream3Plan plan3;
     if (gemv_stream3_plan(w, G, C, M, &plan3)) return gemv_stream3_scratch_bytes(plan3, M, w->N);
     if (!gemv_stream_plan(w, 1, G, C, M, &plan)) return 0;
@@ -84,6 +101,15 @@ int launch_linear(uint16_t* y, const uint16_t* x, const int32_t* x_idx, int64_t 
         rc = launch_gemm_tc((float*)scratch, x, x_idx, M, w, nullptr, G, C, st);
         if (rc != HQM_OK) return rc;
         return launch_rows_from_sums(y, (const float*)scratch, bias, M, w->N, st);
+    }
+    if (gemm_tc3_supported(w, G, C, M)) {
+        const size_t need = gemm_tc3_scratch_bytes(w, G, M);
+        if (scratch == nullptr || scratch_bytes < need) {
+            set_error("linear: scratch of %zu bytes given, %zu needed", scratch_bytes, need);
+            return HQM_ERR_SCRATCH;
+        }
+        HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 15u) == 0, "linear: scratch must be 16-byte aligned");
+        return launch_gemm_tc3(y, scratch, x, x_idx, M, w, bias, G, C, st);
     }
     Stream3Plan plan3;
     if (gemv_stream3_plan(w, G, C, M, &plan3)) {
@@ -115,6 +141,7 @@ extern "C" {
 const char* hqm_last_error(void) { return hqm::g_error; }
 int hqm_version(void) { return 1; }
 int64_t hqm_launch_count(void) { return (int64_t)hqm::launches(); }
+int hqm_set_overlap(int on) { return hqm::set_overlap(on); }
 
 size_t hqm_linear_scratch_bytes(int64_t M, const hqm_weight* w) { return hqm::linear_scratch_bytes(M, w); }
 

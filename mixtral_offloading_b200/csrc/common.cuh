@@ -81,4 +81,33 @@ __device__ __forceinline__ uint32_t ld_stream_4(const void* p) {
     return v;
 }
 
+// ---- programmatic dependent launch ----------------------------------------------------------------
+// A kernel launched with launch_overlapped() may become resident while the kernel in front of it on the
+// stream is still running.  Whatever it does before grid_dependency_wait() overlaps that kernel (set-up
+// work, and reads of memory the kernels in front never write); grid_dependency_wait() returns once
+// every earlier kernel has completed and its writes are visible.  grid_launch_dependents() tells the
+// scheduler that the NEXT kernel may be made resident.  Both are no-ops in a kernel launched the plain way,
+// and a kernel launched the plain way still waits for the whole of its predecessor.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// HQM_NO_OVERLAP=1 in the environment turns launch_overlapped() into a plain launch.
+bool overlap_enabled();
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                     Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, Params(args)...);
+}
+
 }  // namespace hqm

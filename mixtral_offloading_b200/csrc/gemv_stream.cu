@@ -252,16 +252,22 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
     __half* xh = reinterpret_cast<__half*>(warp_mem + (size_t)S::WARP_HALFS * 2 + (size_t)S::DEPTH * S::SLOT_BYTES);
     constexpr int XCOLS = S::XPASS * PW;                                           // [TOKS][XCOLS]
 
+    // The next kernel on the stream may be made resident as SMs free up; this one overlaps the tail of the
+    // kernel in front of it until `synced`: the weights are never written by a kernel of the chain, so the
+    // first passes are requested before the wait; x, the row indices, the expert choice and the partial
+    // buffer belong to earlier kernels and are touched only after it.
+    grid_launch_dependents();
+    bool synced = false;
+    if (ly.table) {
+        grid_dependency_wait();
+        synced = true;
+    }
+
     // token rows that exist only to fill a column tile, and the extra z row, stay zero for the whole kernel
     for (int i = lane; i < S::WARP_HALFS / 2; i += 32) reinterpret_cast<uint32_t*>(xs_w)[i] = 0u;
     __syncwarp();
 
     const uint16_t* xr[TOKS];
-#pragma unroll
-    for (int m = 0; m < TOKS; ++m) {
-        const int mm = (m < M) ? (m_base + m) : m_base;
-        xr[m] = x + (int64_t)(x_idx ? x_idx[mm] : mm) * K;
-    }
     const int sd = lane / LPS;                      // slot this lane decodes
     const int kd = (lane % LPS) * DK;               // its first column inside a sub-pass
     const int sB = g % PER, mB = g / PER;           // slot / token of this lane's B column
@@ -472,6 +478,15 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
             if (pa + sl < pb) issue(sl, pa + sl);
             cp_async_commit();
         }
+        if (!synced) {
+            grid_dependency_wait();
+            synced = true;
+        }
+#pragma unroll
+        for (int m = 0; m < TOKS; ++m) {
+            const int mm = (m < M) ? (m_base + m) : m_base;
+            xr[m] = x + (int64_t)(x_idx ? x_idx[mm] : mm) * K;
+        }
         if constexpr (S::STAGE_X) {
             // the segment's columns of x, converted to fp16 once
             const int c0 = pa * PW, nc = (pb - pa) * PW;
@@ -550,6 +565,8 @@ __device__ __forceinline__ int partial_count(const Split& sp, int n, int N, int 
 __global__ void finalize_linear_kernel(uint16_t* __restrict__ y, const float* __restrict__ partial,
                                        const uint16_t* __restrict__ bias, int64_t MN, int N, int G, int per, int P,
                                        Split sp) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < MN; i += (int64_t)gridDim.x * blockDim.x) {
         const int n = (int)(i % N);
         const int cnt = partial_count(sp, n, N, G, per, P);
@@ -564,6 +581,8 @@ __global__ void finalize_linear_kernel(uint16_t* __restrict__ y, const float* __
 // w1 / w3 halves of a two-layer launch (columns f and F + f).
 __global__ void finalize_silu_mul_kernel(uint16_t* __restrict__ h, const float* __restrict__ partial, int64_t M,
                                          int F, int G, int per, int P, Split sp) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int64_t MF = M * F, M2F = 2 * MF;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < MF; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t m = i / F;
@@ -584,6 +603,8 @@ __global__ void finalize_silu_mul_kernel(uint16_t* __restrict__ h, const float* 
 __global__ void finalize_scatter_kernel(uint16_t* __restrict__ out, const float* __restrict__ partial,
                                         const int32_t* __restrict__ token_idx, const float* __restrict__ route_w,
                                         int64_t M, int H, int G, int per, int P, int accumulate, Split sp) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int64_t MH = M * H;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < MH; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t m = i / H;
@@ -719,8 +740,8 @@ int launch_gemv_stream_partials(float* partial, const uint16_t* x, const int32_t
         const int take = ((int)M - m0 < plan.toks) ? (int)M - m0 : plan.toks;
         const int rc = dispatch(w0->nbits, nb, plan.toks, [&](auto b, auto k, auto t) {
             constexpr int B = decltype(b)::value, NBK = decltype(k)::value, T = decltype(t)::value;
-            gemv_stream_kernel<B, NBK, T><<<plan.grid, 256, Shape<B, NBK, T>::smem_bytes(), st>>>(
-                partial, x, x_idx, take, m0, (int)M, ly, G, C, plan.P, sp, field_consts(w0->nbits));
+            launch_overlapped(gemv_stream_kernel<B, NBK, T>, plan.grid, 256, Shape<B, NBK, T>::smem_bytes(), st, partial,
+                              x, x_idx, take, m0, (int)M, ly, G, C, plan.P, sp, field_consts(w0->nbits));
             return 0;
         });
         if (rc != 0) {
@@ -741,16 +762,16 @@ static inline int blocks_for(int64_t n) {
 int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bias, int64_t M, const hqm_weight* w,
                            int G, const StreamPlan& plan, cudaStream_t st) {
     const int64_t MN = M * w->N;
-    finalize_linear_kernel<<<blocks_for(MN), 256, 0, st>>>(y, partial, bias, MN, w->N, G, codes_per_word(w->nbits),
-                                                           plan.P, Split{plan.P * plan.layers, plan.PT, plan.warps});
+    launch_overlapped(finalize_linear_kernel, blocks_for(MN), 256, 0, st, y, partial, bias, MN, w->N, G,
+                      codes_per_word(w->nbits), plan.P, Split{plan.P * plan.layers, plan.PT, plan.warps});
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }
 
 int launch_finalize_silu_mul(uint16_t* h, const float* partial, int64_t M, const hqm_weight* w1, int G,
                              const StreamPlan& plan, cudaStream_t st) {
-    finalize_silu_mul_kernel<<<blocks_for(M * w1->N), 256, 0, st>>>(
-        h, partial, M, w1->N, G, codes_per_word(w1->nbits), plan.P, Split{plan.P * plan.layers, plan.PT, plan.warps});
+    launch_overlapped(finalize_silu_mul_kernel, blocks_for(M * w1->N), 256, 0, st, h, partial, M, w1->N, G,
+                      codes_per_word(w1->nbits), plan.P, Split{plan.P * plan.layers, plan.PT, plan.warps});
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }
@@ -758,9 +779,9 @@ int launch_finalize_silu_mul(uint16_t* h, const float* partial, int64_t M, const
 int launch_finalize_scatter(uint16_t* out, const float* partial, const int32_t* token_idx, const float* route_w,
                             int accumulate, int64_t M, const hqm_weight* w2, int G, const StreamPlan& plan,
                             cudaStream_t st) {
-    finalize_scatter_kernel<<<blocks_for(M * w2->N), 256, 0, st>>>(
-        out, partial, token_idx, route_w, M, w2->N, G, codes_per_word(w2->nbits), plan.P, accumulate,
-        Split{plan.P * plan.layers, plan.PT, plan.warps});
+    launch_overlapped(finalize_scatter_kernel, blocks_for(M * w2->N), 256, 0, st, out, partial, token_idx, route_w, M,
+                      w2->N, G, codes_per_word(w2->nbits), plan.P, accumulate,
+                      Split{plan.P * plan.layers, plan.PT, plan.warps});
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }

@@ -61,7 +61,14 @@ int launch_rows_from_sums(uint16_t* y, const float* sums, const uint16_t* bias, 
 int launch_silu_mul_from_sums(uint16_t* h, const float* sums, int64_t M, int F, cudaStream_t st);
 int launch_scatter_from_sums(uint16_t* out, const float* sums, const int32_t* token_idx, const float* route_w,
                              int accumulate, int64_t M, int H, cudaStream_t st);
+int* tc_error_ptr();                  // device flag the bounded waits set when they give up
 constexpr int64_t TC_MIN_ROWS = 17;   // fewer rows go to the streaming kernels
+
+// gemm_tc3.cu — the same for 3-bit layers (row counts >= 5).
+bool gemm_tc3_supported(const hqm_weight* w, int G, int C, int64_t M);
+size_t gemm_tc3_scratch_bytes(const hqm_weight* w, int G, int64_t M);
+int launch_gemm_tc3(uint16_t* y, void* scratch, const uint16_t* x, const int32_t* x_idx, int64_t M,
+                    const hqm_weight* w, const uint16_t* bias, int G, int C, cudaStream_t st);
 
 // Dispatcher used by hqm_linear and by the expert FFN: picks the streaming
 // kernel when the layer's shape allows it, the generic one otherwise.

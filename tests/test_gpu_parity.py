@@ -257,6 +257,48 @@ def test_expert_ffn_mid_size(M):
     assert O.rel_err(y, O.expert_ffn(x, *ods)) < TOL
 
 
+def test_overlapped_launches_give_the_same_bits():
+    """A chain of expert FFNs feeding each other, launched back to back with no host work in between: each
+    kernel may start while its predecessor is still running.  The result must be bit-identical to plain
+    launches, eagerly and replayed from a CUDA graph."""
+    hidden, ffn = 1024, 3584
+    experts = []
+    for e in range(3):
+        ods = (random_layer(ffn, hidden, 2, 16, 10 * e + 1), random_layer(hidden, ffn, 2, 16, 10 * e + 2),
+               random_layer(ffn, hidden, 2, 16, 10 * e + 3))
+        experts.append(make_expert(hidden, ffn, ods))
+    x = torch.randn(1, hidden, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).to(DEV)
+
+    def chain(inp):
+        h = inp
+        for rep in range(4):
+            for ex in experts:
+                h = ex(h)
+                h = (h.float() / h.float().abs().max().clamp_min(1e-6)).to(torch.bfloat16)   # keep the scale
+        return h
+
+    prev = _cabi.lib().hqm_set_overlap(0)
+    try:
+        plain = chain(x).clone()
+        assert _cabi.lib().hqm_set_overlap(1) == 0
+        for _ in range(3):
+            assert torch.equal(chain(x), plain)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            chain(x)                                   # allocations settle before capture
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = chain(x)
+        for _ in range(3):
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(out, plain)
+    finally:
+        _cabi.lib().hqm_set_overlap(prev)
+
+
 def test_expert_ffn_routed_accumulates():
     hidden, ffn, T = 256, 512, 9
     ods = (random_layer(ffn, hidden, 2, 16, 1), random_layer(hidden, ffn, 2, 16, 2), random_layer(ffn, hidden, 2, 16, 3))
