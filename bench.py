@@ -288,12 +288,15 @@ def run_moe(args):
 def run_decode(args):
     """BASELINE configs[4](b) on one GPU: a Mixtral-8x7B-shaped decoder (32 layers unless --layers says
     otherwise, hidden 4096, 32 query / 8 KV heads of 128, RoPE theta 1e6, RMSNorm eps 1e-5, vocab 32000,
-    bf16 embeddings and lm_head) with random-initialised weights, every expert resident.  The quantized
-    linears (attention 4-bit g64, experts 2-bit g16) and the MoE block are this library; norms, RoPE and
-    the attention core over the KV cache are plain torch ops (they are not part of the rebuilt path).
-    One greedy decode step at batch 1 is captured in a CUDA graph and replayed; the KV cache holds
-    `--context` positions before the first measured token."""
-    from mixtral_offloading_b200 import BaseQuantizeConfig, HQQLinearTritonSavable, ResidentMoe
+    bf16 embeddings and lm_head) with random-initialised weights, every expert resident.  Each layer is two
+    calls into this library: the attention half (AttentionDecode: norms, 4-bit g64 projections, RoPE, KV
+    cache, attention, residual) and the MoE block (ResidentMoe: router and both 2-bit g16 experts);
+    embedding lookup, lm_head matmul and argmax are torch ops.  One greedy decode step at batch 1 is
+    captured in a CUDA graph and replayed; the KV cache holds `--context` positions before the first
+    measured token.  Before timing, one step is also computed with torch ops around the library's linears
+    (rms_norm, RoPE tables, scaled_dot_product_attention) and the logits of the two are compared."""
+    from mixtral_offloading_b200 import (AttentionDecode, BaseQuantizeConfig, HQQLinearTritonSavable, ResidentMoe,
+                                         add_rmsnorm)
 
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -314,17 +317,20 @@ def run_decode(args):
     for l in range(L):
         gate = torch.nn.Linear(H, E, bias=False, dtype=torch.bfloat16, device=dev)
         gate.weight.data.normal_(0, 0.02)
-        layers.append(dict(
-            q=qlinear(NH * HD, H), k=qlinear(NKV * HD, H), v=qlinear(NKV * HD, H), o=qlinear(H, NH * HD),
-            ln1=torch.ones(H, dtype=torch.bfloat16, device=dev), ln2=torch.ones(H, dtype=torch.bfloat16, device=dev),
-            moe=ResidentMoe(ModelCfg, l, gate, build_pool(dev, E, seed0=1000 * l)),
-            kc=torch.zeros(NKV, max_len, HD, dtype=torch.bfloat16, device=dev).normal_(0, 1),
-            vc=torch.zeros(NKV, max_len, HD, dtype=torch.bfloat16, device=dev).normal_(0, 1)))
+        ly = dict(q=qlinear(NH * HD, H), k=qlinear(NKV * HD, H), v=qlinear(NKV * HD, H), o=qlinear(H, NH * HD),
+                  ln1=(1 + 0.05 * torch.randn(H, device=dev)).to(torch.bfloat16),
+                  ln2=(1 + 0.05 * torch.randn(H, device=dev)).to(torch.bfloat16),
+                  moe=ResidentMoe(ModelCfg, l, gate, build_pool(dev, E, seed0=1000 * l)))
+        ly["attn"] = AttentionDecode(ly["q"], ly["k"], ly["v"], ly["o"], ly["ln1"], ly["ln2"], NH, NKV, HD, max_len,
+                                     rope_theta=1e6, rms_eps=1e-5)
+        ly["kc"], ly["vc"] = ly["attn"].k_cache.normal_(0, 1), ly["attn"].v_cache.normal_(0, 1)
+        layers.append(ly)
     embed = torch.randn(V, H, device=dev).mul_(0.02).to(torch.bfloat16)
     lm_head = torch.randn(V, H, device=dev).mul_(0.02).to(torch.bfloat16)
     ln_f = torch.ones(H, dtype=torch.bfloat16, device=dev)
     inv_freq = 1.0 / (1e6 ** (torch.arange(0, HD, 2, device=dev, dtype=torch.float32) / HD))
     pos = torch.full((1,), args.context, dtype=torch.int64, device=dev)     # position of the token being decoded
+    pos32 = torch.full((1,), args.context, dtype=torch.int32, device=dev)
     tok = torch.zeros((1,), dtype=torch.int64, device=dev)
     positions = torch.arange(max_len, device=dev)
 
@@ -342,7 +348,19 @@ def run_decode(args):
         return (t.float() * cos + rot.float() * sin).to(torch.bfloat16)
 
     def step():
-        h = embed[tok]                                                     # (1, H)
+        h = embed[tok]                                                     # (1, H), a fresh tensor
+        delta = None
+        for ly in layers:
+            x = ly["attn"](h, pos32, delta)                                # h updated in place
+            y, _ = ly["moe"](x.view(1, 1, H))
+            delta = y.view(1, H)
+        logits = torch.matmul(add_rmsnorm(h, delta, ln_f, 1e-5), lm_head.t())
+        tok.copy_(logits.argmax(-1))
+        pos32.add_(1)
+        return logits
+
+    def step_torch_glue():
+        h = embed[tok]
         mask = (positions <= pos).view(1, 1, 1, max_len)
         for ly in layers:
             x = rms(h, ly["ln1"])
@@ -362,9 +380,15 @@ def run_decode(args):
 
     lib = __import__("mixtral_offloading_b200")._cabi.lib()
     with torch.inference_mode():
+        logits_glue = step_torch_glue().float()
+        tok.zero_()
+        logits_lib = step().float()
+        logits_diff = float((logits_lib - logits_glue).abs().max() / logits_glue.abs().max())
         for _ in range(3):
             step()
         torch.cuda.synchronize(dev)
+        tok.zero_()
+        pos32.fill_(args.context)
         launches0 = lib.hqm_launch_count()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
@@ -384,7 +408,7 @@ def run_decode(args):
         ms = ev0.elapsed_time(ev1) / args.steps
         # end to end: the caller feeds the token from the host and reads the chosen token back, every step
         tok_host = torch.zeros(1, dtype=torch.int64).pin_memory()
-        pos.fill_(args.context)
+        pos32.fill_(args.context)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(args.steps):
@@ -407,7 +431,8 @@ def run_decode(args):
         "config": {"workload": f"Mixtral-8x7B-shaped greedy decode, batch 1, {L} of 32 layers built, all experts "
                    f"resident, KV cache of {args.context} positions"
                    + ("" if L == 32 else f"; value scales the measured step time by 32/{L}"),
-                   "l2": "a step touches 5.3 GB of weights at 32 layers"},
+                   "l2": "a step touches 5.3 GB of weights at 32 layers",
+                   "logits_max_rel_diff_vs_torch_glue": logits_diff},
         "hbm_gbs": step_bytes / (ms * 1e-3) / 1e9, "algorithmic_bytes_per_step": step_bytes,
         "e2e": {"value": 1e3 / (ms_e2e * scale), "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": 8,
                 "d2h_bytes_per_step": 8},

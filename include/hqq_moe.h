@@ -60,7 +60,8 @@ int hqm_version(void);
 /* Number of CUDA kernels this library has launched in the process so far (for benchmarks). */
 int64_t hqm_launch_count(void);
 /* 1 if a bounded wait inside a tensor-core GEMM launch ever ran out (that launch skipped its work),
- * 0 otherwise, -1 on a CUDA error.  Synchronises the device; meant for tests and start-up checks. */
+ * 2 if hqm_attn_decode was given a position outside its cache, 0 otherwise, -1 on a CUDA error.  Reading a
+ * non-zero value clears it.  Synchronises the device; meant for tests and start-up checks. */
 int hqm_device_error(void);
 /* No counterpart in the reference.  The streaming kernels and their reductions are launched so that a
  * kernel may become resident, set itself up and start requesting WEIGHT bytes while the kernel in front of
@@ -156,6 +157,36 @@ size_t hqm_moe_decode_scratch_bytes(int32_t E, const hqm_weight* w1, const hqm_w
 int hqm_moe_decode(uint16_t* out, uint16_t* router_logits, const uint16_t* x, const uint16_t* gate_w, int32_t E,
                    const hqm_weight* table, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3,
                    void* scratch, size_t scratch_bytes, void* stream);
+
+/* ---- the attention half of a decoder layer, one token ---------------------- */
+/* The reference takes this step from the Hugging Face Mixtral decoder layer (build_model.py:166-241 builds the
+ * model; the q/k/v/o projections inside it are HQQLinearTritonSavable, custom_layers.py:49-92).  It is offered
+ * here, next to hqm_moe_decode, so that a whole decode step at batch 1 is a fixed sequence of launches:
+ *     h += delta (when delta is given);  x = rmsnorm(h) * ln_in;
+ *     q, k, v = projections of x;  rotate q and k by position *pos (rotate-half RoPE);
+ *     k_cache[:, *pos] = k;  v_cache[:, *pos] = v;
+ *     ctx = softmax(q K^T / sqrt(head_dim)) V over positions 0..*pos, n_heads / n_kv_heads query heads per
+ *     key/value head;  h += o(ctx);  x_out = rmsnorm(h) * ln_post.
+ * h (hidden) bf16 is the residual stream, updated in place; x_out (hidden) bf16 is the MoE block's input.
+ * pos: one int32 in DEVICE memory (the caller advances it), so a captured graph can be replayed.
+ * A position outside [0, max_len) writes nothing and makes hqm_device_error() return 2.
+ * The four projections must share K-compatible streaming formats (2- or 4-bit); head_dim must be 128. */
+typedef struct {
+    hqm_weight q, k, v, o;
+    const uint16_t* ln_in;    /* bf16 (hidden): input_layernorm.weight */
+    const uint16_t* ln_post;  /* bf16 (hidden): post_attention_layernorm.weight */
+    uint16_t* k_cache;        /* bf16 (n_kv_heads, max_len, head_dim) */
+    uint16_t* v_cache;
+    int32_t n_heads, n_kv_heads, head_dim, max_len;
+    float rope_theta, rms_eps;
+} hqm_attn_layer;
+size_t hqm_attn_decode_scratch_bytes(const hqm_attn_layer* layer);
+int hqm_attn_decode(uint16_t* h, uint16_t* x_out, const uint16_t* delta, const hqm_attn_layer* layer,
+                    const int32_t* pos, void* scratch, size_t scratch_bytes, void* stream);
+/* h = bf16(h + delta) when delta is given; x_out = bf16(weight * bf16(h * rsqrt(mean(h^2) + eps))): the RMSNorm
+ * of the Hugging Face decoder with the preceding residual add (used for the last layer's output and the final norm). */
+int hqm_add_rmsnorm(uint16_t* h, const uint16_t* delta, const uint16_t* weight, uint16_t* x_out, int32_t hidden,
+                    float eps, void* stream);
 
 /* ---- expert residency: src/expert_cache.py -------------------------------- */
 /* ExpertCache (expert_cache.py:55-201).  The handle owns the bookkeeping of

@@ -26,6 +26,16 @@ class HqmWeight(C.Structure):
     ]
 
 
+class HqmAttnLayer(C.Structure):
+    """struct hqm_attn_layer."""
+    _fields_ = [
+        ("q", HqmWeight), ("k", HqmWeight), ("v", HqmWeight), ("o", HqmWeight),
+        ("ln_in", C.c_void_p), ("ln_post", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+        ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("max_len", C.c_int32),
+        ("rope_theta", C.c_float), ("rms_eps", C.c_float),
+    ]
+
+
 _P = C.c_void_p
 _I64 = C.c_int64
 _I32 = C.c_int32
@@ -53,6 +63,9 @@ SIGNATURES = {
     "hqm_expert_ffn": (C.c_int, [_P, _P, _I64, _P, _P, C.c_int, _WP, _WP, _WP, _P, C.c_size_t, _P]),
     "hqm_moe_decode_scratch_bytes": (C.c_size_t, [_I32, _WP, _WP, _WP]),
     "hqm_moe_decode": (C.c_int, [_P, _P, _P, _P, _I32, _P, _WP, _WP, _WP, _P, C.c_size_t, _P]),
+    "hqm_attn_decode_scratch_bytes": (C.c_size_t, [C.POINTER(HqmAttnLayer)]),
+    "hqm_attn_decode": (C.c_int, [_P, _P, _P, C.POINTER(HqmAttnLayer), _P, _P, C.c_size_t, _P]),
+    "hqm_add_rmsnorm": (C.c_int, [_P, _P, _P, _P, _I32, C.c_float, _P]),
     "hqm_router_top2": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),
     "hqm_cache_create": (C.c_int, [C.POINTER(_P), _I32, _I32, _I32, C.c_size_t, C.POINTER(_P), _I32]),
     "hqm_cache_destroy": (None, [_P]),

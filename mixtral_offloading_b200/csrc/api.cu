@@ -78,8 +78,9 @@ size_t linear_scratch_bytes(int64_t M, const hqm_weight* w) {
     if (gemm_tc3_supported(w, G, C, M)) return gemm_tc3_scratch_bytes(w, G, M);
     Stream3Plan plan3;
     if (gemv_stream3_plan(w, G, C, M, &plan3)) return gemv_stream3_scratch_bytes(plan3, M, w->N);
-    if (!gemv_stream_plan(w, 1, G, C, M, &plan)) return 0;
-    return (gemv_stream_scratch_bytes(plan, M, w->N) + 255) / 256 * 256;
+    const hqm_weight* one[1] = {w};
+    if (!gemv_stream_plan(one, 1, M, &plan)) return 0;
+    return (gemv_stream_scratch_bytes(plan, M) + 255) / 256 * 256;
 }
 
 int launch_linear(uint16_t* y, const uint16_t* x, const int32_t* x_idx, int64_t M, const hqm_weight* w,
@@ -120,16 +121,19 @@ int launch_linear(uint16_t* y, const uint16_t* x, const int32_t* x_idx, int64_t 
         }
         return launch_gemv_stream3(y, (float*)scratch, x, x_idx, M, w, bias, G, C, plan3, st);
     }
-    if (gemv_stream_plan(w, 1, G, C, M, &plan)) {
-        const size_t need = gemv_stream_scratch_bytes(plan, M, w->N);
+    const hqm_weight* one[1] = {w};
+    if (gemv_stream_plan(one, 1, M, &plan)) {
+        const size_t need = gemv_stream_scratch_bytes(plan, M);
         if (scratch == nullptr || scratch_bytes < need) {
             set_error("linear: scratch of %zu bytes given, %zu needed", scratch_bytes, need);
             return HQM_ERR_SCRATCH;
         }
         HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 15u) == 0, "linear: scratch must be 16-byte aligned");
-        rc = launch_gemv_stream_partials((float*)scratch, x, x_idx, M, w, nullptr, G, C, plan, st);
+        StreamJob job{};
+        job.w[0] = w;
+        rc = launch_gemv_stream((float*)scratch, x, x_idx, M, job, plan, st);
         if (rc != HQM_OK) return rc;
-        return launch_finalize_linear(y, (const float*)scratch, bias, M, w, G, plan, st);
+        return launch_finalize_linear(y, (const float*)scratch, bias, M, plan, st);
     }
     return launch_linear_generic(y, x, x_idx, M, w, G, C, bias, st);
 }

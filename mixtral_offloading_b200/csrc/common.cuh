@@ -94,20 +94,37 @@ __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddep
 // HQM_NO_OVERLAP=1 in the environment turns launch_overlapped() into a plain launch.
 bool overlap_enabled();
 
+// `cluster` > 1 launches thread-block clusters of that many CTAs along x (the grid must be a multiple).
 template <typename... Params, typename... Args>
-inline cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
-                                     Args&&... args) {
+inline cudaError_t launch_overlapped_cluster(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                             int cluster, cudaStream_t st, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (cluster > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = (unsigned)cluster;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (overlap_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = overlap_enabled() ? 1 : 0;
+    cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, Params(args)...);
+}
+template <typename... Params, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                     Args&&... args) {
+    return launch_overlapped_cluster(kernel, grid, block, smem, 1, st, static_cast<Args&&>(args)...);
 }
 
 }  // namespace hqm

@@ -75,12 +75,12 @@ static bool fused_plan(int64_t M, const hqm_weight* w1, const hqm_weight* w2, co
         check_weight(w2, &fp->G2, &fp->C2) != HQM_OK)
         return false;
     if (x && (reinterpret_cast<uintptr_t>(x) & 15u) != 0) return false;
-    if (!gemv_stream_plan(w1, 2, fp->G1, fp->C1, M, &fp->up) || !gemv_stream_plan(w3, 2, fp->G1, fp->C1, M, &fp->up) ||
-        !gemv_stream_plan(w2, 1, fp->G2, fp->C2, M, &fp->down))
-        return false;
-    fp->up_bytes = align_up(gemv_stream_scratch_bytes(fp->up, M, w1->N), 256);
+    const hqm_weight* up[2] = {w1, w3};
+    const hqm_weight* down[1] = {w2};
+    if (!gemv_stream_plan(up, 2, M, &fp->up) || !gemv_stream_plan(down, 1, M, &fp->down)) return false;
+    fp->up_bytes = align_up(gemv_stream_scratch_bytes(fp->up, M), 256);
     fp->h_bytes = align_up((size_t)M * w1->N * 2, 256);
-    fp->down_bytes = align_up(gemv_stream_scratch_bytes(fp->down, M, w2->N), 256);
+    fp->down_bytes = align_up(gemv_stream_scratch_bytes(fp->down, M), 256);
     return true;
 }
 
@@ -142,13 +142,17 @@ int hqm_expert_ffn(uint16_t* out, const uint16_t* x, int64_t M, const int32_t* t
         float* up = (float*)p;
         uint16_t* h = (uint16_t*)(p + fp.up_bytes);
         float* down = (float*)(p + fp.up_bytes + fp.h_bytes);
-        int rc = launch_gemv_stream_partials(up, x, token_idx, M, w1, w3, fp.G1, fp.C1, fp.up, st);
+        StreamJob gate_up{}, down_proj{};
+        gate_up.w[0] = w1;
+        gate_up.w[1] = w3;
+        down_proj.w[0] = w2;
+        int rc = launch_gemv_stream(up, x, token_idx, M, gate_up, fp.up, st);
         if (rc != HQM_OK) return rc;
-        rc = launch_finalize_silu_mul(h, up, M, w1, fp.G1, fp.up, st);
+        rc = launch_finalize_silu_mul(h, up, M, fp.up, st);
         if (rc != HQM_OK) return rc;
-        rc = launch_gemv_stream_partials(down, h, nullptr, M, w2, nullptr, fp.G2, fp.C2, fp.down, st);
+        rc = launch_gemv_stream(down, h, nullptr, M, down_proj, fp.down, st);
         if (rc != HQM_OK) return rc;
-        return launch_finalize_scatter(out, down, token_idx, route_w, accumulate, M, w2, fp.G2, fp.down, st);
+        return launch_finalize_scatter(out, down, token_idx, route_w, accumulate, M, fp.down, st);
     }
     uint16_t* a = (uint16_t*)p;
     p += align_up((size_t)M * F * 2, 256);
@@ -176,13 +180,32 @@ int hqm_expert_ffn(uint16_t* out, const uint16_t* x, int64_t M, const int32_t* t
 }
 
 // ---- single-token MoE block with every expert resident: the host never learns the routing ----------
-static size_t moe_decode_router_bytes(int E) { return hqm::align_up((size_t)(4 + 4 + 2 * E + 1 + 4) * 4, 256); }
+// Both experts of the token share every launch: [w1; w3] of expert A and of expert B in one streaming
+// launch (4 layers), one silu-mul over both, the two w2 in one launch (2 layers, each reading its own h
+// row), one weighted sum.
+namespace hqm {
+struct MoeDecodePlan {
+    StreamPlan up, down;
+    size_t router_bytes, up_bytes, h_bytes, down_bytes;
+};
+static bool moe_decode_plan(int E, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3, MoeDecodePlan* mp) {
+    const hqm_weight* up[4] = {w1, w3, w1, w3};
+    const hqm_weight* down[2] = {w2, w2};
+    if (!same_format(w1, w3) || !gemv_stream_plan(up, 4, 1, &mp->up) || !gemv_stream_plan(down, 2, 1, &mp->down))
+        return false;
+    mp->router_bytes = align_up((size_t)(4 + 4 + 2 * E + 1 + 4) * 4, 256);
+    mp->up_bytes = align_up(gemv_stream_scratch_bytes(mp->up, 1), 256);
+    mp->h_bytes = align_up((size_t)2 * w1->N * 2, 256);
+    mp->down_bytes = align_up(gemv_stream_scratch_bytes(mp->down, 1), 256);
+    return true;
+}
+}  // namespace hqm
 
 size_t hqm_moe_decode_scratch_bytes(int32_t E, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3) {
     if (!w1 || !w2 || !w3 || E < 2) return 0;
-    hqm::FusedPlan fp;
-    if (!hqm::fused_plan(1, w1, w2, w3, nullptr, &fp)) return 0;
-    return moe_decode_router_bytes(E) + fp.up_bytes + fp.h_bytes + fp.down_bytes;
+    hqm::MoeDecodePlan mp;
+    if (!hqm::moe_decode_plan(E, w1, w2, w3, &mp)) return 0;
+    return mp.router_bytes + mp.up_bytes + mp.h_bytes + mp.down_bytes;
 }
 
 int hqm_moe_decode(uint16_t* out, uint16_t* router_logits, const uint16_t* x, const uint16_t* gate_w, int32_t E,
@@ -191,9 +214,10 @@ int hqm_moe_decode(uint16_t* out, uint16_t* router_logits, const uint16_t* x, co
     using namespace hqm;
     HQM_CHECK_ARG(out && router_logits && x && gate_w && table && w1 && w2 && w3, "moe_decode: null pointer");
     HQM_CHECK_ARG(E >= 2 && E <= 32, "moe_decode: %d experts not supported (2..32)", E);
-    FusedPlan fp;
-    HQM_CHECK_ARG(fused_plan(1, w1, w2, w3, x, &fp), "moe_decode: these expert shapes are outside the streaming path");
-    const size_t need = hqm_moe_decode_scratch_bytes(E, w1, w2, w3);
+    HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(x) & 15u) == 0, "moe_decode: x must be 16-byte aligned");
+    MoeDecodePlan mp;
+    HQM_CHECK_ARG(moe_decode_plan(E, w1, w2, w3, &mp), "moe_decode: these expert shapes are outside the streaming path");
+    const size_t need = mp.router_bytes + mp.up_bytes + mp.h_bytes + mp.down_bytes;
     if (scratch == nullptr || scratch_bytes < need) {
         set_error("moe_decode: scratch of %zu bytes given, %zu needed", scratch_bytes, need);
         return HQM_ERR_SCRATCH;
@@ -203,31 +227,33 @@ int hqm_moe_decode(uint16_t* out, uint16_t* router_logits, const uint16_t* x, co
     // router outputs live at the head of the scratch buffer
     float* topk_w = (float*)scratch;                    // [2] (+2 pad)
     int32_t* topk_idx = (int32_t*)(topk_w + 4);         // [2] (+2 pad)
-    int32_t* counts = topk_idx + 4;                     // [E]
-    int32_t* offsets = counts + E;                      // [E + 1]
-    int32_t* tok_idx = offsets + E + 1;                 // [2]
-    float* tok_w = (float*)(tok_idx + 2);               // [2]
-    int rc = hqm_router_top2(router_logits, topk_w, topk_idx, counts, offsets, tok_idx, tok_w, x, gate_w, 1, w1->K, E,
-                             stream);
+    int rc = launch_router_top2(router_logits, topk_w, topk_idx, x, gate_w, 1, w1->K, E, st);
     if (rc != HQM_OK) return rc;
-    uint8_t* p = (uint8_t*)scratch + moe_decode_router_bytes(E);
+    uint8_t* p = (uint8_t*)scratch + mp.router_bytes;
     float* up = (float*)p;
-    uint16_t* h = (uint16_t*)(p + fp.up_bytes);
-    float* down = (float*)(p + fp.up_bytes + fp.h_bytes);
+    uint16_t* h = (uint16_t*)(p + mp.up_bytes);         // [2][F]: one row per chosen expert
+    float* down = (float*)(p + mp.up_bytes + mp.h_bytes);
+    // the experts are whatever the router wrote to topk_idx[0..1]; their descriptors come from the table
+    StreamJob gate_up{}, down_proj{};
+    gate_up.table = down_proj.table = table;
     for (int slot = 0; slot < 2; ++slot) {
-        // the expert is whatever the router wrote to topk_idx[slot]; its descriptors come from the table
-        const ExpertPick gate_up{table, topk_idx + slot, {0, 2}};
-        const ExpertPick down_proj{table, topk_idx + slot, {1, 1}};
-        rc = launch_gemv_stream_partials(up, x, nullptr, 1, w1, w3, fp.G1, fp.C1, fp.up, st, &gate_up);
-        if (rc != HQM_OK) return rc;
-        rc = launch_finalize_silu_mul(h, up, 1, w1, fp.G1, fp.up, st);
-        if (rc != HQM_OK) return rc;
-        rc = launch_gemv_stream_partials(down, h, nullptr, 1, w2, nullptr, fp.G2, fp.C2, fp.down, st, &down_proj);
-        if (rc != HQM_OK) return rc;
-        rc = launch_finalize_scatter(out, down, nullptr, topk_w + slot, /*accumulate=*/slot, 1, w2, fp.G2, fp.down, st);
-        if (rc != HQM_OK) return rc;
+        gate_up.w[2 * slot] = w1;
+        gate_up.w[2 * slot + 1] = w3;
+        gate_up.sel[2 * slot] = gate_up.sel[2 * slot + 1] = topk_idx + slot;
+        gate_up.which[2 * slot] = 0;
+        gate_up.which[2 * slot + 1] = 2;
+        down_proj.w[slot] = w2;
+        down_proj.sel[slot] = topk_idx + slot;
+        down_proj.which[slot] = 1;
+        down_proj.xrow[slot] = slot;
     }
-    return HQM_OK;
+    rc = launch_gemv_stream(up, x, nullptr, 1, gate_up, mp.up, st);
+    if (rc != HQM_OK) return rc;
+    rc = launch_finalize_silu_mul(h, up, 1, mp.up, st);
+    if (rc != HQM_OK) return rc;
+    rc = launch_gemv_stream(down, h, nullptr, 1, down_proj, mp.down, st);
+    if (rc != HQM_OK) return rc;
+    return launch_finalize_scatter(out, down, nullptr, topk_w, /*accumulate=*/0, 1, mp.down, st);
 }
 
 }  // extern "C"

@@ -428,13 +428,14 @@ int launch_scatter_from_sums(uint16_t* out, const float* sums, const int32_t* to
 
 }  // namespace hqm
 
-// 1 if a bounded wait inside a tensor-core GEMM launch ever ran out (the launch then skipped its
-// work); synchronises the device.  Not part of the per-token path.
+// Reads and clears the device-side failure flag (see the header); synchronises the device.  Not part of
+// the per-token path.
 extern "C" int hqm_device_error(void) {
     int v = 0;
     int* p = hqm::tc_error_ptr();
     if (!p) return -1;
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
     if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (v != 0 && cudaMemset(p, 0, sizeof(int)) != cudaSuccess) return -1;
     return v;
 }

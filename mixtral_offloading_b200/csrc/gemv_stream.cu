@@ -42,6 +42,7 @@
 
 #include "common.cuh"
 #include "kernels.cuh"
+#include "stream_split.cuh"
 
 namespace hqm {
 
@@ -134,22 +135,6 @@ template <> struct Fields<4> {
 };
 
 // --------------------------------------------------------------------------- kernel
-// Work split shared by the kernel and the finalize step: passes are numbered
-// L = rho * PT + p (PT passes per residue); warp c of the grid owns [c*Ltot/grid, (c+1)*Ltot/grid).
-// (32-bit arithmetic throughout: the planner rejects layers with total() * grid >= 2^31.)
-struct Split {
-    int P, PT, grid;
-    __host__ __device__ uint32_t total() const { return (uint32_t)P * (uint32_t)PT; }
-    __host__ __device__ uint32_t begin(int c) const { return (uint32_t)c * total() / (uint32_t)grid; }
-    // warp whose range contains pass L
-    __host__ __device__ int owner(uint32_t L) const {
-        int c = (int)(L * (uint32_t)grid / total());
-        while (c + 1 < grid && begin(c + 1) <= L) ++c;
-        while (c > 0 && begin(c) > L) --c;
-        return c;
-    }
-};
-
 // Compile-time shape of an instantiation.
 //   NB   blocks of 16 group members (group_size = 16 * NB)
 //   TOKS rows of x decoded per launch (1, 2, 4, 8, 16)
@@ -167,7 +152,7 @@ struct Shape {
     static constexpr int ROW = 72;                              // 64 columns + padding against bank conflicts
     static constexpr int WARP_HALFS = SUB * (MTOK * PER + PER + 1) * ROW;   // xs rows, z rows, one zero row
     static constexpr int NW = 8;
-    static constexpr int XPASS = 8;                             // longest range (passes) a warp may be given
+    static constexpr int XPASS = (TOKS == 1) ? 16 : 8;          // longest range (passes) a warp may be given
     // Asynchronous-copy ring: per warp DEPTH slots, each one pass of 16-byte cells per lane:
     // per sub-pass 2*NB weight-row cells and 1 cell scale_q | zero_q: the bytes that come from HBM.  The fp16
     // meta of scale/zero (L2 resident) is loaded to registers one pass ahead; x comes from the per-segment
@@ -216,25 +201,30 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// Up to two layers of identical shape share one launch (the expert's w1 and w3): their
-// residues are numbered one after the other and the output columns of layer 1 follow
-// those of layer 0.
+// Up to four layers share one launch (an expert's w1 and w3; the q, k and v projections; both experts
+// of a token): same K, bit width and group size, their N may differ.  Their residues are numbered one
+// after the other (rho0), their output columns follow each other in the partial rows (col0), and each
+// reads its own block of rows of x (xrow).
 // With `table` set the layers are not the descriptors passed by value but entries of a descriptor table in
 // device memory, picked by an index that is itself in device memory (the router's choice): layer l is
-// table[3 * *sel + pick[l]].  w[0] then only carries the common shape.  This keeps the host out of the
+// table[3 * *sel[l] + which[l]].  w[l] then only carries the shape.  This keeps the host out of the
 // loop when all experts are resident.
 struct Layers {
-    hqm_weight w[2];
+    hqm_weight w[STREAM_MAX_LAYERS];
     int count;
+    int rho0[STREAM_MAX_LAYERS + 1];
+    int col0[STREAM_MAX_LAYERS + 1];
+    int G[STREAM_MAX_LAYERS], C[STREAM_MAX_LAYERS];
+    int xrow[STREAM_MAX_LAYERS];
     const hqm_weight* table;
-    const int32_t* sel;
-    int pick[2];
+    const int32_t* sel[STREAM_MAX_LAYERS];
+    int which[STREAM_MAX_LAYERS];
 };
 
 template <int NBITS, int NB, int TOKS>
 __global__ void __launch_bounds__(256, (NB == 1 && TOKS <= 2) ? 2 : 1)
 gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, const int32_t* __restrict__ x_idx,
-                   int M, int m_base, int M_total, Layers ly, int G, int C, int P, Split sp, FieldConsts fc) {
+                   int M, int m_base, int M_total, Layers ly, Split sp, FieldConsts fc) {
     using F = Fields<NBITS>;
     using S = Shape<NBITS, NB, TOKS>;
     constexpr int PER = S::PER, TPT = S::TPT, NT = S::NT, MTOK = S::MTOK, LPS = S::LPS, DK = S::DK, SUB = S::SUB,
@@ -243,8 +233,8 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int K = ly.w[0].K, N = ly.w[0].N, PT = sp.PT;
-    const int N_total = N * ly.count;
+    const int K = ly.w[0].K, PT = sp.PT;
+    const int N_total = ly.col0[ly.count];
     unsigned char* warp_mem = smem_raw + (size_t)wi * S::WARP_BYTES;               // everything is warp-private
     __half* xs_w = reinterpret_cast<__half*>(warp_mem);                             // [SUB][MTOK][PER][ROW]
     __half* zz_w = xs_w + SUB * MTOK * PER * ROW;                                  // [SUB][PER + 1][ROW], last row zero
@@ -276,10 +266,6 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
     const int zrow = (g < PER ? g : PER) * ROW + 16 * t;      // this lane's row of the z tile (row PER is zero)
     const uint32_t olo = ((g & 1) ? F::off_lo(1) : F::off_lo(0)) * 0x00010001u & keep;
     const uint32_t ohi = ((g & 1) ? F::off_hi(1) : F::off_hi(0)) * 0x00010001u & keep;
-    uint32_t qoff[NB];                              // this lane's weight rows, bytes from W_q + rho*K + k0
-#pragma unroll
-    for (int b = 0; b < NB; ++b) qoff[b] = (uint32_t)(16 * b + g) * (uint32_t)P * (uint32_t)K + 16u * t;
-    const uint32_t qoff8 = 8u * (uint32_t)P * (uint32_t)K;
 
     const int gw = blockIdx.x * NW + wi;                                           // this warp in the grid
     const uint32_t L_begin = sp.begin(gw), L_end = sp.begin(gw + 1);
@@ -288,8 +274,16 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
         const int rho_g = (int)(L / (uint32_t)PT), pa = (int)(L - (uint32_t)rho_g * (uint32_t)PT);
         const int pb = min(PT, pa + (int)(L_end - L));
         L += (uint32_t)(pb - pa);
-        const int layer = rho_g / P, rho = rho_g - layer * P;
-        const hqm_weight w = ly.table ? ly.table[3 * ly.sel[0] + ly.pick[layer]] : ly.w[layer];
+        int layer = 0;
+#pragma unroll
+        for (int l = 1; l < STREAM_MAX_LAYERS; ++l) layer += (l < ly.count && rho_g >= ly.rho0[l]) ? 1 : 0;
+        const int rho = rho_g - ly.rho0[layer];
+        const int P = ly.rho0[layer + 1] - ly.rho0[layer], G = ly.G[layer], C = ly.C[layer];
+        const hqm_weight w = ly.table ? ly.table[3 * ly.sel[layer][0] + ly.which[layer]] : ly.w[layer];
+        uint32_t qoff[NB];                          // this lane's weight rows, bytes from W_q + rho*K + k0
+#pragma unroll
+        for (int b = 0; b < NB; ++b) qoff[b] = (uint32_t)(16 * b + g) * (uint32_t)P * (uint32_t)K + 16u * t;
+        const uint32_t qoff8 = 8u * (uint32_t)P * (uint32_t)K;
 
         float acc[NB][NT][PER][4];
         float accc[NT][4];
@@ -485,7 +479,7 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
 #pragma unroll
         for (int m = 0; m < TOKS; ++m) {
             const int mm = (m < M) ? (m_base + m) : m_base;
-            xr[m] = x + (int64_t)(x_idx ? x_idx[mm] : mm) * K;
+            xr[m] = x + ((int64_t)(x_idx ? x_idx[mm] : mm) + ly.xrow[layer]) * K;
         }
         if constexpr (S::STAGE_X) {
             // the segment's columns of x, converted to fp16 once
@@ -529,7 +523,7 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
             const float cb = __shfl_sync(0xffffffffu, mine, (sa + 1) * 4 + t);
             const int m = tau * TPT + (2 * t) / PER;
             if (m < M) {
-                float* dst = partial + ((int64_t)slot_idx * M_total + m_base + m) * N_total + (int64_t)layer * N +
+                float* dst = partial + ((int64_t)slot_idx * M_total + m_base + m) * N_total + ly.col0[layer] +
                              PER * rho + sa;
 #pragma unroll
                 for (int b = 0; b < NB; ++b) {
@@ -554,44 +548,34 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
     }
 }
 
-// Number of partial row-sets that hold a piece of output column n (of N_total = layers * N).
-__device__ __forceinline__ int partial_count(const Split& sp, int n, int N, int G, int per, int P) {
-    const int layer = n / N, nn = n - layer * N;
-    const uint32_t rho_g = (uint32_t)(layer * P + (nn % G) / per);
-    return sp.owner(rho_g * sp.PT + sp.PT - 1) - sp.owner(rho_g * sp.PT) + 1;
-}
-
-// y = bf16( sum of the partials + bias )
+// y = bf16( sum of the partials + bias ); the layers of the launch end up side by side in a row of y
 __global__ void finalize_linear_kernel(uint16_t* __restrict__ y, const float* __restrict__ partial,
-                                       const uint16_t* __restrict__ bias, int64_t MN, int N, int G, int per, int P,
-                                       Split sp) {
+                                       const uint16_t* __restrict__ bias, int64_t M, int row, Split sp, ColMap cm) {
     grid_launch_dependents();
     grid_dependency_wait();
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < MN; i += (int64_t)gridDim.x * blockDim.x) {
-        const int n = (int)(i % N);
-        const int cnt = partial_count(sp, n, N, G, per, P);
-        float v = 0.f;
-        for (int s = 0; s < cnt; ++s) v += partial[s * MN + i];
+    const int64_t MR = M * row;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < MR; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / row;
+        const int n = (int)(i - m * row);
+        float v = partial_sum(partial, sp, cm, m, n, row, MR);
         if (bias) v += bf16_bits_to_float(bias[n]);
         y[i] = float_to_bf16_bits(v);
     }
 }
 
-// h[m, f] = bf16( bf16(silu(bf16(a))) * bf16(b) ) with a / b the summed partials of the
-// w1 / w3 halves of a two-layer launch (columns f and F + f).
+// h[p][m, f] = bf16( bf16(silu(bf16(a))) * bf16(b) ) with a / b the summed partials of layers 2p / 2p + 1
+// of the launch (an expert's w1 and w3), for each of the launch's layer pairs p.
 __global__ void finalize_silu_mul_kernel(uint16_t* __restrict__ h, const float* __restrict__ partial, int64_t M,
-                                         int F, int G, int per, int P, Split sp) {
+                                         int F, int pairs, int row, Split sp, ColMap cm) {
     grid_launch_dependents();
     grid_dependency_wait();
-    const int64_t MF = M * F, M2F = 2 * MF;
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < MF; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t m = i / F;
-        const int f = (int)(i - m * F);
-        const int cnt = partial_count(sp, f, F, G, per, P);      // same split position for both halves? no: count each
-        const int cnt3 = partial_count(sp, F + f, F, G, per, P);
-        float a = 0.f, b = 0.f;
-        for (int s = 0; s < cnt; ++s) a += partial[s * M2F + m * 2 * F + f];
-        for (int s = 0; s < cnt3; ++s) b += partial[s * M2F + m * 2 * F + F + f];
+    const int64_t MF = M * F, total = MF * pairs, MR = M * row;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int p = (int)(i / MF);
+        const int64_t m = (i - p * MF) / F;
+        const int f = (int)(i - p * MF - m * F);
+        float a = partial_sum(partial, sp, cm, m, cm.col0[2 * p] + f, row, MR);
+        float b = partial_sum(partial, sp, cm, m, cm.col0[2 * p + 1] + f, row, MR);
         a = round_bf16(a);
         b = round_bf16(b);
         const float act = round_bf16(a / (1.f + __expf(-a)));
@@ -599,24 +583,27 @@ __global__ void finalize_silu_mul_kernel(uint16_t* __restrict__ h, const float* 
     }
 }
 
-// out[t] = (accumulate ? out[t] : 0) + bf16(w_i * bf16(sum of the partials)), t = token_idx[i]
+// out[t] = (accumulate ? out[t] : 0) + sum over the launch's layers l of bf16(w[l*M + i] * bf16(partial sum of
+// layer l)), added in layer order with a bf16 rounding after each step (as consecutive index_add_ calls do);
+// t = token_idx[i].
 __global__ void finalize_scatter_kernel(uint16_t* __restrict__ out, const float* __restrict__ partial,
                                         const int32_t* __restrict__ token_idx, const float* __restrict__ route_w,
-                                        int64_t M, int H, int G, int per, int P, int accumulate, Split sp) {
+                                        int64_t M, int H, int row, int accumulate, Split sp, ColMap cm) {
     grid_launch_dependents();
     grid_dependency_wait();
-    const int64_t MH = M * H;
+    const int64_t MH = M * H, MR = M * row;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < MH; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t m = i / H;
         const int n = (int)(i - m * H);
-        const int cnt = partial_count(sp, n, H, G, per, P);
-        float v = 0.f;
-        for (int s = 0; s < cnt; ++s) v += partial[s * MH + i];
         const int64_t tk = token_idx ? token_idx[m] : m;
-        const float wgt = route_w ? route_w[m] : 1.f;
-        v = round_bf16(round_bf16(v) * wgt);
         uint16_t* dst = out + tk * H + n;
-        *dst = float_to_bf16_bits(accumulate ? bf16_bits_to_float(*dst) + v : v);
+        float acc = accumulate ? bf16_bits_to_float(*dst) : 0.f;
+        for (int l = 0; l < cm.count; ++l) {
+            const float wgt = route_w ? route_w[l * M + m] : 1.f;
+            const float v = round_bf16(round_bf16(partial_sum(partial, sp, cm, m, cm.col0[l] + n, row, MR)) * wgt);
+            acc = (l == 0 && !accumulate) ? v : round_bf16(acc + v);
+        }
+        *dst = float_to_bf16_bits(acc);
     }
 }
 
@@ -670,7 +657,9 @@ static int dispatch(int nbits, int nb, int toks, Fn&& fn) {
     return -1;
 }
 
-bool gemv_stream_plan(const hqm_weight* w, int layers, int G, int C, int64_t M, StreamPlan* plan) {
+bool gemv_stream_plan(const hqm_weight* const* ws, int count, int64_t M, StreamPlan* plan) {
+    if (count < 1 || count > STREAM_MAX_LAYERS || force_generic()) return false;
+    const hqm_weight* w = ws[0];
     if (w->nbits != 2 && w->nbits != 4) return false;
     const int per = codes_per_word(w->nbits);
     const int dk = w->nbits == 2 ? 8 : 4;
@@ -678,21 +667,35 @@ bool gemv_stream_plan(const hqm_weight* w, int layers, int G, int C, int64_t M, 
     const bool group_ok = (w->nbits == 2) ? (g == 16 || g == 32) : (g == 32 || g == 64);
     const int nb = g / 16;
     const int pw = nb == 1 ? 128 : 64;
-    if (!group_ok || G % per != 0 || w->K % pw != 0 || C % dk != 0) return false;
+    if (!group_ok || w->K % pw != 0) return false;
     if (M < 1 || M > 16) return false;
-    if ((int64_t)G * w->K >= (int64_t)1 << 31 || (int64_t)(w->N / per) * w->K >= (int64_t)1 << 31) return false;
-    if (!aligned16(w->W_q) || !aligned16(w->scale_q) || !aligned16(w->zero_q) || !aligned16(w->ms_scale) ||
-        !aligned16(w->mz_scale) || !aligned16(w->ms_zero) || !aligned16(w->mz_zero))
-        return false;
+    plan->count = count;
+    plan->rho0[0] = 0;
+    plan->col0[0] = 0;
+    for (int l = 0; l < count; ++l) {
+        const hqm_weight* v = ws[l];
+        int G, C;
+        if (check_weight(v, &G, &C) != HQM_OK) return false;
+        if (v->nbits != w->nbits || v->group_size != g || v->K != w->K || v->meta_group != w->meta_group) return false;
+        if (G % per != 0 || C % dk != 0) return false;
+        if ((int64_t)G * v->K >= (int64_t)1 << 31 || (int64_t)(v->N / per) * v->K >= (int64_t)1 << 31) return false;
+        if (!aligned16(v->W_q) || !aligned16(v->scale_q) || !aligned16(v->zero_q) || !aligned16(v->ms_scale) ||
+            !aligned16(v->mz_scale) || !aligned16(v->ms_zero) || !aligned16(v->mz_zero))
+            return false;
+        plan->G[l] = G;
+        plan->C[l] = C;
+        plan->rho0[l + 1] = plan->rho0[l] + G / per;
+        plan->col0[l + 1] = plan->col0[l] + v->N;
+    }
     const int toks = toks_for(w->nbits, nb, (int)M);
     int grid = dispatch(w->nbits, nb, toks, [](auto b, auto k, auto t) {
         return resident_grid<decltype(b)::value, decltype(k)::value, decltype(t)::value>();
     });
     if (grid <= 0) return false;
-    plan->P = G / per;
-    plan->layers = layers;
+    plan->nbits = w->nbits;
+    plan->nb = nb;
     plan->PT = w->K / pw;
-    const int64_t total = (int64_t)plan->P * layers * plan->PT;
+    const int64_t total = (int64_t)plan->rho0[count] * plan->PT;
     // Whole CTAs per SM, so that every SM carries the same load; fewer of them (and, for small layers,
     // fewer SMs) rather than ranges shorter than ~3 passes, each of which costs a partial row-set.
     {
@@ -709,7 +712,7 @@ bool gemv_stream_plan(const hqm_weight* w, int layers, int G, int C, int64_t M, 
     }
     const int64_t warps = (int64_t)grid * 8;
     if (total * warps >= ((int64_t)1 << 31)) return false;
-    if (toks <= 2 && (total + warps - 1) / warps + 1 > 8) return false;   // a range must fit the x staging buffer
+    if (toks <= 2 && (total + warps - 1) / warps + 1 > (toks == 1 ? 16 : 8)) return false;   // the x staging buffer
     plan->grid = grid;
     plan->warps = (int)warps;
     plan->toks = toks;
@@ -718,34 +721,39 @@ bool gemv_stream_plan(const hqm_weight* w, int layers, int G, int C, int64_t M, 
     return true;
 }
 
-size_t gemv_stream_scratch_bytes(const StreamPlan& plan, int64_t M, int N) {
-    return (size_t)plan.slots * (size_t)M * (size_t)N * (size_t)plan.layers * sizeof(float);
+size_t gemv_stream_scratch_bytes(const StreamPlan& plan, int64_t M) {
+    return (size_t)plan.slots * (size_t)M * (size_t)plan.col0[plan.count] * sizeof(float);
 }
 
-int launch_gemv_stream_partials(float* partial, const uint16_t* x, const int32_t* x_idx, int64_t M,
-                                const hqm_weight* w0, const hqm_weight* w1, int G, int C, const StreamPlan& plan,
-                                cudaStream_t st, const ExpertPick* pick) {
-    const int nb = w0->group_size / 16;
-    const Split sp{plan.P * plan.layers, plan.PT, plan.warps};
-    Layers ly;
-    ly.w[0] = *w0;
-    ly.w[1] = w1 ? *w1 : *w0;
-    ly.count = plan.layers;
-    ly.table = pick ? pick->table : nullptr;
-    ly.sel = pick ? pick->sel : nullptr;
-    ly.pick[0] = pick ? pick->which[0] : 0;
-    ly.pick[1] = pick ? pick->which[1] : 0;
+int launch_gemv_stream(float* partial, const uint16_t* x, const int32_t* x_idx, int64_t M, const StreamJob& job,
+                       const StreamPlan& plan, cudaStream_t st) {
+    Layers ly{};
+    ly.count = plan.count;
+    for (int l = 0; l < plan.count; ++l) {
+        ly.w[l] = *job.w[l];
+        ly.G[l] = plan.G[l];
+        ly.C[l] = plan.C[l];
+        ly.rho0[l] = plan.rho0[l];
+        ly.col0[l] = plan.col0[l];
+        ly.xrow[l] = job.xrow[l];
+        ly.sel[l] = job.sel[l];
+        ly.which[l] = job.which[l];
+    }
+    ly.rho0[plan.count] = plan.rho0[plan.count];
+    ly.col0[plan.count] = plan.col0[plan.count];
+    ly.table = job.table;
+    const Split sp = split_of(plan);
     // rows beyond one launch's tokens go in further launches over the same split
     for (int m0 = 0; m0 < (int)M; m0 += plan.toks) {
         const int take = ((int)M - m0 < plan.toks) ? (int)M - m0 : plan.toks;
-        const int rc = dispatch(w0->nbits, nb, plan.toks, [&](auto b, auto k, auto t) {
+        const int rc = dispatch(plan.nbits, plan.nb, plan.toks, [&](auto b, auto k, auto t) {
             constexpr int B = decltype(b)::value, NBK = decltype(k)::value, T = decltype(t)::value;
             launch_overlapped(gemv_stream_kernel<B, NBK, T>, plan.grid, 256, Shape<B, NBK, T>::smem_bytes(), st, partial,
-                              x, x_idx, take, m0, (int)M, ly, G, C, plan.P, sp, field_consts(w0->nbits));
+                              x, x_idx, take, m0, (int)M, ly, sp, field_consts(plan.nbits));
             return 0;
         });
         if (rc != 0) {
-            set_error("gemv_stream: no instantiation for nbits=%d group_size=%d", w0->nbits, w0->group_size);
+            set_error("gemv_stream: no instantiation for nbits=%d group_size=%d", plan.nbits, 16 * plan.nb);
             return HQM_ERR_ARG;
         }
         HQM_LAUNCH_CHECK();
@@ -759,29 +767,28 @@ static inline int blocks_for(int64_t n) {
     return (int)(blocks < 1 ? 1 : blocks);
 }
 
-int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bias, int64_t M, const hqm_weight* w,
-                           int G, const StreamPlan& plan, cudaStream_t st) {
-    const int64_t MN = M * w->N;
-    launch_overlapped(finalize_linear_kernel, blocks_for(MN), 256, 0, st, y, partial, bias, MN, w->N, G,
-                      codes_per_word(w->nbits), plan.P, Split{plan.P * plan.layers, plan.PT, plan.warps});
+int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bias, int64_t M, const StreamPlan& plan,
+                           cudaStream_t st) {
+    const int row = plan.col0[plan.count];
+    launch_overlapped(finalize_linear_kernel, blocks_for(M * row), 256, 0, st, y, partial, bias, M, row, split_of(plan),
+                      colmap_of(plan));
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }
 
-int launch_finalize_silu_mul(uint16_t* h, const float* partial, int64_t M, const hqm_weight* w1, int G,
-                             const StreamPlan& plan, cudaStream_t st) {
-    launch_overlapped(finalize_silu_mul_kernel, blocks_for(M * w1->N), 256, 0, st, h, partial, M, w1->N, G,
-                      codes_per_word(w1->nbits), plan.P, Split{plan.P * plan.layers, plan.PT, plan.warps});
+int launch_finalize_silu_mul(uint16_t* h, const float* partial, int64_t M, const StreamPlan& plan, cudaStream_t st) {
+    const int F = plan.col0[1], pairs = plan.count / 2, row = plan.col0[plan.count];
+    launch_overlapped(finalize_silu_mul_kernel, blocks_for(M * F * pairs), 256, 0, st, h, partial, M, F, pairs, row,
+                      split_of(plan), colmap_of(plan));
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }
 
 int launch_finalize_scatter(uint16_t* out, const float* partial, const int32_t* token_idx, const float* route_w,
-                            int accumulate, int64_t M, const hqm_weight* w2, int G, const StreamPlan& plan,
-                            cudaStream_t st) {
-    launch_overlapped(finalize_scatter_kernel, blocks_for(M * w2->N), 256, 0, st, out, partial, token_idx, route_w, M,
-                      w2->N, G, codes_per_word(w2->nbits), plan.P, accumulate,
-                      Split{plan.P * plan.layers, plan.PT, plan.warps});
+                            int accumulate, int64_t M, const StreamPlan& plan, cudaStream_t st) {
+    const int H = plan.col0[1], row = plan.col0[plan.count];
+    launch_overlapped(finalize_scatter_kernel, blocks_for(M * H), 256, 0, st, out, partial, token_idx, route_w, M, H, row,
+                      accumulate, split_of(plan), colmap_of(plan));
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }

@@ -9,36 +9,47 @@ int launch_linear_generic(uint16_t* y, const uint16_t* x, const int32_t* x_idx, 
                           int C, const uint16_t* bias, cudaStream_t st);
 
 // gemv_stream.cu — the weight-streaming path for small row counts.
+constexpr int STREAM_MAX_LAYERS = 4;
+// What one launch multiplies: up to four layers of the same K, bit width and group size (N may differ).
+// Layer l reads rows x_idx?[m] + xrow[l] of x.  With `table` set, layer l's descriptor is read on the
+// device: table[3 * *sel[l] + which[l]] (3 descriptors per expert: w1, w2, w3), and w[l] only gives the shape.
+struct StreamJob {
+    const hqm_weight* w[STREAM_MAX_LAYERS];
+    int xrow[STREAM_MAX_LAYERS];
+    const hqm_weight* table;
+    const int32_t* sel[STREAM_MAX_LAYERS];
+    int which[STREAM_MAX_LAYERS];
+};
 struct StreamPlan {
-    int P;       // storage-row residues of one layer
-    int layers;  // 1, or 2 when an expert's w1 and w3 share the launch
+    int count;                          // layers in the launch
+    int nbits, nb;                      // bit width, group size / 16
+    int G[STREAM_MAX_LAYERS], C[STREAM_MAX_LAYERS];
+    int rho0[STREAM_MAX_LAYERS + 1];    // first storage-row residue of each layer; [count] = all of them
+    int col0[STREAM_MAX_LAYERS + 1];    // first column of each layer in a partial row; [count] = row length
     int PT;      // passes per residue (K / pass width)
     int grid;    // CTAs of the single-wave persistent grid
     int warps;   // warps of that grid: the units the passes are split over
     int toks;    // rows of x decoded per launch
-    int slots;   // upper bound on the warps contributing to one residue: fp32 partials [slots][M][layers*N]
+    int slots;   // upper bound on the warps contributing to one residue: fp32 partials [slots][M][row length]
 };
-// False when the layer / row count is outside what the streaming kernels cover.
-bool gemv_stream_plan(const hqm_weight* w, int layers, int G, int C, int64_t M, StreamPlan* plan);
-size_t gemv_stream_scratch_bytes(const StreamPlan& plan, int64_t M, int N);
-// Device-side choice of the expert whose layers a streaming launch reads: descriptor table (3 per expert:
-// w1, w2, w3), pointer to the expert index, and which of the three each of the (up to 2) layers is.
-struct ExpertPick {
-    const hqm_weight* table;
-    const int32_t* sel;
-    int which[2];
-};
-int launch_gemv_stream_partials(float* partial, const uint16_t* x, const int32_t* x_idx, int64_t M,
-                                const hqm_weight* w0, const hqm_weight* w1, int G, int C, const StreamPlan& plan,
-                                cudaStream_t st, const ExpertPick* pick = nullptr);
-int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bias, int64_t M, const hqm_weight* w,
-                           int G, const StreamPlan& plan, cudaStream_t st);
-int launch_finalize_silu_mul(uint16_t* h, const float* partial, int64_t M, const hqm_weight* w1, int G,
-                             const StreamPlan& plan, cudaStream_t st);
+// False when the layers / row count are outside what the streaming kernels cover.
+bool gemv_stream_plan(const hqm_weight* const* ws, int count, int64_t M, StreamPlan* plan);
+size_t gemv_stream_scratch_bytes(const StreamPlan& plan, int64_t M);
+int launch_gemv_stream(float* partial, const uint16_t* x, const int32_t* x_idx, int64_t M, const StreamJob& job,
+                       const StreamPlan& plan, cudaStream_t st);
+// y (M, row length) = bf16(sums + bias)
+int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bias, int64_t M, const StreamPlan& plan,
+                           cudaStream_t st);
+// h[p] (M, F) = silu(layer 2p) * layer 2p+1 for each pair of layers of the launch
+int launch_finalize_silu_mul(uint16_t* h, const float* partial, int64_t M, const StreamPlan& plan, cudaStream_t st);
+// out[token_idx[m]] (+)= sum over the launch's layers l of route_w[l * M + m] * layer l
 int launch_finalize_scatter(uint16_t* out, const float* partial, const int32_t* token_idx, const float* route_w,
-                            int accumulate, int64_t M, const hqm_weight* w2, int G, const StreamPlan& plan,
-                            cudaStream_t st);
+                            int accumulate, int64_t M, const StreamPlan& plan, cudaStream_t st);
 bool force_generic();
+
+// router.cu — logits, top-2 indices and weights of M tokens (no per-expert lists).
+int launch_router_top2(uint16_t* router_logits, float* topk_w, int32_t* topk_idx, const uint16_t* x,
+                       const uint16_t* gate_w, int64_t M, int64_t K, int32_t E, cudaStream_t st);
 
 // gemv_stream3.cu — the weight-streaming path for 3-bit layers.
 struct Stream3Plan {

@@ -7,33 +7,66 @@
 
 namespace hqm {
 
-// One warp per token.  EMAX bounds the number of experts held in registers.
+// One CTA per token: the 256 threads split the hidden dimension in 16-byte pieces (8 columns of x
+// against the same 8 columns of every expert's gate row), the E dot products are reduced through
+// shared memory and thread 0 finishes softmax / top-2.  EMAX bounds the experts held in registers.
 template <int EMAX>
 __global__ void __launch_bounds__(256)
 router_logits_top2_kernel(uint16_t* __restrict__ logits_out, float* __restrict__ topk_w, int32_t* __restrict__ topk_idx,
                           const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate_w, int M, int K, int E) {
-    const int lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (t >= M) return;
+    __shared__ float s_part[8][EMAX];
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
+    const int t = blockIdx.x;
     float acc[EMAX];
 #pragma unroll
     for (int e = 0; e < EMAX; ++e) acc[e] = 0.f;
     const uint16_t* xr = x + (int64_t)t * K;
-    for (int k = lane; k < K; k += 32) {
-        const float xv = bf16_bits_to_float(xr[k]);
+    const bool vec = (K % 8 == 0) && ((reinterpret_cast<uintptr_t>(xr) | reinterpret_cast<uintptr_t>(gate_w)) & 15u) == 0;
+    if (vec) {
+        for (int k = 8 * threadIdx.x; k < K; k += 8 * 256) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(xr + k);
+            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-        for (int e = 0; e < EMAX; ++e)
-            if (e < E) acc[e] = fmaf(xv, bf16_bits_to_float(gate_w[(int64_t)e * K + k]), acc[e]);
+            for (int e = 0; e < EMAX; ++e) {
+                if (e < E) {
+                    const uint4 gv = *reinterpret_cast<const uint4*>(gate_w + (int64_t)e * K + k);
+                    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        acc[e] = fmaf(__uint_as_float(xw[j] << 16), __uint_as_float(gw[j] << 16), acc[e]);
+                        acc[e] = fmaf(__uint_as_float(xw[j] & 0xffff0000u), __uint_as_float(gw[j] & 0xffff0000u), acc[e]);
+                    }
+                }
+            }
+        }
+    } else {
+        for (int k = threadIdx.x; k < K; k += 256) {
+            const float xv = bf16_bits_to_float(xr[k]);
+#pragma unroll
+            for (int e = 0; e < EMAX; ++e)
+                if (e < E) acc[e] = fmaf(xv, bf16_bits_to_float(gate_w[(int64_t)e * K + k]), acc[e]);
+        }
     }
+#pragma unroll
+    for (int e = 0; e < EMAX; ++e) {
+        const float v = warp_sum(acc[e]);
+        if (lane == 0) s_part[wi][e] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
     // The gate is a linear layer in the activation dtype: its output is rounded
     // before the fp32 softmax sees it.
     float mx = -INFINITY;
 #pragma unroll
     for (int e = 0; e < EMAX; ++e) {
-        acc[e] = round_bf16(warp_sum(acc[e]));
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) v += s_part[w][e];
+        acc[e] = round_bf16(v);
         if (e < E) mx = fmaxf(mx, acc[e]);
     }
-    if (lane != 0) return;
     float p[EMAX], sum = 0.f;
 #pragma unroll
     for (int e = 0; e < EMAX; ++e) {
@@ -67,6 +100,8 @@ __global__ void router_lists_kernel(int32_t* __restrict__ counts, int32_t* __res
                                     int E) {
     __shared__ int s_count[32];
     __shared__ int s_off[33];
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int lane = threadIdx.x & 31, e = threadIdx.x >> 5;
     int cnt = 0;
     for (int t0 = 0; t0 < M; t0 += 32) {
@@ -108,6 +143,21 @@ __global__ void router_lists_kernel(int32_t* __restrict__ counts, int32_t* __res
 
 }  // namespace hqm
 
+namespace hqm {
+// Logits, top-2 indices and weights only (no per-expert lists): what the single-token MoE block needs.
+int launch_router_top2(uint16_t* router_logits, float* topk_w, int32_t* topk_idx, const uint16_t* x,
+                       const uint16_t* gate_w, int64_t M, int64_t K, int32_t E, cudaStream_t st) {
+    if (E <= 8)
+        launch_overlapped(router_logits_top2_kernel<8>, (int)M, 256, 0, st, router_logits, topk_w, topk_idx, x, gate_w,
+                          (int)M, (int)K, (int)E);
+    else
+        launch_overlapped(router_logits_top2_kernel<32>, (int)M, 256, 0, st, router_logits, topk_w, topk_idx, x, gate_w,
+                          (int)M, (int)K, (int)E);
+    HQM_LAUNCH_CHECK();
+    return HQM_OK;
+}
+}  // namespace hqm
+
 extern "C" int hqm_router_top2(uint16_t* router_logits, float* topk_w, int32_t* topk_idx, int32_t* counts,
                                int32_t* offsets, int32_t* token_idx, float* token_w, const uint16_t* x,
                                const uint16_t* gate_w, int64_t M, int64_t K, int32_t E, void* stream) {
@@ -120,16 +170,11 @@ extern "C" int hqm_router_top2(uint16_t* router_logits, float* topk_w, int32_t* 
     if (M > 0) {
         HQM_CHECK_ARG(router_logits && topk_w && topk_idx && token_idx && token_w && x && gate_w,
                       "router: null pointer");
-        const int blocks = (int)((M + 7) / 8);
-        if (E <= 8)
-            router_logits_top2_kernel<8><<<blocks, 256, 0, st>>>(router_logits, topk_w, topk_idx, x, gate_w, (int)M,
-                                                                  (int)K, E);
-        else
-            router_logits_top2_kernel<32><<<blocks, 256, 0, st>>>(router_logits, topk_w, topk_idx, x, gate_w, (int)M,
-                                                                   (int)K, E);
-        HQM_LAUNCH_CHECK();
+        const int rc = launch_router_top2(router_logits, topk_w, topk_idx, x, gate_w, M, K, E, st);
+        if (rc != HQM_OK) return rc;
     }
-    router_lists_kernel<<<1, 32 * E, 0, st>>>(counts, offsets, token_idx, token_w, topk_w, topk_idx, (int)M, E);
+    launch_overlapped(router_lists_kernel, 1, 32 * E, 0, st, counts, offsets, token_idx, token_w, (const float*)topk_w,
+                      (const int32_t*)topk_idx, (int)M, (int)E);
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }

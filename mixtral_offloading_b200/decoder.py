@@ -1,0 +1,89 @@
+"""The steps either side of the MoE block for single-token decode, as device-side launch sequences.
+
+In the reference these steps are the Hugging Face Mixtral decoder layer (src/build_model.py:166-241
+assembles the model; its q/k/v/o projections are HQQLinearTritonSavable modules,
+src/custom_layers.py:49-92).  AttentionDecode runs them for ONE new token without returning to the
+host: RMSNorm, the three projections in one streaming launch, rotate-half RoPE, the KV-cache append, the
+attention over the cache, the output projection, the residual add and the post-attention RMSNorm
+(hqm_attn_decode).  Together with ResidentMoe a whole decode step is a fixed sequence of launches that a
+CUDA graph can replay.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+from torch import nn
+
+from . import _cabi
+from .custom_layers import HQQLinearTritonSavable, _scratch
+
+
+def _bf16_vec(t: torch.Tensor, n: int) -> torch.Tensor:
+    assert t.is_cuda and t.dtype == torch.bfloat16 and t.numel() == n and t.is_contiguous()
+    return t
+
+
+def add_rmsnorm(h: torch.Tensor, delta, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """h += delta (in place, when delta is given); returns rmsnorm(h) * weight.  h: (1, hidden) bf16."""
+    hidden = h.shape[-1]
+    _bf16_vec(h, hidden), _bf16_vec(weight, hidden)
+    if delta is not None:
+        _bf16_vec(delta, hidden)
+    x = torch.empty_like(h)
+    _cabi.check(_cabi.lib().hqm_add_rmsnorm(_cabi.ptr(h), _cabi.ptr(delta) if delta is not None else None,
+                                            _cabi.ptr(weight), _cabi.ptr(x), hidden, eps, _cabi.stream_ptr(h.device)))
+    return x
+
+
+class AttentionDecode(nn.Module):
+    """Attention half of a decoder layer for one token at a time, with its own KV cache.
+
+    q, k, v, o: HQQLinearTritonSavable.  ln_in / ln_post: the RMSNorm weights in front of the attention and
+    in front of the MoE block (bf16, hidden).  The cache holds `max_len` positions."""
+
+    def __init__(self, q: HQQLinearTritonSavable, k: HQQLinearTritonSavable, v: HQQLinearTritonSavable,
+                 o: HQQLinearTritonSavable, ln_in: torch.Tensor, ln_post: torch.Tensor, n_heads: int, n_kv_heads: int,
+                 head_dim: int, max_len: int, rope_theta: float = 1e6, rms_eps: float = 1e-5):
+        super().__init__()
+        self.q_proj, self.k_proj, self.v_proj, self.o_proj = q, k, v, o
+        self.ln_in, self.ln_post = ln_in, ln_post
+        self.n_heads, self.n_kv_heads, self.head_dim, self.max_len = n_heads, n_kv_heads, head_dim, max_len
+        self.rope_theta, self.rms_eps = rope_theta, rms_eps
+        dev = ln_in.device
+        self.k_cache = torch.zeros((n_kv_heads, max_len, head_dim), dtype=torch.bfloat16, device=dev)
+        self.v_cache = torch.zeros((n_kv_heads, max_len, head_dim), dtype=torch.bfloat16, device=dev)
+        self._layer = None
+
+    def _descriptor(self) -> _cabi.HqmAttnLayer:
+        if self._layer is None:
+            hidden = self.n_heads * self.head_dim
+            self._layer = _cabi.HqmAttnLayer(
+                q=self.q_proj.descriptor(), k=self.k_proj.descriptor(), v=self.v_proj.descriptor(),
+                o=self.o_proj.descriptor(), ln_in=_bf16_vec(self.ln_in, hidden).data_ptr(),
+                ln_post=_bf16_vec(self.ln_post, hidden).data_ptr(), k_cache=self.k_cache.data_ptr(),
+                v_cache=self.v_cache.data_ptr(), n_heads=self.n_heads, n_kv_heads=self.n_kv_heads,
+                head_dim=self.head_dim, max_len=self.max_len, rope_theta=self.rope_theta, rms_eps=self.rms_eps)
+        return self._layer
+
+    @torch.inference_mode()
+    def forward(self, h: torch.Tensor, pos: torch.Tensor, delta=None) -> torch.Tensor:
+        """h: (1, hidden) bf16 residual stream, updated in place (h += delta first when delta is given).
+        pos: int32 tensor of one element on the device, the position of this token.  Returns the
+        post-attention RMSNorm of the updated h: the MoE block's input."""
+        hidden = h.shape[-1]
+        _bf16_vec(h, hidden)
+        assert pos.is_cuda and pos.dtype == torch.int32 and pos.numel() == 1
+        if delta is not None:
+            _bf16_vec(delta, hidden)
+        lib = _cabi.lib()
+        layer = self._descriptor()
+        need = lib.hqm_attn_decode_scratch_bytes(C.byref(layer))
+        if need == 0:
+            raise ValueError(lib.hqm_last_error().decode() or "attention decode: unsupported layer")
+        ws = _scratch(h.device, need)
+        x_out = torch.empty_like(h)
+        _cabi.check(lib.hqm_attn_decode(_cabi.ptr(h), _cabi.ptr(x_out), _cabi.ptr(delta) if delta is not None else None,
+                                        C.byref(layer), _cabi.ptr(pos), _cabi.ptr(ws), ws.numel(),
+                                        _cabi.stream_ptr(h.device)))
+        return x_out

@@ -1,0 +1,160 @@
+"""The single-token attention block (hqm_attn_decode) and the fused residual-add + RMSNorm against a torch
+restatement of the Hugging Face decoder-layer arithmetic on the oracle's dequantised weights."""
+import math
+
+import pytest
+import torch
+
+from mixtral_offloading_b200 import AttentionDecode, add_rmsnorm
+from oracle import hqq_oracle as O
+from tests.helpers import layer_from_oracle, random_layer
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+HD = 128
+
+
+def bf(x):
+    return x.to(torch.bfloat16).float()
+
+
+def rms_ref(h, w, eps):
+    v = h.float()
+    return bf(w.float() * bf(v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)))
+
+
+def rope_ref(t, pos, theta):                       # t: (heads, HD) float holding bf16 values
+    inv = theta ** (-torch.arange(0, HD, 2, dtype=torch.float32) / HD)
+    ang = pos * inv
+    cos, sin = bf(torch.cat([ang.cos(), ang.cos()])), bf(torch.cat([ang.sin(), ang.sin()]))
+    rot = torch.cat([-t[:, HD // 2:], t[:, :HD // 2]], -1)
+    return bf(bf(t * cos) + bf(rot * sin))
+
+
+class RefLayer:
+    """Float restatement of one attention block with its own cache."""
+
+    def __init__(self, ods, ln_in, ln_post, n_heads, n_kv, max_len, theta, eps):
+        self.W = [O.dequantize(od).float() for od in ods]          # q, k, v, o as (N, K)
+        self.ln_in, self.ln_post = ln_in.float(), ln_post.float()
+        self.nh, self.nkv, self.theta, self.eps = n_heads, n_kv, theta, eps
+        self.kc = torch.zeros(n_kv, max_len, HD)
+        self.vc = torch.zeros(n_kv, max_len, HD)
+
+    def step(self, h, pos, delta=None):
+        h = h.float()
+        if delta is not None:
+            h = bf(h + delta.float())
+        x = rms_ref(h, self.ln_in, self.eps)
+        q = bf(x @ self.W[0].t()).view(self.nh, HD)
+        k = bf(x @ self.W[1].t()).view(self.nkv, HD)
+        v = bf(x @ self.W[2].t()).view(self.nkv, HD)
+        q, k = rope_ref(q, pos, self.theta), rope_ref(k, pos, self.theta)
+        self.kc[:, pos], self.vc[:, pos] = k, v
+        grp = self.nh // self.nkv
+        K = self.kc[:, :pos + 1].repeat_interleave(grp, 0)          # (nh, len, HD)
+        V = self.vc[:, :pos + 1].repeat_interleave(grp, 0)
+        p = torch.softmax(torch.einsum("hd,hld->hl", q, K) / math.sqrt(HD), -1)
+        ctx = bf(torch.einsum("hl,hld->hd", p, V)).reshape(1, -1)
+        h = bf(h + bf(ctx @ self.W[3].t()))
+        return h, rms_ref(h, self.ln_post, self.eps)
+
+
+def build(n_heads, n_kv, max_len, seed, theta=1e6, eps=1e-5):
+    hidden = n_heads * HD
+    shapes = [(hidden, hidden), (n_kv * HD, hidden), (n_kv * HD, hidden), (hidden, hidden)]
+    ods = [random_layer(N, K, 4, 64, seed + i, std=0.05) for i, (N, K) in enumerate(shapes)]
+    g = torch.Generator().manual_seed(seed + 99)
+    ln_in = (1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16)
+    ln_post = (1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16)
+    layers = [layer_from_oracle(od, DEV) for od in ods]
+    mod = AttentionDecode(*layers, ln_in.to(DEV), ln_post.to(DEV), n_heads, n_kv, HD, max_len, theta, eps)
+    return mod, RefLayer(ods, ln_in, ln_post, n_heads, n_kv, max_len, theta, eps), hidden
+
+
+def rel(a, b):
+    return float((a.float().cpu() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-9))
+
+
+@pytest.mark.parametrize("n_heads,n_kv", [(4, 2), (8, 8), (8, 1)])
+def test_attention_decode_follows_the_reference_over_several_positions(n_heads, n_kv):
+    mod, ref, hidden = build(n_heads, n_kv, max_len=48, seed=11 * n_heads + n_kv)
+    g = torch.Generator().manual_seed(3)
+    pos = torch.zeros(1, dtype=torch.int32, device=DEV)
+    h_ref = torch.randn(1, hidden, generator=g).to(torch.bfloat16)
+    h = h_ref.clone().to(DEV)
+    for step in range(40):
+        delta = (0.3 * torch.randn(1, hidden, generator=g)).to(torch.bfloat16) if step % 2 else None
+        x = mod(h, pos, None if delta is None else delta.to(DEV))
+        h_ref, x_ref = ref.step(h_ref, step, delta)
+        assert rel(h, h_ref) < 2e-2, step
+        assert rel(x, x_ref) < 2e-2, step
+        h_ref = h.cpu().clone()                      # keep the two residual streams from drifting apart
+        # the cache rows the kernel wrote are what the reference wrote
+        assert rel(mod.k_cache[:, step], ref.kc[:, step]) < 2e-2
+        assert rel(mod.v_cache[:, step], ref.vc[:, step]) < 2e-2
+        ref.kc[:, step], ref.vc[:, step] = mod.k_cache[:, step].float().cpu(), mod.v_cache[:, step].float().cpu()
+        pos += 1
+
+
+def test_attention_decode_full_size_long_context_in_a_graph():
+    """Mixtral shape (32 / 8 heads), 700 cached positions, captured and replayed with an advancing position."""
+    n_heads, n_kv, max_len, ctx_len = 32, 8, 768, 700
+    mod, ref, hidden = build(n_heads, n_kv, max_len, seed=5)
+    g = torch.Generator().manual_seed(8)
+    kc = torch.randn(n_kv, ctx_len, HD, generator=g).to(torch.bfloat16)
+    vc = torch.randn(n_kv, ctx_len, HD, generator=g).to(torch.bfloat16)
+    mod.k_cache[:, :ctx_len], mod.v_cache[:, :ctx_len] = kc.to(DEV), vc.to(DEV)
+    ref.kc[:, :ctx_len], ref.vc[:, :ctx_len] = kc.float(), vc.float()
+    pos = torch.full((1,), ctx_len, dtype=torch.int32, device=DEV)
+    h0 = torch.randn(1, hidden, generator=g).to(torch.bfloat16)
+    h = h0.clone().to(DEV)
+    h_in = h0.clone().to(DEV)
+
+    def step():
+        h.copy_(h_in)
+        x = mod(h, pos)
+        pos.add_(1)
+        return x
+
+    step()                                            # settle allocations
+    pos.fill_(ctx_len)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        x = step()
+    pos.fill_(ctx_len)
+    for i in range(3):
+        graph.replay()
+        torch.cuda.synchronize()
+        h_ref, x_ref = ref.step(h0, ctx_len + i)
+        assert rel(h, h_ref) < 2e-2 and rel(x, x_ref) < 2e-2, i
+        ref.kc[:, ctx_len + i] = mod.k_cache[:, ctx_len + i].float().cpu()
+        ref.vc[:, ctx_len + i] = mod.v_cache[:, ctx_len + i].float().cpu()
+    assert int(pos.item()) == ctx_len + 3
+
+
+def test_position_outside_the_cache_is_reported_not_written():
+    from mixtral_offloading_b200 import _cabi
+    mod, _, hidden = build(4, 2, max_len=8, seed=2)
+    h = torch.randn(1, hidden).to(torch.bfloat16).to(DEV)
+    before = mod.k_cache.clone()
+    mod(h, torch.full((1,), 8, dtype=torch.int32, device=DEV))
+    assert _cabi.lib().hqm_device_error() == 2
+    assert torch.equal(mod.k_cache, before)
+    assert _cabi.lib().hqm_device_error() == 0           # reading the flag cleared it
+
+
+def test_add_rmsnorm():
+    g = torch.Generator().manual_seed(1)
+    for hidden in (512, 4096, 5120):
+        h = torch.randn(1, hidden, generator=g).to(torch.bfloat16)
+        d = torch.randn(1, hidden, generator=g).to(torch.bfloat16)
+        w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16)
+        hd = h.clone().to(DEV)
+        x = add_rmsnorm(hd, d.to(DEV), w.to(DEV), 1e-5)
+        h_ref = bf(h.float() + d.float())
+        assert torch.equal(hd.cpu().float(), h_ref)
+        assert rel(x, rms_ref(h_ref, w, 1e-5)) < 1e-2
+        hd2 = h.clone().to(DEV)
+        x2 = add_rmsnorm(hd2, None, w.to(DEV), 1e-5)
+        assert torch.equal(hd2.cpu(), h) and rel(x2, rms_ref(h, w, 1e-5)) < 1e-2
