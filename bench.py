@@ -1,14 +1,16 @@
 """Benchmark of the quantized-expert hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens M] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload ...]
 
-Workload (BASELINE.json configs[1]): one Mixtral expert FFN, HQQ 2-bit / group 16 with
-8-bit scale and zero in groups of 256 — w1, w3 14336x4096 and w2 4096x14336 quantised from
-bf16 N(0, 0.02^2) weights (seeded), activations bf16 N(0, 1).  A step is one pass of
-y = w2(silu(w1 x) * w3 x) over a batch of M tokens (default 1: decode at batch 1).  Steps
-rotate over a pool of distinct experts larger than L2, so every step streams its weights
-from HBM.  With N GPUs each rank runs its own experts on its own tokens (experts are
-independent; no data-path collective) and the value is the sum over ranks.
+Default workload (BASELINE.json configs[4](b) on one GPU, the configuration the metric "Mixtral-shape decode
+tok/s bs1" is quoted on): a Mixtral-8x7B-shaped decoder, 32 layers, hidden 4096, 32 query / 8 KV heads, 8
+experts per layer of which the router picks 2, attention projections HQQ 4-bit g64, experts 2-bit g16,
+8-bit scale/zero in groups of 256, random-initialised weights, every expert resident in HBM.  A step is one
+greedy decode step at batch 1 on a KV cache of --context positions.  With N GPUs each rank decodes its own
+sequence on its own replica (no data-path collective) and the value is the sum over ranks.
+
+--workload expert is BASELINE.json configs[1] (one expert FFN per step, --tokens rows), --workload moe one
+expert-parallel MoE block per step, --workload offload the ExpertCache with half the experts in host memory.
 
 One JSON line is printed by rank 0; see DESIGN.md for the meaning of each key.
 """
@@ -53,6 +55,11 @@ def measured_peak():
     return 6650.0, "fallback"
 
 
+def decode_workload_name(layers, context):
+    return (f"configs[4](b) on one GPU: Mixtral-8x7B-shaped greedy decode, batch 1, {layers} of 32 layers built, "
+            f"8 experts per layer all resident (2-bit g16), attention 4-bit g64, KV cache of {context} positions")
+
+
 def workload_name(tokens):
     return (f"configs[1]: one Mixtral expert FFN, HQQ 2-bit g16 + 8-bit scale/zero g256 "
             f"(w1,w3 14336x4096; w2 4096x14336), tokens={tokens}")
@@ -94,9 +101,64 @@ def time_cpu_expert(ods, tokens, steps, warmup):
     return (time.perf_counter() - t0) / steps
 
 
+def cpu_decode_dicts():
+    """One layer's quantized tensors (q, k, v, o at 4-bit g64; w1, w2, w3 of one expert at 2-bit g16),
+    quantised on the CPU by the oracle from seeded N(0, 0.02^2) weights."""
+    from oracle import hqq_oracle as O
+    g = torch.Generator().manual_seed(0)
+    attn = [O.quantize((torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16), 4, 64, 256)
+            for N, K in ((4096, HIDDEN), (1024, HIDDEN), (1024, HIDDEN), (HIDDEN, 4096))]
+    return attn, cpu_expert_dicts()
+
+
+def time_cpu_decode(attn_ods, expert_ods, steps, warmup, layers=32, vocab=32000):
+    """Seconds per decoded token of the reference's CPU-runnable path (dequantize() + matmul,
+    custom_layers.py:95-116), extrapolated from a bounded sample: per step ONE layer's quantized linears
+    (q, k, v, o and two experts' FFNs) and the lm_head matmul are timed; a token costs `layers` times the
+    former plus the latter.  Norms, RoPE and the attention core are left out (they favour the CPU figure)."""
+    from oracle import hqq_oracle as O
+    x = torch.randn(1, HIDDEN, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
+    head = (torch.randn(vocab, HIDDEN, generator=torch.Generator().manual_seed(2)) * 0.02).to(torch.bfloat16)
+    t_layer = t_head = 0.0
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        for od in attn_ods:
+            O.reference_cpu_linear(x, od)
+        for _ in range(2):
+            O.reference_cpu_expert(x, *expert_ods)
+        t1 = time.perf_counter()
+        torch.matmul(x.float(), head.float().t())
+        t2 = time.perf_counter()
+        if i >= warmup:
+            t_layer += t1 - t0
+            t_head += t2 - t1
+    return (layers * t_layer + t_head) / steps
+
+
+CPU_DECODE_SAMPLE = ("per step one layer's quantized linears (q, k, v, o and two expert FFNs, dequantize + matmul) "
+                     "and the lm_head matmul; a token = 32 x the layer time + the lm_head time")
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
+        return
+    cores = torch.get_num_threads()
+    if args.workload == "decode":
+        attn_ods, expert_ods = cpu_decode_dicts()
+        sec = time_cpu_decode(attn_ods, expert_ods, args.steps, args.warmup)
+        value = 1.0 / sec
+        sample = f"{args.steps} steps after {args.warmup} warm-up; {CPU_DECODE_SAMPLE}"
+        print(json.dumps({
+            "impl": "reference", "metric": "decode_tokens_per_s_bs1", "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": decode_workload_name(32, args.context), "path": "oracle port of the reference's torch "
+                       "CPU dequantize()+matmul (the reference tree itself does not travel to the GPU box)"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                             "os_cpu_count": os.cpu_count()},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }))
         return
     # One full pass tells how long a step is; if K steps would not fit in ~2 minutes, each step
     # runs an expert with the intermediate size cut by `cut` (bytes and flops are linear in it)
@@ -110,7 +172,6 @@ def run_reference(args):
         ods = cpu_expert_dicts(ffn=FFN // cut)
     sec = time_cpu_expert(ods, args.tokens, args.steps, args.warmup) * cut
     value = args.tokens / sec
-    cores = torch.get_num_threads()
     sample = (f"{args.steps} passes of {args.tokens} token(s) after {args.warmup} warm-up; each pass an expert FFN "
               f"with intermediate size {FFN // cut} (1/{cut} of 14336), time scaled by {cut}")
     print(json.dumps({
@@ -174,7 +235,7 @@ class ClockSampler:
         return out
 
 
-def build_pool(device, n_experts, seed0):
+def build_pool(device, n_experts, seed0, cpu_first=True):
     """Experts built through the package's own constructors from seeded N(0, 0.02^2) weights."""
     from mixtral_offloading_b200 import BaseQuantizeConfig, MixtralExpertWrapper, QuantConfig, make_empty_expert
 
@@ -190,7 +251,7 @@ def build_pool(device, n_experts, seed0):
         for name in ("w1", "w2", "w3"):
             lyr = getattr(expert, name)
             N, K = lyr.meta["shape"]
-            if e == 0:      # expert 0 is the one the CPU baseline also builds: identical values
+            if e == 0 and cpu_first:      # expert 0 is the one the CPU baseline also builds: identical values
                 W = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16).to(device)
             else:
                 W = (torch.randn(N, K, device=device) * 0.02).to(torch.bfloat16)
@@ -298,12 +359,33 @@ def run_decode(args):
     from mixtral_offloading_b200 import (AttentionDecode, BaseQuantizeConfig, HQQLinearTritonSavable, ResidentMoe,
                                          add_rmsnorm)
 
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     L, H, NH, NKV, HD, E, V = args.layers, HIDDEN, 32, 8, 128, 8, 32000
     max_len = args.context + args.steps + args.warmup + 8
     attn_cfg = BaseQuantizeConfig(nbits=4, group_size=64, quant_zero=True, quant_scale=True)
-    torch.manual_seed(0)
+    torch.manual_seed(rank)
 
     class ModelCfg:
         hidden_size, intermediate_size, num_local_experts, num_experts_per_tok, hidden_act = H, FFN, E, 2, "silu"
@@ -320,7 +402,7 @@ def run_decode(args):
         ly = dict(q=qlinear(NH * HD, H), k=qlinear(NKV * HD, H), v=qlinear(NKV * HD, H), o=qlinear(H, NH * HD),
                   ln1=(1 + 0.05 * torch.randn(H, device=dev)).to(torch.bfloat16),
                   ln2=(1 + 0.05 * torch.randn(H, device=dev)).to(torch.bfloat16),
-                  moe=ResidentMoe(ModelCfg, l, gate, build_pool(dev, E, seed0=1000 * l)))
+                  moe=ResidentMoe(ModelCfg, l, gate, build_pool(dev, E, seed0=1000 * l, cpu_first=False)))
         ly["attn"] = AttentionDecode(ly["q"], ly["k"], ly["v"], ly["o"], ly["ln1"], ly["ln2"], NH, NKV, HD, max_len,
                                      rope_theta=1e6, rms_eps=1e-5)
         ly["kc"], ly["vc"] = ly["attn"].k_cache.normal_(0, 1), ly["attn"].v_cache.normal_(0, 1)
@@ -359,10 +441,13 @@ def run_decode(args):
         pos32.add_(1)
         return logits
 
+    trace = []                                   # per layer: (input h, output h, router logits) of the torch-glue step
+
     def step_torch_glue():
         h = embed[tok]
         mask = (positions <= pos).view(1, 1, 1, max_len)
         for ly in layers:
+            h_in = h.clone()
             x = rms(h, ly["ln1"])
             qk = rope(torch.cat([ly["q"](x).view(NH, HD), ly["k"](x).view(NKV, HD)], 0))
             v = ly["v"](x).view(NKV, HD)
@@ -371,19 +456,38 @@ def run_decode(args):
             ctx = F.scaled_dot_product_attention(qk[:NH].view(1, NH, 1, HD), ly["kc"].unsqueeze(0), ly["vc"].unsqueeze(0),
                                                  attn_mask=mask, enable_gqa=True)
             h = h + ly["o"](ctx.view(1, NH * HD))
-            y, _ = ly["moe"](rms(h, ly["ln2"]).view(1, 1, H))
+            y, rl = ly["moe"](rms(h, ly["ln2"]).view(1, 1, H))
             h = h + y.view(1, H)
+            trace.append((h_in, h.clone(), rl.float().clone()))
         logits = torch.matmul(rms(h, ln_f), lm_head.t())
         tok.copy_(logits.argmax(-1))
         pos.add_(1)
         return logits
 
+    def layerwise_check():
+        """Every layer of the library path on the torch-glue step's input of that layer: worst relative
+        difference of the layer outputs over the layers where both routers picked the same two experts
+        (a near-tie in bf16 router logits can legitimately flip), and the number of layers where they did not."""
+        worst, flipped = 0.0, 0
+        for ly, (h_in, h_out, rl) in zip(layers, trace):
+            h = h_in.clone()
+            x = ly["attn"](h, pos32, None)
+            y, rl2 = ly["moe"](x.view(1, 1, H))
+            out = (h + y.view(1, H)).float()
+            if set(rl.view(-1).topk(2).indices.tolist()) != set(rl2.float().view(-1).topk(2).indices.tolist()):
+                flipped += 1
+                continue
+            worst = max(worst, float((out - h_out.float()).abs().max() / h_out.float().abs().max()))
+        return worst, flipped
+
     lib = __import__("mixtral_offloading_b200")._cabi.lib()
     with torch.inference_mode():
         logits_glue = step_torch_glue().float()
         tok.zero_()
+        layer_diff, layers_flipped = layerwise_check()
         logits_lib = step().float()
         logits_diff = float((logits_lib - logits_glue).abs().max() / logits_glue.abs().max())
+        trace.clear()
         for _ in range(3):
             step()
         torch.cuda.synchronize(dev)
@@ -396,19 +500,20 @@ def run_decode(args):
         launches_per_step = lib.hqm_launch_count() - launches0
         for _ in range(args.warmup):
             graph.replay()
-        torch.cuda.synchronize(dev)
-        sampler = ClockSampler(0)
+        barrier()
+        sampler = ClockSampler(local) if rank == 0 else None
         stream = torch.cuda.current_stream(dev)
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record(stream)
         for _ in range(args.steps):
             graph.replay()
         ev1.record(stream)
-        torch.cuda.synchronize(dev)
-        ms = ev0.elapsed_time(ev1) / args.steps
+        barrier()
+        ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
         # end to end: the caller feeds the token from the host and reads the chosen token back, every step
         tok_host = torch.zeros(1, dtype=torch.int64).pin_memory()
         pos32.fill_(args.context)
+        barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(args.steps):
@@ -417,27 +522,75 @@ def run_decode(args):
             tok_host.copy_(tok, non_blocking=True)
             stream.synchronize()
         e1.record(stream)
+        barrier()
+        ms_e2e = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+
+        # the dominant kernel alone: the 2-bit streaming linear (w1 / w3 shape), rotating over layer 0's experts
+        lin_layers = [getattr(w._expert, n) for w in layers[0]["moe"]._experts for n in ("w1", "w3")]
+        x_lin = torch.randn(1, H, device=dev).to(torch.bfloat16)
+        reps = 128
+        for l in lin_layers[:4]:
+            l(x_lin)
         torch.cuda.synchronize(dev)
-        ms_e2e = e0.elapsed_time(e1) / args.steps
-        clocks = sampler.stop()
+        lin_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(lin_graph):
+            for i in range(reps):
+                lin_layers[i % len(lin_layers)](x_lin)
+        lin_graph.replay()
+        barrier()
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record(stream)
+        lin_graph.replay()
+        k1.record(stream)
+        barrier()
+        kernel_ms = k0.elapsed_time(k1) / reps
+        clocks = sampler.stop() if sampler is not None else None
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+    lin_bytes = layer_bytes(FFN, HIDDEN) + 2 * (HIDDEN + FFN)
+    peak, peak_kind = measured_peak()
+    achieved = lin_bytes / (kernel_ms * 1e-3) / 1e9
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        attn_ods = [oracle_dict(layers[0][n]) for n in ("q", "k", "v", "o")]
+        expert_ods = [oracle_dict(getattr(layers[0]["moe"]._experts[0]._expert, n)) for n in ("w1", "w2", "w3")]
+        cpu_steps = 3
+        sec = time_cpu_decode(attn_ods, expert_ods, cpu_steps, 1)
+        cpu = {"value": 1.0 / sec, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+               "sample": f"{cpu_steps} steps after 1 warm-up; {CPU_DECODE_SAMPLE}", "os_cpu_count": os.cpu_count()}
+
     attn_bytes = 2 * layer_bytes(4096, 4096, 4, 64) + 2 * layer_bytes(1024, 4096, 4, 64)
     kv_bytes = 2 * NKV * args.context * HD * 2
     step_bytes = L * (attn_bytes + 2 * EXPERT_BYTES + kv_bytes) + V * H * 2
     scale = 32.0 / L
     print(json.dumps({
-        "metric": "decode_tokens_per_s_bs1", "value": 1e3 / (ms * scale), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"Mixtral-8x7B-shaped greedy decode, batch 1, {L} of 32 layers built, all experts "
-                   f"resident, KV cache of {args.context} positions"
+        "metric": "decode_tokens_per_s_bs1", "value": world * 1e3 / (ms * scale), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": decode_workload_name(L, args.context)
                    + ("" if L == 32 else f"; value scales the measured step time by 32/{L}"),
-                   "l2": "a step touches 5.3 GB of weights at 32 layers",
-                   "logits_max_rel_diff_vs_torch_glue": logits_diff},
-        "hbm_gbs": step_bytes / (ms * 1e-3) / 1e9, "algorithmic_bytes_per_step": step_bytes,
-        "e2e": {"value": 1e3 / (ms_e2e * scale), "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": 8,
+                   "l2": f"a step touches {step_bytes / 1e9:.2f} GB of weights and cache (> 126 MB L2)",
+                   "per_gpu": "own replica, own sequence",
+                   "check_vs_torch_ops_around_the_linears": {
+                       "layer_output_max_rel_diff_same_input": layer_diff, "layers_routed_differently": layers_flipped,
+                       "final_logits_max_rel_diff_free_running": logits_diff}},
+        "hbm_gbs_per_gpu_step": step_bytes / (ms * 1e-3) / 1e9, "algorithmic_bytes_per_step": step_bytes,
+        "hbm_frac_per_gpu_step": step_bytes / (ms * 1e-3) / 1e9 / peak,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "kernel": "quantized linear 14336x4096 2-bit g16 (w1/w3 of layer 0's experts, "
+                     f"354 MB rotated), {reps} launches, CUDA events", "algorithmic_bytes": lin_bytes,
+                     "us_per_launch": kernel_ms * 1e3, "peak_kind": f"{peak_kind} HBM copy bandwidth",
+                     "frac_of_8tbs": achieved / 8000.0},
+        "cpu_baseline": cpu,
+        "e2e": {"value": world * 1e3 / (ms_e2e * scale), "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": 8,
                 "d2h_bytes_per_step": 8},
         "gpu_launches": int(launches_per_step * args.steps), "clocks": clocks,
     }))
+    if dist is not None:
+        dist.destroy_process_group()
 
 
 def run_offload(args):
@@ -697,17 +850,21 @@ def main():
     ap.add_argument("--tokens", type=int, default=1)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--layers", type=int, default=8, help="layers built by the offload / decode workloads")
+    ap.add_argument("--layers", type=int, default=None,
+                    help="layers built by the decode (default 32) / offload (default 8) workloads")
     ap.add_argument("--context", type=int, default=512, help="KV-cache positions before the first decoded token")
-    ap.add_argument("--workload", default="expert", choices=["expert", "moe", "offload", "decode"],
-                    help="expert: one expert FFN per step (the default, BASELINE configs[1]); moe: one MoE block "
-                         "per step, expert-parallel over the ranks")
+    ap.add_argument("--workload", default="decode", choices=["decode", "expert", "moe", "offload"],
+                    help="decode: one greedy decode step of the Mixtral-shaped model (the default, BASELINE "
+                         "configs[4](b)); expert: one expert FFN per step (configs[1]); moe: one MoE block per step, "
+                         "expert-parallel over the ranks; offload: ExpertCache with half the experts in host memory")
     ap.add_argument("--combine", default="all_reduce", choices=["all_reduce", "all_to_all"])
     ap.add_argument("--layer", default="14336x4096:2:16", help="NxK:nbits:group for --profile-linear")
     ap.add_argument("--profile-linear", type=int, default=0, metavar="N",
                     help="only launch N quantized linears (w1 shape, rotating over 6 layers > L2) and exit; "
                          "the small case meant to be run under ncu")
     args = ap.parse_args()
+    if args.layers is None:
+        args.layers = 32 if args.workload == "decode" else 8
     if args.impl == "reference":
         args.steps = 3 if args.steps is None else args.steps
         args.warmup = 1 if args.warmup is None else args.warmup

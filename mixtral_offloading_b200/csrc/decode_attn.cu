@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(64) finalize_qkv_rope_kernel(uint16_t* __restr
 }
 
 // A cluster of ATTN_SPLIT CTAs per query head, 8 warps each; the cached positions are dealt round-robin to
-// the cluster's 8 * ATTN_SPLIT warps, four at a time per warp: lane l holds 4 of the 128 dimensions, a
+// the cluster's 8 * ATTN_SPLIT warps, eight at a time per warp: lane l holds 4 of the 128 dimensions, a
 // score is a warp reduction, the running (max, sum, weighted V) are kept per warp, merged per CTA in shared
 // memory, and the CTAs' results are merged by the cluster's first CTA through distributed shared memory.
 constexpr int ATTN_SPLIT = 4;
@@ -192,11 +192,12 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(uint16_t* __restrict__
     }
     constexpr int WARPS = 8 * ATTN_SPLIT;               // warps sharing the head
     float m = -INFINITY, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int j0 = part * 8 + wi; j0 < len; j0 += 4 * WARPS) {
-        float s[4];
-        uint2 vv[4];
+    constexpr int U = 8;                                // positions per warp and iteration
+    for (int j0 = part * 8 + wi; j0 < len; j0 += U * WARPS) {
+        float s[U];
+        uint2 vv[U];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < U; ++u) {
             const int j = j0 + WARPS * u;
             const bool ok = j < len;
             const uint2 kv = ok ? *reinterpret_cast<const uint2*>(K + (int64_t)j * HEAD_DIM) : make_uint2(0u, 0u);
@@ -207,18 +208,18 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(uint16_t* __restrict__
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
+            for (int u = 0; u < U; ++u) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
         }
         float m_new = m;
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < U; ++u)
             if (j0 + WARPS * u < len) m_new = fmaxf(m_new, s[u]);
         const float corr = __expf(m - m_new);           // 0 on the first chunk (m = -inf)
         l *= corr;
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[c] *= corr;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < U; ++u) {
             if (j0 + WARPS * u < len) {
                 const float p = __expf(s[u] - m_new);
                 l += p;

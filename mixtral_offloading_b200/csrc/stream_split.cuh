@@ -41,18 +41,17 @@ __device__ __forceinline__ int partial_count(const Split& sp, const ColMap& cm, 
 }
 
 // Sum of the partial row-sets of element (m, col); `row` is the row length, MR = rows * row.  The row-sets
-// are read four at a time (independent loads in flight together) and added in a fixed order.
+// are read eight at a time (independent loads in flight together) and added in a fixed order.
 __device__ __forceinline__ float partial_sum(const float* __restrict__ partial, const Split& sp, const ColMap& cm,
                                              int64_t m, int col, int row, int64_t MR) {
     const int cnt = partial_count(sp, cm, col);
     const float* p = partial + m * row + col;
     float v = 0.f;
-    for (int s = 0; s < cnt; s += 4) {
-        const float a0 = p[(int64_t)s * MR];
-        const float a1 = (s + 1 < cnt) ? p[(int64_t)(s + 1) * MR] : 0.f;
-        const float a2 = (s + 2 < cnt) ? p[(int64_t)(s + 2) * MR] : 0.f;
-        const float a3 = (s + 3 < cnt) ? p[(int64_t)(s + 3) * MR] : 0.f;
-        v += (a0 + a1) + (a2 + a3);
+    for (int s = 0; s < cnt; s += 8) {
+        float a[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = (s + j < cnt) ? p[(int64_t)(s + j) * MR] : 0.f;
+        v += ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
     }
     return v;
 }
