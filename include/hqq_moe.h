@@ -183,6 +183,27 @@ typedef struct {
 size_t hqm_attn_decode_scratch_bytes(const hqm_attn_layer* layer);
 int hqm_attn_decode(uint16_t* h, uint16_t* x_out, const uint16_t* delta, const hqm_attn_layer* layer,
                     const int32_t* pos, void* scratch, size_t scratch_bytes, void* stream);
+/* A whole decoder layer for one token, attention half and MoE block (hqm_attn_decode then hqm_moe_decode with
+ * the residual adds and norms between them), as 8 launches: the steps between the quantized projections are
+ * folded into their neighbours (RoPE / cache append into the attention kernel, the router into the
+ * post-attention norm, the experts' weighted sum and the NEXT layer's input norm into one kernel).
+ *   x   (hidden) bf16, in: rmsnorm(h) * this layer's input_layernorm weight (hqm_add_rmsnorm gives the first
+ *       layer's); out: rmsnorm(updated h) * next_ln, i.e. the next layer's x (next_ln = the next layer's
+ *       input_layernorm weight, or the model's final norm weight after the last layer).
+ *   h   (hidden) bf16 residual stream, updated in place by both halves.
+ *   router_logits (1, n_experts) bf16 out.  attn.ln_in is not used (x arrives normalised).
+ *   table: 3 * n_experts descriptors in DEVICE memory as for hqm_moe_decode; w1 / w2 / w3 give the shapes. */
+typedef struct {
+    hqm_attn_layer attn;
+    const uint16_t* gate_w;   /* bf16 (n_experts, hidden) */
+    const hqm_weight* table;
+    hqm_weight w1, w2, w3;
+    const uint16_t* next_ln;  /* bf16 (hidden) */
+    int32_t n_experts, reserved;
+} hqm_decoder_layer;
+size_t hqm_decode_layer_scratch_bytes(const hqm_decoder_layer* layer);
+int hqm_decode_layer(uint16_t* h, uint16_t* x, uint16_t* router_logits, const hqm_decoder_layer* layer,
+                     const int32_t* pos, void* scratch, size_t scratch_bytes, void* stream);
 /* h = bf16(h + delta) when delta is given; x_out = bf16(weight * bf16(h * rsqrt(mean(h^2) + eps))): the RMSNorm
  * of the Hugging Face decoder with the preceding residual add (used for the last layer's output and the final norm). */
 int hqm_add_rmsnorm(uint16_t* h, const uint16_t* delta, const uint16_t* weight, uint16_t* x_out, int32_t hidden,

@@ -36,6 +36,15 @@ class HqmAttnLayer(C.Structure):
     ]
 
 
+class HqmDecoderLayer(C.Structure):
+    """struct hqm_decoder_layer."""
+    _fields_ = [
+        ("attn", HqmAttnLayer), ("gate_w", C.c_void_p), ("table", C.c_void_p),
+        ("w1", HqmWeight), ("w2", HqmWeight), ("w3", HqmWeight), ("next_ln", C.c_void_p),
+        ("n_experts", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
 _P = C.c_void_p
 _I64 = C.c_int64
 _I32 = C.c_int32
@@ -65,6 +74,8 @@ SIGNATURES = {
     "hqm_moe_decode": (C.c_int, [_P, _P, _P, _P, _I32, _P, _WP, _WP, _WP, _P, C.c_size_t, _P]),
     "hqm_attn_decode_scratch_bytes": (C.c_size_t, [C.POINTER(HqmAttnLayer)]),
     "hqm_attn_decode": (C.c_int, [_P, _P, _P, C.POINTER(HqmAttnLayer), _P, _P, C.c_size_t, _P]),
+    "hqm_decode_layer_scratch_bytes": (C.c_size_t, [C.POINTER(HqmDecoderLayer)]),
+    "hqm_decode_layer": (C.c_int, [_P, _P, _P, C.POINTER(HqmDecoderLayer), _P, _P, C.c_size_t, _P]),
     "hqm_add_rmsnorm": (C.c_int, [_P, _P, _P, _P, _I32, C.c_float, _P]),
     "hqm_router_top2": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),
     "hqm_cache_create": (C.c_int, [C.POINTER(_P), _I32, _I32, _I32, C.c_size_t, C.POINTER(_P), _I32]),

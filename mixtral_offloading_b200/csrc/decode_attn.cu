@@ -120,6 +120,138 @@ __global__ void __launch_bounds__(NORM_THREADS) finalize_add_rmsnorm_kernel(uint
     }
 }
 
+// finalize_add_rmsnorm_kernel followed by the top-2 router on its result, in one launch: every thread multiplies
+// the x values it holds with the E gate rows, the E dot products are reduced over the cluster like the sum of
+// squares, and the first CTA finishes softmax / top-2 exactly as router_logits_top2_kernel does.  E <= 8.
+constexpr int ROUTER_EMAX = 8;
+__global__ void __launch_bounds__(NORM_THREADS) finalize_add_rmsnorm_router_kernel(
+    uint16_t* __restrict__ h, const float* __restrict__ partial, const uint16_t* __restrict__ w, uint16_t* __restrict__ x,
+    int H, float eps, Split sp, ColMap cm, const uint16_t* __restrict__ gate_w, int E, uint16_t* __restrict__ logits_out,
+    float* __restrict__ topk_w, int32_t* __restrict__ topk_idx) {
+    __shared__ float red[32];
+    __shared__ float mine;
+    __shared__ float s_part[NORM_THREADS / 32][ROUTER_EMAX];
+    __shared__ float s_cta[ROUTER_EMAX];
+    cg::cluster_group cluster = cg::this_cluster();
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int stride = NORM_CTAS * NORM_THREADS, first = blockIdx.x * NORM_THREADS + threadIdx.x;
+    const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
+    float v[NORM_PER_THREAD];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NORM_PER_THREAD; ++j) {
+        const int i = first + j * stride;
+        v[j] = 0.f;
+        if (i < H) {
+            const float y = round_bf16(partial_sum(partial, sp, cm, 0, i, H, H));
+            v[j] = round_bf16(bf16_bits_to_float(h[i]) + y);
+            h[i] = float_to_bf16_bits(v[j]);
+        }
+        ss += v[j] * v[j];
+    }
+    const float rstd = rsqrtf(cluster_sum(ss, red, &mine) / (float)H + eps);
+    float acc[ROUTER_EMAX];
+#pragma unroll
+    for (int e = 0; e < ROUTER_EMAX; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int j = 0; j < NORM_PER_THREAD; ++j) {
+        const int i = first + j * stride;
+        if (i < H) {
+            const uint16_t xb = float_to_bf16_bits(bf16_bits_to_float(w[i]) * round_bf16(v[j] * rstd));
+            x[i] = xb;
+            const float xv = bf16_bits_to_float(xb);
+#pragma unroll
+            for (int e = 0; e < ROUTER_EMAX; ++e)
+                if (e < E) acc[e] = fmaf(xv, bf16_bits_to_float(gate_w[(int64_t)e * H + i]), acc[e]);
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < ROUTER_EMAX; ++e) {
+        const float t = warp_sum(acc[e]);
+        if (lane == 0) s_part[wi][e] = t;
+    }
+    __syncthreads();
+    if (threadIdx.x < ROUTER_EMAX) {
+        float t = 0.f;
+#pragma unroll
+        for (int q = 0; q < NORM_THREADS / 32; ++q) t += s_part[q][threadIdx.x];
+        s_cta[threadIdx.x] = t;
+    }
+    cluster.sync();
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < ROUTER_EMAX; ++e) {
+            float t = 0.f;
+#pragma unroll
+            for (int r = 0; r < NORM_CTAS; ++r) t += cluster.map_shared_rank(s_cta, r)[e];
+            acc[e] = round_bf16(t);                     // the gate's output in the activation dtype
+            if (e < E) mx = fmaxf(mx, acc[e]);
+        }
+        float p[ROUTER_EMAX], sum = 0.f;
+#pragma unroll
+        for (int e = 0; e < ROUTER_EMAX; ++e) {
+            p[e] = (e < E) ? expf(acc[e] - mx) : 0.f;
+            sum += p[e];
+        }
+        int i0 = 0, i1 = -1;
+        float p0 = -1.f, p1 = -1.f;
+#pragma unroll
+        for (int e = 0; e < ROUTER_EMAX; ++e) {
+            if (e < E) {
+                const float pe = p[e] / sum;
+                logits_out[e] = float_to_bf16_bits(acc[e]);
+                if (pe > p0) { p1 = p0; i1 = i0; p0 = pe; i0 = e; }
+                else if (pe > p1) { p1 = pe; i1 = e; }
+            }
+        }
+        if (i1 < 0) { i1 = i0; p1 = 0.f; }
+        const float norm = p0 + p1;
+        topk_w[0] = round_bf16(p0 / norm);
+        topk_w[1] = round_bf16(p1 / norm);
+        topk_idx[0] = i0;
+        topk_idx[1] = i1;
+    }
+    cluster.sync();
+}
+
+// The end of the MoE block and the start of the next layer in one launch: y = sum over the launch's layers l of
+// bf16(route_w[l] * bf16(partial sums of layer l)) (bf16 rounding after each add, as finalize_scatter_kernel),
+// h = bf16(h + y), x = rmsnorm(h) * w.
+__global__ void __launch_bounds__(NORM_THREADS) finalize_scatter_add_rmsnorm_kernel(
+    uint16_t* __restrict__ h, const float* __restrict__ partial, const float* __restrict__ route_w,
+    const uint16_t* __restrict__ w, uint16_t* __restrict__ x, int H, int row, float eps, Split sp, ColMap cm) {
+    __shared__ float red[32];
+    __shared__ float mine;
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int stride = NORM_CTAS * NORM_THREADS, first = blockIdx.x * NORM_THREADS + threadIdx.x;
+    float v[NORM_PER_THREAD];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NORM_PER_THREAD; ++j) {
+        const int i = first + j * stride;
+        v[j] = 0.f;
+        if (i < H) {
+            float y = 0.f;
+            for (int l = 0; l < cm.count; ++l) {
+                const float t = round_bf16(round_bf16(partial_sum(partial, sp, cm, 0, cm.col0[l] + i, row, row)) * route_w[l]);
+                y = (l == 0) ? t : round_bf16(y + t);
+            }
+            v[j] = round_bf16(bf16_bits_to_float(h[i]) + y);
+            h[i] = float_to_bf16_bits(v[j]);
+        }
+        ss += v[j] * v[j];
+    }
+    const float rstd = rsqrtf(cluster_sum(ss, red, &mine) / (float)H + eps);
+#pragma unroll
+    for (int j = 0; j < NORM_PER_THREAD; ++j) {
+        const int i = first + j * stride;
+        if (i < H) x[i] = float_to_bf16_bits(bf16_bits_to_float(w[i]) * round_bf16(v[j] * rstd));
+    }
+}
+
 // One CTA of 64 threads per head of the [q | k | v] partial row: sums the partials, rounds to bf16 (the
 // projection's output), rotates q and k by the position's angles and writes q to `qbuf`, k and v to the
 // caches at `pos`.  A position outside the cache sets the error flag and writes nothing.
@@ -162,12 +294,39 @@ __global__ void __launch_bounds__(64) finalize_qkv_rope_kernel(uint16_t* __restr
 // the cluster's 8 * ATTN_SPLIT warps, eight at a time per warp: lane l holds 4 of the 128 dimensions, a
 // score is a warp reduction, the running (max, sum, weighted V) are kept per warp, merged per CTA in shared
 // memory, and the CTAs' results are merged by the cluster's first CTA through distributed shared memory.
+//
+// FUSED = true folds the step in front into the kernel (one launch less per layer): every CTA sums the
+// projection partials of its head's q and of its key/value head's new k and v itself, rotates q and k, keeps
+// them in shared memory, and attends to the cached positions 0..pos-1 plus the new position from shared
+// memory; one CTA per key/value head also appends k and v to the cache.
 constexpr int ATTN_SPLIT = 4;
 
+struct QkvSource {                 // FUSED only: where q, k, v of this token come from
+    const float* partial;
+    int n_heads, n_kv, row;
+    float theta;
+    Split sp;
+    ColMap cm;
+    int* error_flag;
+};
+
+// rotate-half RoPE of the pair (a, b) = (t[d], t[d + 64]) at position pos, bf16 arithmetic as Hugging Face does it
+__device__ __forceinline__ void rope_pair(float a, float b, int d, int pos, float theta, float& o0, float& o1) {
+    const float inv_freq = powf(theta, -(float)(2 * d) / (float)HEAD_DIM);
+    float sn, cs;
+    sincosf((float)pos * inv_freq, &sn, &cs);
+    sn = round_bf16(sn);
+    cs = round_bf16(cs);
+    o0 = round_bf16(round_bf16(a * cs) + round_bf16(-b * sn));
+    o1 = round_bf16(round_bf16(b * cs) + round_bf16(a * sn));
+}
+
+template <bool FUSED>
 __global__ void __launch_bounds__(256) attn_decode_kernel(uint16_t* __restrict__ ctx, const uint16_t* __restrict__ qbuf,
-                                                          const uint16_t* __restrict__ k_cache,
-                                                          const uint16_t* __restrict__ v_cache,
-                                                          const int32_t* __restrict__ pos_ptr, int group, int max_len) {
+                                                          uint16_t* __restrict__ k_cache, uint16_t* __restrict__ v_cache,
+                                                          const int32_t* __restrict__ pos_ptr, int group, int max_len,
+                                                          QkvSource src) {
+    __shared__ float s_q[HEAD_DIM], s_kn[HEAD_DIM], s_vn[HEAD_DIM];
     __shared__ float s_m[8], s_l[8];
     __shared__ float s_acc[8][HEAD_DIM];
     __shared__ float c_m, c_l;                          // this CTA's merged state, read by the cluster's first CTA
@@ -177,19 +336,46 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(uint16_t* __restrict__
     grid_dependency_wait();
     const int head = blockIdx.x / ATTN_SPLIT, part = blockIdx.x % ATTN_SPLIT;
     const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
-    const int len = min(max(pos_ptr[0] + 1, 0), max_len);
+    const int pos = pos_ptr[0];
     const int kvh = head / group;
-    const uint16_t* K = k_cache + (int64_t)kvh * max_len * HEAD_DIM + 4 * lane;
-    const uint16_t* V = v_cache + (int64_t)kvh * max_len * HEAD_DIM + 4 * lane;
     const float scale = rsqrtf((float)HEAD_DIM);
+    int len;                                            // positions read from the cache
+    bool fresh = false;                                 // the new position is attended to from shared memory
     float q[4];
-    {
+    if constexpr (FUSED) {
+        const bool pos_ok = pos >= 0 && pos < max_len;
+        if (!pos_ok && blockIdx.x == 0 && threadIdx.x == 0 && src.error_flag) atomicExch(src.error_flag, 2);
+        const int which = threadIdx.x >> 6, d = threadIdx.x & 63;     // 0: q, 1: k, 2: v;  pair (d, d + 64)
+        if (which < 3) {
+            const int col = (which == 0 ? head : (which == 1 ? src.n_heads + kvh : src.n_heads + src.n_kv + kvh)) * HEAD_DIM + d;
+            const float a = round_bf16(partial_sum(src.partial, src.sp, src.cm, 0, col, src.row, src.row));
+            const float b = round_bf16(partial_sum(src.partial, src.sp, src.cm, 0, col + HEAD_DIM / 2, src.row, src.row));
+            float o0 = a, o1 = b;
+            if (which < 2) rope_pair(a, b, d, pos, src.theta, o0, o1);
+            float* dst = which == 0 ? s_q : (which == 1 ? s_kn : s_vn);
+            dst[d] = o0;
+            dst[d + HEAD_DIM / 2] = o1;
+            if (which > 0 && pos_ok && part == 0 && head % group == 0) {     // one CTA per key/value head appends
+                uint16_t* row = (which == 1 ? k_cache : v_cache) + ((int64_t)kvh * max_len + pos) * HEAD_DIM;
+                row[d] = float_to_bf16_bits(o0);
+                row[d + HEAD_DIM / 2] = float_to_bf16_bits(o1);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) q[c] = s_q[4 * lane + c] * scale;
+        len = min(max(pos, 0), max_len);
+        fresh = pos_ok && part == 0 && wi == 0;
+    } else {
+        len = min(max(pos + 1, 0), max_len);
         const uint2 qv = *reinterpret_cast<const uint2*>(qbuf + head * HEAD_DIM + 4 * lane);
         q[0] = __uint_as_float(qv.x << 16) * scale;
         q[1] = __uint_as_float(qv.x & 0xffff0000u) * scale;
         q[2] = __uint_as_float(qv.y << 16) * scale;
         q[3] = __uint_as_float(qv.y & 0xffff0000u) * scale;
     }
+    const uint16_t* K = k_cache + (int64_t)kvh * max_len * HEAD_DIM + 4 * lane;
+    const uint16_t* V = v_cache + (int64_t)kvh * max_len * HEAD_DIM + 4 * lane;
     constexpr int WARPS = 8 * ATTN_SPLIT;               // warps sharing the head
     float m = -INFINITY, l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
     constexpr int U = 8;                                // positions per warp and iteration
@@ -229,6 +415,16 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(uint16_t* __restrict__
                 acc[3] += p * __uint_as_float(vv[u].y & 0xffff0000u);
             }
         }
+        m = m_new;
+    }
+    if (fresh) {                                        // the new token's own key and value
+        float sc = q[0] * s_kn[4 * lane] + q[1] * s_kn[4 * lane + 1] + q[2] * s_kn[4 * lane + 2] + q[3] * s_kn[4 * lane + 3];
+        sc = warp_sum(sc);
+        const float m_new = fmaxf(m, sc);
+        const float corr = __expf(m - m_new), p = __expf(sc - m_new);
+        l = l * corr + p;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[c] = acc[c] * corr + p * s_vn[4 * lane + c];
         m = m_new;
     }
     if (lane == 0) {
@@ -364,15 +560,119 @@ int hqm_attn_decode(uint16_t* h, uint16_t* x_out, const uint16_t* delta, const h
                       (const float*)qkv_part, pos, (int)L->n_heads, (int)L->n_kv_heads, (int)L->max_len, L->rope_theta,
                       ap.qkv.col0[3], split_of(ap.qkv), colmap_of(ap.qkv), tc_error_ptr());
     HQM_LAUNCH_CHECK();
-    launch_overlapped_cluster(attn_decode_kernel, (int)L->n_heads * ATTN_SPLIT, 256, 0, ATTN_SPLIT, st, ctx, (const uint16_t*)qbuf,
-                      (const uint16_t*)L->k_cache, (const uint16_t*)L->v_cache, pos, (int)(L->n_heads / L->n_kv_heads),
-                      (int)L->max_len);
+    launch_overlapped_cluster(attn_decode_kernel<false>, (int)L->n_heads * ATTN_SPLIT, 256, 0, ATTN_SPLIT, st, ctx,
+                              (const uint16_t*)qbuf, L->k_cache, L->v_cache, pos, (int)(L->n_heads / L->n_kv_heads),
+                              (int)L->max_len, QkvSource{});
     HQM_LAUNCH_CHECK();
     rc = launch_gemv_stream(o_part, ctx, nullptr, 1, oj, ap.o, st);
     if (rc != HQM_OK) return rc;
     launch_overlapped_cluster(finalize_add_rmsnorm_kernel, NORM_CTAS, NORM_THREADS, 0, NORM_CTAS, st, h,
                               (const float*)o_part, L->ln_post, x_out, hidden, L->rms_eps, split_of(ap.o),
                               colmap_of(ap.o));
+    HQM_LAUNCH_CHECK();
+    return HQM_OK;
+}
+
+// ---- a whole decoder layer for one token: 8 launches -------------------------------------------------
+static int decoder_layer_plan(const hqm_decoder_layer* L, hqm::AttnPlan* ap, hqm::MoeDecodePlan* mp) {
+    using namespace hqm;
+    HQM_CHECK_ARG(L != nullptr, "decode_layer: null layer");
+    int rc = attn_plan(&L->attn, ap);
+    if (rc != HQM_OK) return rc;
+    HQM_CHECK_ARG(L->gate_w && L->table && L->next_ln, "decode_layer: null tensor");
+    HQM_CHECK_ARG(L->n_experts >= 2 && L->n_experts <= ROUTER_EMAX, "decode_layer: %d experts not supported (2..%d)",
+                  L->n_experts, ROUTER_EMAX);
+    HQM_CHECK_ARG(L->w1.K == L->attn.q.K && L->w2.N == L->attn.q.K, "decode_layer: expert shapes do not fit the hidden size");
+    HQM_CHECK_ARG(moe_decode_plan(L->n_experts, &L->w1, &L->w2, &L->w3, mp),
+                  "decode_layer: these expert shapes are outside the streaming path");
+    return HQM_OK;
+}
+
+size_t hqm_decode_layer_scratch_bytes(const hqm_decoder_layer* L) {
+    hqm::AttnPlan ap;
+    hqm::MoeDecodePlan mp;
+    if (decoder_layer_plan(L, &ap, &mp) != HQM_OK) return 0;
+    return ap.total() + mp.router_bytes + mp.up_bytes + mp.h_bytes + mp.down_bytes;
+}
+
+int hqm_decode_layer(uint16_t* h, uint16_t* x, uint16_t* router_logits, const hqm_decoder_layer* L, const int32_t* pos,
+                     void* scratch, size_t scratch_bytes, void* stream) {
+    using namespace hqm;
+    HQM_CHECK_ARG(h && x && router_logits && pos, "decode_layer: null pointer");
+    HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(x) & 15u) == 0, "decode_layer: x must be 16-byte aligned");
+    AttnPlan ap;
+    MoeDecodePlan mp;
+    int rc = decoder_layer_plan(L, &ap, &mp);
+    if (rc != HQM_OK) return rc;
+    const size_t need = ap.total() + mp.router_bytes + mp.up_bytes + mp.h_bytes + mp.down_bytes;
+    if (scratch == nullptr || scratch_bytes < need) {
+        set_error("decode_layer: scratch of %zu bytes given, %zu needed", scratch_bytes, need);
+        return HQM_ERR_SCRATCH;
+    }
+    HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "decode_layer: scratch must be 256-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    const hqm_attn_layer* A = &L->attn;
+    const int hidden = A->q.K, E = L->n_experts;
+    uint8_t* p = (uint8_t*)scratch;
+    uint16_t* x2 = (uint16_t*)p;                                   // the MoE block's input
+    float* qkv_part = (float*)(p + ap.x_bytes);
+    uint16_t* ctx = (uint16_t*)(p + ap.x_bytes + ap.qkv_bytes + ap.q_bytes);
+    float* o_part = (float*)(p + ap.x_bytes + ap.qkv_bytes + ap.q_bytes + ap.ctx_bytes);
+    uint8_t* m0 = p + ap.total();
+    float* topk_w = (float*)m0;                                    // [2] (+2 pad)
+    int32_t* topk_idx = (int32_t*)(topk_w + 4);                    // [2]
+    float* up = (float*)(m0 + mp.router_bytes);
+    uint16_t* hh = (uint16_t*)(m0 + mp.router_bytes + mp.up_bytes);    // [2][F]
+    float* down = (float*)(m0 + mp.router_bytes + mp.up_bytes + mp.h_bytes);
+
+    // 1. q, k, v projections of x
+    StreamJob qkv{}, oj{};
+    qkv.w[0] = &A->q;
+    qkv.w[1] = &A->k;
+    qkv.w[2] = &A->v;
+    oj.w[0] = &A->o;
+    rc = launch_gemv_stream(qkv_part, x, nullptr, 1, qkv, ap.qkv, st);
+    if (rc != HQM_OK) return rc;
+    // 2. RoPE, cache append and attention
+    QkvSource src{qkv_part, (int)A->n_heads, (int)A->n_kv_heads, ap.qkv.col0[3], A->rope_theta, split_of(ap.qkv),
+                  colmap_of(ap.qkv), tc_error_ptr()};
+    launch_overlapped_cluster(attn_decode_kernel<true>, (int)A->n_heads * ATTN_SPLIT, 256, 0, ATTN_SPLIT, st, ctx,
+                              (const uint16_t*)nullptr, A->k_cache, A->v_cache, pos, (int)(A->n_heads / A->n_kv_heads),
+                              (int)A->max_len, src);
+    HQM_LAUNCH_CHECK();
+    // 3. output projection
+    rc = launch_gemv_stream(o_part, ctx, nullptr, 1, oj, ap.o, st);
+    if (rc != HQM_OK) return rc;
+    // 4. residual add, post-attention norm, router
+    launch_overlapped_cluster(finalize_add_rmsnorm_router_kernel, NORM_CTAS, NORM_THREADS, 0, NORM_CTAS, st, h,
+                              (const float*)o_part, A->ln_post, x2, hidden, A->rms_eps, split_of(ap.o), colmap_of(ap.o),
+                              L->gate_w, E, router_logits, topk_w, topk_idx);
+    HQM_LAUNCH_CHECK();
+    // 5.-7. both chosen experts: [w1; w3] x 2, silu * mul, w2 x 2
+    StreamJob gate_up{}, down_proj{};
+    gate_up.table = down_proj.table = L->table;
+    for (int slot = 0; slot < 2; ++slot) {
+        gate_up.w[2 * slot] = &L->w1;
+        gate_up.w[2 * slot + 1] = &L->w3;
+        gate_up.sel[2 * slot] = gate_up.sel[2 * slot + 1] = topk_idx + slot;
+        gate_up.which[2 * slot] = 0;
+        gate_up.which[2 * slot + 1] = 2;
+        down_proj.w[slot] = &L->w2;
+        down_proj.sel[slot] = topk_idx + slot;
+        down_proj.which[slot] = 1;
+        down_proj.xrow[slot] = slot;
+    }
+    down_proj.sel_settled = 1;
+    rc = launch_gemv_stream(up, x2, nullptr, 1, gate_up, mp.up, st);
+    if (rc != HQM_OK) return rc;
+    rc = launch_finalize_silu_mul(hh, up, 1, mp.up, st, /*late_trigger=*/true);
+    if (rc != HQM_OK) return rc;
+    rc = launch_gemv_stream(down, hh, nullptr, 1, down_proj, mp.down, st);
+    if (rc != HQM_OK) return rc;
+    // 8. weighted sum of the two experts, residual add, the next layer's input norm
+    launch_overlapped_cluster(finalize_scatter_add_rmsnorm_kernel, NORM_CTAS, NORM_THREADS, 0, NORM_CTAS, st, h,
+                              (const float*)down, (const float*)topk_w, L->next_ln, x, hidden, mp.down.col0[2],
+                              A->rms_eps, split_of(mp.down), colmap_of(mp.down));
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }

@@ -183,12 +183,10 @@ int hqm_expert_ffn(uint16_t* out, const uint16_t* x, int64_t M, const int32_t* t
 // Both experts of the token share every launch: [w1; w3] of expert A and of expert B in one streaming
 // launch (4 layers), one silu-mul over both, the two w2 in one launch (2 layers, each reading its own h
 // row), one weighted sum.
+}  // extern "C"
+
 namespace hqm {
-struct MoeDecodePlan {
-    StreamPlan up, down;
-    size_t router_bytes, up_bytes, h_bytes, down_bytes;
-};
-static bool moe_decode_plan(int E, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3, MoeDecodePlan* mp) {
+bool moe_decode_plan(int E, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3, MoeDecodePlan* mp) {
     const hqm_weight* up[4] = {w1, w3, w1, w3};
     const hqm_weight* down[2] = {w2, w2};
     if (!same_format(w1, w3) || !gemv_stream_plan(up, 4, 1, &mp->up) || !gemv_stream_plan(down, 2, 1, &mp->down))
@@ -200,6 +198,8 @@ static bool moe_decode_plan(int E, const hqm_weight* w1, const hqm_weight* w2, c
     return true;
 }
 }  // namespace hqm
+
+extern "C" {
 
 size_t hqm_moe_decode_scratch_bytes(int32_t E, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3) {
     if (!w1 || !w2 || !w3 || E < 2) return 0;
@@ -247,9 +247,12 @@ int hqm_moe_decode(uint16_t* out, uint16_t* router_logits, const uint16_t* x, co
         down_proj.which[slot] = 1;
         down_proj.xrow[slot] = slot;
     }
+    // the down projections may read the router's choice and start on their weights while the silu kernel runs:
+    // that kernel releases its successor only after the gate / up launch (and so the router) has completed
+    down_proj.sel_settled = 1;
     rc = launch_gemv_stream(up, x, nullptr, 1, gate_up, mp.up, st);
     if (rc != HQM_OK) return rc;
-    rc = launch_finalize_silu_mul(h, up, 1, mp.up, st);
+    rc = launch_finalize_silu_mul(h, up, 1, mp.up, st, /*late_trigger=*/true);
     if (rc != HQM_OK) return rc;
     rc = launch_gemv_stream(down, h, nullptr, 1, down_proj, mp.down, st);
     if (rc != HQM_OK) return rc;

@@ -219,6 +219,7 @@ struct Layers {
     const hqm_weight* table;
     const int32_t* sel[STREAM_MAX_LAYERS];
     int which[STREAM_MAX_LAYERS];
+    int sel_settled;    // the indices behind `sel` were complete before this kernel could start (see StreamJob)
 };
 
 template <int NBITS, int NB, int TOKS>
@@ -248,7 +249,7 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
     // buffer belong to earlier kernels and are touched only after it.
     grid_launch_dependents();
     bool synced = false;
-    if (ly.table) {
+    if (ly.table && !ly.sel_settled) {
         grid_dependency_wait();
         synced = true;
     }
@@ -279,7 +280,9 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
         for (int l = 1; l < STREAM_MAX_LAYERS; ++l) layer += (l < ly.count && rho_g >= ly.rho0[l]) ? 1 : 0;
         const int rho = rho_g - ly.rho0[layer];
         const int P = ly.rho0[layer + 1] - ly.rho0[layer], G = ly.G[layer], C = ly.C[layer];
-        const hqm_weight w = ly.table ? ly.table[3 * ly.sel[layer][0] + ly.which[layer]] : ly.w[layer];
+        // (__ldcg: the index may have been written by a kernel that finished while an earlier kernel on this SM
+        // still had the previous value in L1)
+        const hqm_weight w = ly.table ? ly.table[3 * __ldcg(ly.sel[layer]) + ly.which[layer]] : ly.w[layer];
         uint32_t qoff[NB];                          // this lane's weight rows, bytes from W_q + rho*K + k0
 #pragma unroll
         for (int b = 0; b < NB; ++b) qoff[b] = (uint32_t)(16 * b + g) * (uint32_t)P * (uint32_t)K + 16u * t;
@@ -565,10 +568,12 @@ __global__ void finalize_linear_kernel(uint16_t* __restrict__ y, const float* __
 
 // h[p][m, f] = bf16( bf16(silu(bf16(a))) * bf16(b) ) with a / b the summed partials of layers 2p / 2p + 1
 // of the launch (an expert's w1 and w3), for each of the launch's layer pairs p.
+// With `late_trigger` the next kernel may only start once everything in front of this one has completed.
 __global__ void finalize_silu_mul_kernel(uint16_t* __restrict__ h, const float* __restrict__ partial, int64_t M,
-                                         int F, int pairs, int row, Split sp, ColMap cm) {
-    grid_launch_dependents();
+                                         int F, int pairs, int row, int late_trigger, Split sp, ColMap cm) {
+    if (!late_trigger) grid_launch_dependents();
     grid_dependency_wait();
+    if (late_trigger) grid_launch_dependents();
     const int64_t MF = M * F, total = MF * pairs, MR = M * row;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int p = (int)(i / MF);
@@ -742,6 +747,7 @@ int launch_gemv_stream(float* partial, const uint16_t* x, const int32_t* x_idx, 
     ly.rho0[plan.count] = plan.rho0[plan.count];
     ly.col0[plan.count] = plan.col0[plan.count];
     ly.table = job.table;
+    ly.sel_settled = job.sel_settled;
     const Split sp = split_of(plan);
     // rows beyond one launch's tokens go in further launches over the same split
     for (int m0 = 0; m0 < (int)M; m0 += plan.toks) {
@@ -776,10 +782,11 @@ int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bi
     return HQM_OK;
 }
 
-int launch_finalize_silu_mul(uint16_t* h, const float* partial, int64_t M, const StreamPlan& plan, cudaStream_t st) {
+int launch_finalize_silu_mul(uint16_t* h, const float* partial, int64_t M, const StreamPlan& plan, cudaStream_t st,
+                             bool late_trigger) {
     const int F = plan.col0[1], pairs = plan.count / 2, row = plan.col0[plan.count];
     launch_overlapped(finalize_silu_mul_kernel, blocks_for(M * F * pairs), 256, 0, st, h, partial, M, F, pairs, row,
-                      split_of(plan), colmap_of(plan));
+                      late_trigger ? 1 : 0, split_of(plan), colmap_of(plan));
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }

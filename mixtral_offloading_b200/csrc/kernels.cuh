@@ -19,6 +19,10 @@ struct StreamJob {
     const hqm_weight* table;
     const int32_t* sel[STREAM_MAX_LAYERS];
     int which[STREAM_MAX_LAYERS];
+    // Set only when the kernel launched in front of this one lets its successor start after everything
+    // before it has completed (launch_finalize_silu_mul(..., late_trigger = true)) and the indices behind
+    // `sel` are older than that: the launch then reads them, and starts on the weights, without waiting.
+    int sel_settled;
 };
 struct StreamPlan {
     int count;                          // layers in the launch
@@ -41,7 +45,8 @@ int launch_gemv_stream(float* partial, const uint16_t* x, const int32_t* x_idx, 
 int launch_finalize_linear(uint16_t* y, const float* partial, const uint16_t* bias, int64_t M, const StreamPlan& plan,
                            cudaStream_t st);
 // h[p] (M, F) = silu(layer 2p) * layer 2p+1 for each pair of layers of the launch
-int launch_finalize_silu_mul(uint16_t* h, const float* partial, int64_t M, const StreamPlan& plan, cudaStream_t st);
+int launch_finalize_silu_mul(uint16_t* h, const float* partial, int64_t M, const StreamPlan& plan, cudaStream_t st,
+                             bool late_trigger = false);
 // out[token_idx[m]] (+)= sum over the launch's layers l of route_w[l * M + m] * layer l
 int launch_finalize_scatter(uint16_t* out, const float* partial, const int32_t* token_idx, const float* route_w,
                             int accumulate, int64_t M, const StreamPlan& plan, cudaStream_t st);
@@ -80,6 +85,13 @@ bool gemm_tc3_supported(const hqm_weight* w, int G, int C, int64_t M);
 size_t gemm_tc3_scratch_bytes(const hqm_weight* w, int G, int64_t M);
 int launch_gemm_tc3(uint16_t* y, void* scratch, const uint16_t* x, const int32_t* x_idx, int64_t M,
                     const hqm_weight* w, const uint16_t* bias, int G, int C, cudaStream_t st);
+
+// ffn.cu — launches of the single-token MoE block: [w1; w3] of both chosen experts (4 layers), then both w2.
+struct MoeDecodePlan {
+    StreamPlan up, down;
+    size_t router_bytes, up_bytes, h_bytes, down_bytes;
+};
+bool moe_decode_plan(int E, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3, MoeDecodePlan* mp);
 
 // Dispatcher used by hqm_linear and by the expert FFN: picks the streaming
 // kernel when the layer's shape allows it, the generic one otherwise.

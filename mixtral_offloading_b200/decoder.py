@@ -16,7 +16,7 @@ import torch
 from torch import nn
 
 from . import _cabi
-from .custom_layers import HQQLinearTritonSavable, _scratch
+from .custom_layers import HQQLinearTritonSavable, ResidentMoe, _scratch
 
 
 def _bf16_vec(t: torch.Tensor, n: int) -> torch.Tensor:
@@ -87,3 +87,50 @@ class AttentionDecode(nn.Module):
                                         C.byref(layer), _cabi.ptr(pos), _cabi.ptr(ws), ws.numel(),
                                         _cabi.stream_ptr(h.device)))
         return x_out
+
+
+class DecoderLayerDecode(nn.Module):
+    """One decoder layer for one token: AttentionDecode followed by a ResidentMoe block, with the residual adds
+    and norms between and after them, as one launch sequence (hqm_decode_layer).
+
+    attention: an AttentionDecode (its ln_in is the norm the CALLER applies to produce x for the first layer);
+    moe: a ResidentMoe; next_ln: the RMSNorm weight applied to the layer's output: the next layer's
+    input_layernorm weight, or the model's final norm weight after the last layer."""
+
+    def __init__(self, attention: AttentionDecode, moe: ResidentMoe, next_ln: torch.Tensor):
+        super().__init__()
+        self.attention, self.moe, self.next_ln = attention, moe, next_ln
+        self._layer = None
+        self._gate_w = None
+
+    def _descriptor(self, device) -> _cabi.HqmDecoderLayer:
+        if self._layer is None:
+            hidden = self.attention.n_heads * self.attention.head_dim
+            gate = self.moe.gate.weight
+            self._gate_w = gate if gate.dtype == torch.bfloat16 else gate.to(torch.bfloat16)
+            f0 = self.moe._ffn(self.moe._experts[0])
+            self._layer = _cabi.HqmDecoderLayer(
+                attn=self.attention._descriptor(), gate_w=self._gate_w.data_ptr(),
+                table=self.moe._descriptor_table(device).data_ptr(), w1=f0.w1.descriptor(), w2=f0.w2.descriptor(),
+                w3=f0.w3.descriptor(), next_ln=_bf16_vec(self.next_ln, hidden).data_ptr(),
+                n_experts=self.moe.num_experts, reserved=0)
+        return self._layer
+
+    @torch.inference_mode()
+    def forward(self, h: torch.Tensor, x: torch.Tensor, pos: torch.Tensor):
+        """h: (1, hidden) bf16 residual stream, updated in place.  x: (1, hidden) bf16, on entry the normalised
+        input of this layer, on return the normalised input of the next one (updated in place).
+        pos: int32 tensor of one element on the device.  Returns the router logits (1, n_experts)."""
+        hidden = h.shape[-1]
+        _bf16_vec(h, hidden), _bf16_vec(x, hidden)
+        assert pos.is_cuda and pos.dtype == torch.int32 and pos.numel() == 1
+        lib = _cabi.lib()
+        layer = self._descriptor(h.device)
+        need = lib.hqm_decode_layer_scratch_bytes(C.byref(layer))
+        if need == 0:
+            raise ValueError(lib.hqm_last_error().decode() or "decoder layer: unsupported shapes")
+        ws = _scratch(h.device, need)
+        logits = torch.empty((1, self.moe.num_experts), dtype=torch.bfloat16, device=h.device)
+        _cabi.check(lib.hqm_decode_layer(_cabi.ptr(h), _cabi.ptr(x), _cabi.ptr(logits), C.byref(layer), _cabi.ptr(pos),
+                                         _cabi.ptr(ws), ws.numel(), _cabi.stream_ptr(h.device)))
+        return logits

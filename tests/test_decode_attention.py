@@ -5,7 +5,7 @@ import math
 import pytest
 import torch
 
-from mixtral_offloading_b200 import AttentionDecode, add_rmsnorm
+from mixtral_offloading_b200 import AttentionDecode, DecoderLayerDecode, ResidentMoe, add_rmsnorm
 from oracle import hqq_oracle as O
 from tests.helpers import layer_from_oracle, random_layer
 
@@ -158,3 +158,46 @@ def test_add_rmsnorm():
         hd2 = h.clone().to(DEV)
         x2 = add_rmsnorm(hd2, None, w.to(DEV), 1e-5)
         assert torch.equal(hd2.cpu(), h) and rel(x2, rms_ref(h, w, 1e-5)) < 1e-2
+
+
+class _Cfg:
+    def __init__(self, hidden, ffn, n_exp):
+        self.hidden_size, self.intermediate_size, self.num_local_experts = hidden, ffn, n_exp
+        self.num_experts_per_tok, self.hidden_act = 2, "silu"
+
+
+def test_fused_decoder_layer_matches_the_two_separate_calls():
+    """hqm_decode_layer against AttentionDecode + ResidentMoe + add_rmsnorm on the same weights, over several
+    positions: same residual stream, same next-layer input, same router logits, same cache rows."""
+    from tests.test_gpu_parity import make_expert
+    n_heads, n_kv, ffn, E, max_len = 8, 2, 3584, 8, 32
+    hidden = n_heads * HD
+    mod, _, _ = build(n_heads, n_kv, max_len, seed=21)
+    mod2, _, _ = build(n_heads, n_kv, max_len, seed=21)                 # same weights, own cache
+    experts = [make_expert(hidden, ffn, (random_layer(ffn, hidden, 2, 16, 100 + 3 * e), random_layer(hidden, ffn, 2, 16, 101 + 3 * e),
+                                         random_layer(ffn, hidden, 2, 16, 102 + 3 * e))) for e in range(E)]
+    g = torch.Generator().manual_seed(4)
+    gate = torch.nn.Linear(hidden, E, bias=False, dtype=torch.bfloat16, device=DEV)
+    gate.weight.data.copy_((0.5 * torch.randn(E, hidden, generator=g)).to(torch.bfloat16))
+    moe = ResidentMoe(_Cfg(hidden, ffn, E), 0, gate, experts)
+    next_ln = (1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16).to(DEV)
+    fused = DecoderLayerDecode(mod2, moe, next_ln)
+    pos = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for step in range(12):
+        h0 = torch.randn(1, hidden, generator=g).to(torch.bfloat16).to(DEV)
+        # separate calls
+        h_a = h0.clone()
+        x_moe = mod(h_a, pos)                                            # norm(ln_in) inside
+        y, logits_a = moe(x_moe.view(1, 1, hidden))
+        x_a = add_rmsnorm(h_a, y.view(1, hidden), next_ln, 1e-5)
+        # fused layer: the caller provides the normalised input
+        h_b = h0.clone()
+        x_b = add_rmsnorm(h_b, None, mod.ln_in, 1e-5)
+        logits_b = fused(h_b, x_b, pos)
+        assert rel(logits_b, logits_a.float().cpu()) < 1e-2, step
+        if set(logits_a.float().view(-1).topk(2).indices.tolist()) == set(logits_b.float().view(-1).topk(2).indices.tolist()):
+            assert rel(h_b, h_a.float().cpu()) < 1e-2, step
+            assert rel(x_b, x_a.float().cpu()) < 1e-2, step
+        assert rel(mod2.k_cache[:, step], mod.k_cache[:, step].float().cpu()) < 1e-2
+        assert rel(mod2.v_cache[:, step], mod.v_cache[:, step].float().cpu()) < 1e-2
+        pos += 1
