@@ -6,6 +6,8 @@
 //
 // The weight is the MMA's A operand (M = 128 rows of W), the tokens are its N dimension
 // (64 / 128 / 256 per tile), so a small batch wastes nothing.  Per 64-column k-block a CTA
+//   0. requests every global load of the block at once (scale / zero bytes and their fp16
+//      meta, the packed words, the x columns: one exposed round trip per block),
 //   1. decodes scale and zero (8 bit -> s and -z*s, bf16) for the tile's residues once
 //      into shared memory,
 //   2. dequantises its 128 x 64 weights straight from the packed words into a
@@ -142,27 +144,83 @@ gemm_tc_kernel(Params prm) {
             __nv_bfloat16* sS = reinterpret_cast<__nv_bfloat16*>(st + CF::A_BYTES + CF::B_BYTES);   // [RES][64]  s
             __nv_bfloat16* sT = sS + RES * BK;                                                       // [RES][64] -z*s
             const int k0 = (kb_begin + it) * BK;
-            // ---- 1. scale / zero of the tile's RES residue rows x 64 columns
-            for (int e = tid; e < RES * BK; e += PRODUCERS) {
-                const int ri = e / BK, kk = e % BK;
-                const int r = PER * rho0 + ri;                        // residue = (rho0 + ri / PER) * PER + ri % PER
-                const uint32_t idx = (uint32_t)r * (uint32_t)K + (uint32_t)(k0 + kk);   // < 2^31 (checked on the host)
-                const uint32_t col = idx % (uint32_t)prm.C;
-                const float sc = ((float)w.scale_q[idx] - f16_bits_to_float(w.mz_scale[col])) *
-                                 f16_bits_to_float(w.ms_scale[col]);
-                const float zr = ((float)w.zero_q[idx] - f16_bits_to_float(w.mz_zero[col])) *
-                                 f16_bits_to_float(w.ms_zero[col]);
-                sS[e] = __float2bfloat16_rn(sc);
-                sT[e] = __float2bfloat16_rn(-zr * sc);
+            // ---- every global load of the k-block is requested up front (one exposed round trip per k-block):
+            // (a) scale / zero bytes and their fp16 meta for 4 consecutive columns of one residue row,
+            // (b) the packed words of this thread's dequantisation tasks, (c) its chunks of the x tile
+            constexpr int META_TASKS = RES * (BK / 4);
+            constexpr int NTASK = RT * GS * 4 / PRODUCERS;
+            static_assert(RT * GS * 4 % PRODUCERS == 0 && META_TASKS <= PRODUCERS, "task split");
+            uint32_t sq4 = 0u, zq4 = 0u;
+            uint2 m_ss = make_uint2(0u, 0u), m_zs = m_ss, m_sz = m_ss, m_zz = m_ss;
+            const int mri = tid / (BK / 4), mkk = (tid % (BK / 4)) * 4;
+            if (tid < META_TASKS) {
+                const uint32_t idx = (uint32_t)(PER * rho0 + mri) * (uint32_t)K + (uint32_t)(k0 + mkk);
+                const uint32_t col = idx % (uint32_t)prm.C;              // C % 4 == 0: the 4 columns do not wrap
+                sq4 = *reinterpret_cast<const uint32_t*>(w.scale_q + idx);
+                zq4 = *reinterpret_cast<const uint32_t*>(w.zero_q + idx);
+                m_ss = *reinterpret_cast<const uint2*>(w.ms_scale + col);
+                m_zs = *reinterpret_cast<const uint2*>(w.mz_scale + col);
+                m_sz = *reinterpret_cast<const uint2*>(w.ms_zero + col);
+                m_zz = *reinterpret_cast<const uint2*>(w.mz_zero + col);
+            }
+            constexpr bool X_EARLY = NTOK <= 128;      // the 256-token tile is streamed chunk by chunk after the dequantisation
+            uint4 pk[NTASK];
+            auto load_w = [&]() {
+#pragma unroll
+                for (int q = 0; q < NTASK; ++q) {
+                    const int task = tid + q * PRODUCERS;
+                    const int qq = task >> 2, c = task & 3;
+                    const int rr = qq / GS, j = qq % GS;
+                    const int64_t R = (int64_t)(rho0 + rr) + (int64_t)j * P;
+                    pk[q] = ld_stream_16(Wq + R * K + k0 + 16 * c);
+                }
+            };
+            if constexpr (X_EARLY) load_w();
+            // (with 256 tokens the x tile is 16 chunks per thread: too many registers to hold across the
+            // dequantisation, so it is fetched afterwards)
+            constexpr int XT = X_EARLY ? NTOK * 8 / PRODUCERS : 1;
+            uint4 xv[XT];
+            auto load_x = [&]() {
+#pragma unroll
+                for (int q = 0; q < XT; ++q) {
+                    const int task = tid + q * PRODUCERS;
+                    const int tok = task >> 3, ch = task & 7;
+                    xv[q] = make_uint4(0u, 0u, 0u, 0u);
+                    if (tok < prm.M) {
+                        const int mm = prm.m_base + tok;
+                        const int64_t xrow = prm.x_idx ? prm.x_idx[mm] : mm;
+                        xv[q] = *reinterpret_cast<const uint4*>(prm.x + xrow * K + k0 + 8 * ch);
+                    }
+                }
+            };
+            if constexpr (X_EARLY) load_x();
+            // ---- 1. scale / zero of the tile's RES residue rows x 64 columns: s and -z*s as bf16
+            if (tid < META_TASKS) {
+                const uint32_t ms_s[2] = {m_ss.x, m_ss.y}, mz_s[2] = {m_zs.x, m_zs.y};
+                const uint32_t ms_z[2] = {m_sz.x, m_sz.y}, mz_z[2] = {m_zz.x, m_zz.y};
+                __nv_bfloat16 so[4], to[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const uint32_t sh = 16u * (e & 1);
+                    const float sc = ((float)((sq4 >> (8 * e)) & 0xffu) - f16_bits_to_float((uint16_t)(mz_s[e >> 1] >> sh))) *
+                                     f16_bits_to_float((uint16_t)(ms_s[e >> 1] >> sh));
+                    const float zr = ((float)((zq4 >> (8 * e)) & 0xffu) - f16_bits_to_float((uint16_t)(mz_z[e >> 1] >> sh))) *
+                                     f16_bits_to_float((uint16_t)(ms_z[e >> 1] >> sh));
+                    so[e] = __float2bfloat16_rn(sc);
+                    to[e] = __float2bfloat16_rn(-zr * sc);
+                }
+                *reinterpret_cast<uint2*>(sS + mri * BK + mkk) = *reinterpret_cast<const uint2*>(so);
+                *reinterpret_cast<uint2*>(sT + mri * BK + mkk) = *reinterpret_cast<const uint2*>(to);
             }
             asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
             // ---- 2. dequantise: one task = 16 bytes of one storage row = 16 columns x PER output rows
-            for (int task = tid; task < RT * GS * 4; task += PRODUCERS) {
-                const int q = task >> 2, c = task & 3;
-                const int rr = q / GS, j = q % GS;
-                const int64_t R = (int64_t)(rho0 + rr) + (int64_t)j * P;
-                const uint4 pk = ld_stream_16(Wq + R * K + k0 + 16 * c);
-                const uint32_t words[4] = {pk.x, pk.y, pk.z, pk.w};
+            if constexpr (!X_EARLY) load_w();
+#pragma unroll
+            for (int q = 0; q < NTASK; ++q) {
+                const int task = tid + q * PRODUCERS;
+                const int qq = task >> 2, c = task & 3;
+                const int rr = qq / GS, j = qq % GS;
+                const uint32_t words[4] = {pk[q].x, pk[q].y, pk[q].z, pk[q].w};
 #pragma unroll
                 for (int sl = 0; sl < PER; ++sl) {
                     const int ri = rr * PER + sl;
@@ -185,15 +243,24 @@ gemm_tc_kernel(Params prm) {
                 }
             }
             // ---- 3. the tokens' 64 columns of x
-            for (int task = tid; task < NTOK * 8; task += PRODUCERS) {
-                const int tok = task >> 3, ch = task & 7;
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (tok < prm.M) {
-                    const int mm = prm.m_base + tok;
-                    const int64_t xrow = prm.x_idx ? prm.x_idx[mm] : mm;
-                    v = *reinterpret_cast<const uint4*>(prm.x + xrow * K + k0 + 8 * ch);
+            if constexpr (X_EARLY) {
+#pragma unroll
+                for (int q = 0; q < XT; ++q) {
+                    const int task = tid + q * PRODUCERS;
+                    *reinterpret_cast<uint4*>(sB + sw128(task >> 3, task & 7)) = xv[q];
                 }
-                *reinterpret_cast<uint4*>(sB + sw128(tok, ch)) = v;
+            } else {
+#pragma unroll 4
+                for (int task = tid; task < NTOK * 8; task += PRODUCERS) {
+                    const int tok = task >> 3, ch = task & 7;
+                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                    if (tok < prm.M) {
+                        const int mm = prm.m_base + tok;
+                        const int64_t xrow = prm.x_idx ? prm.x_idx[mm] : mm;
+                        v = *reinterpret_cast<const uint4*>(prm.x + xrow * K + k0 + 8 * ch);
+                    }
+                    *reinterpret_cast<uint4*>(sB + sw128(tok, ch)) = v;
+                }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor core
             mbar_arrive(full + s);
@@ -295,8 +362,9 @@ bool gemm_tc_supported(const hqm_weight* w, int G, int C, int64_t M) {
     const int rt = 128 / (g * per);
     if (G % per != 0 || (G / per) % rt != 0 || w->K % 64 != 0 || M < 1) return false;
     if ((int64_t)G * w->K >= ((int64_t)1 << 31)) return false;
-    (void)C;
-    return tc_aligned16(w->W_q);
+    if (C % 4 != 0) return false;                  // 4 consecutive scale/zero columns share one meta load
+    return tc_aligned16(w->W_q) && tc_aligned16(w->scale_q) && tc_aligned16(w->zero_q) && tc_aligned16(w->ms_scale) &&
+           tc_aligned16(w->mz_scale) && tc_aligned16(w->ms_zero) && tc_aligned16(w->mz_zero);
 }
 
 int gemm_tc_splitk(const hqm_weight* w, int layers, int G) {
