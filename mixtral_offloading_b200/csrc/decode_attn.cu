@@ -234,11 +234,10 @@ __global__ void __launch_bounds__(NORM_THREADS) finalize_scatter_add_rmsnorm_ker
         const int i = first + j * stride;
         v[j] = 0.f;
         if (i < H) {
-            float y = 0.f;
-            for (int l = 0; l < cm.count; ++l) {
-                const float t = round_bf16(round_bf16(partial_sum(partial, sp, cm, 0, cm.col0[l] + i, row, row)) * route_w[l]);
-                y = (l == 0) ? t : round_bf16(y + t);
-            }
+            // the launch holds the token's two experts: both sums are requested together
+            float s0, s1;
+            partial_sum_pair(partial, sp, cm, 0, cm.col0[0] + i, cm.col0[1] + i, row, row, s0, s1);
+            const float y = round_bf16(round_bf16(round_bf16(s0) * route_w[0]) + round_bf16(round_bf16(s1) * route_w[1]));
             v[j] = round_bf16(bf16_bits_to_float(h[i]) + y);
             h[i] = float_to_bf16_bits(v[j]);
         }
@@ -270,8 +269,10 @@ __global__ void __launch_bounds__(64) finalize_qkv_rope_kernel(uint16_t* __restr
         return;
     }
     const int col = head * HEAD_DIM + d;                 // q heads, then k heads, then v heads: the row's order
-    const float a = round_bf16(partial_sum(partial, sp, cm, 0, col, row, row));
-    const float b = round_bf16(partial_sum(partial, sp, cm, 0, col + HEAD_DIM / 2, row, row));
+    float a, b;
+    partial_sum_pair(partial, sp, cm, 0, col, col + HEAD_DIM / 2, row, row, a, b);
+    a = round_bf16(a);
+    b = round_bf16(b);
     float o0 = a, o1 = b;
     if (head < n_heads + n_kv) {
         const float inv_freq = powf(theta, -(float)(2 * d) / (float)HEAD_DIM);
@@ -348,8 +349,10 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(uint16_t* __restrict__
         const int which = threadIdx.x >> 6, d = threadIdx.x & 63;     // 0: q, 1: k, 2: v;  pair (d, d + 64)
         if (which < 3) {
             const int col = (which == 0 ? head : (which == 1 ? src.n_heads + kvh : src.n_heads + src.n_kv + kvh)) * HEAD_DIM + d;
-            const float a = round_bf16(partial_sum(src.partial, src.sp, src.cm, 0, col, src.row, src.row));
-            const float b = round_bf16(partial_sum(src.partial, src.sp, src.cm, 0, col + HEAD_DIM / 2, src.row, src.row));
+            float a, b;
+            partial_sum_pair(src.partial, src.sp, src.cm, 0, col, col + HEAD_DIM / 2, src.row, src.row, a, b);
+            a = round_bf16(a);
+            b = round_bf16(b);
             float o0 = a, o1 = b;
             if (which < 2) rope_pair(a, b, d, pos, src.theta, o0, o1);
             float* dst = which == 0 ? s_q : (which == 1 ? s_kn : s_vn);

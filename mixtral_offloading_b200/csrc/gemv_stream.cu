@@ -579,8 +579,8 @@ __global__ void finalize_silu_mul_kernel(uint16_t* __restrict__ h, const float* 
         const int p = (int)(i / MF);
         const int64_t m = (i - p * MF) / F;
         const int f = (int)(i - p * MF - m * F);
-        float a = partial_sum(partial, sp, cm, m, cm.col0[2 * p] + f, row, MR);
-        float b = partial_sum(partial, sp, cm, m, cm.col0[2 * p + 1] + f, row, MR);
+        float a, b;
+        partial_sum_pair(partial, sp, cm, m, layer_col0(cm, 2 * p) + f, layer_col0(cm, 2 * p + 1) + f, row, MR, a, b);
         a = round_bf16(a);
         b = round_bf16(b);
         const float act = round_bf16(a / (1.f + __expf(-a)));
@@ -603,10 +603,13 @@ __global__ void finalize_scatter_kernel(uint16_t* __restrict__ out, const float*
         const int64_t tk = token_idx ? token_idx[m] : m;
         uint16_t* dst = out + tk * H + n;
         float acc = accumulate ? bf16_bits_to_float(*dst) : 0.f;
-        for (int l = 0; l < cm.count; ++l) {
-            const float wgt = route_w ? route_w[l * M + m] : 1.f;
-            const float v = round_bf16(round_bf16(partial_sum(partial, sp, cm, m, cm.col0[l] + n, row, MR)) * wgt);
-            acc = (l == 0 && !accumulate) ? v : round_bf16(acc + v);
+#pragma unroll
+        for (int l = 0; l < STREAM_MAX_LAYERS; ++l) {
+            if (l < cm.count) {
+                const float wgt = route_w ? route_w[l * M + m] : 1.f;
+                const float v = round_bf16(round_bf16(partial_sum(partial, sp, cm, m, cm.col0[l] + n, row, MR)) * wgt);
+                acc = (l == 0 && !accumulate) ? v : round_bf16(acc + v);
+            }
         }
         *dst = float_to_bf16_bits(acc);
     }

@@ -30,13 +30,25 @@ struct ColMap {
     int G[STREAM_MAX_LAYERS];
 };
 
+// First column of layer l (l may be a run-time value: the selects keep the arrays in the parameter bank).
+__device__ __forceinline__ int layer_col0(const ColMap& cm, int l) {
+    int c = cm.col0[0];
+#pragma unroll
+    for (int i = 1; i <= STREAM_MAX_LAYERS; ++i) c = (l == i) ? cm.col0[i] : c;
+    return c;
+}
+
 // Number of partial row-sets that hold a piece of column `col` of a partial row.
 __device__ __forceinline__ int partial_count(const Split& sp, const ColMap& cm, int col) {
-    int layer = 0;
+    int c0 = cm.col0[0], r0 = cm.rho0[0], G = cm.G[0];
 #pragma unroll
-    for (int l = 1; l < STREAM_MAX_LAYERS; ++l) layer += (l < cm.count && col >= cm.col0[l]) ? 1 : 0;
-    const int nn = col - cm.col0[layer];
-    const uint32_t rho_g = (uint32_t)(cm.rho0[layer] + (nn % cm.G[layer]) / cm.per);
+    for (int l = 1; l < STREAM_MAX_LAYERS; ++l) {
+        const bool in = l < cm.count && col >= cm.col0[l];
+        c0 = in ? cm.col0[l] : c0;
+        r0 = in ? cm.rho0[l] : r0;
+        G = in ? cm.G[l] : G;
+    }
+    const uint32_t rho_g = (uint32_t)(r0 + ((col - c0) % G) / cm.per);
     return sp.owner(rho_g * sp.PT + sp.PT - 1) - sp.owner(rho_g * sp.PT) + 1;
 }
 
@@ -54,6 +66,30 @@ __device__ __forceinline__ float partial_sum(const float* __restrict__ partial, 
         v += ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
     }
     return v;
+}
+
+// Two elements of the same row at once (a rotation pair, the gate and up halves of an FFN, the two experts of a
+// token): the row-sets of both are requested together, so the pair costs the round trips of one.
+__device__ __forceinline__ void partial_sum_pair(const float* __restrict__ partial, const Split& sp, const ColMap& cm,
+                                                 int64_t m, int col_a, int col_b, int row, int64_t MR, float& out_a,
+                                                 float& out_b) {
+    const int cnt_a = partial_count(sp, cm, col_a), cnt_b = partial_count(sp, cm, col_b);
+    const float* pa = partial + m * row + col_a;
+    const float* pb = partial + m * row + col_b;
+    float va = 0.f, vb = 0.f;
+    const int cnt = cnt_a > cnt_b ? cnt_a : cnt_b;
+    for (int s = 0; s < cnt; s += 8) {
+        float a[8], b[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            a[j] = (s + j < cnt_a) ? pa[(int64_t)(s + j) * MR] : 0.f;
+            b[j] = (s + j < cnt_b) ? pb[(int64_t)(s + j) * MR] : 0.f;
+        }
+        va += ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
+        vb += ((b[0] + b[1]) + (b[2] + b[3])) + ((b[4] + b[5]) + (b[6] + b[7]));
+    }
+    out_a = va;
+    out_b = vb;
 }
 
 inline Split split_of(const StreamPlan& plan) { return Split{plan.rho0[plan.count], plan.PT, plan.warps}; }
