@@ -88,49 +88,57 @@ __device__ __forceinline__ uint32_t and_or(uint32_t v, uint32_t mask, uint32_t m
 }
 
 // Masks and fp16 magic numbers of the extraction, passed as a kernel parameter so that
-// they live in (uniform) registers instead of being re-materialised as immediates.
+// they live in (uniform) registers instead of being re-materialised as immediates.  A field at bit b of a
+// 16-bit half lies inside the fp16 mantissa when b + width <= 10; OR-ed into the constant 2^(10-b) its lowest
+// bit weighs exactly 1, so the half reads 2^(10-b) + code.  Fields above the mantissa are shifted down first.
 struct FieldConsts {
-    uint32_t mask_a, mask_b, mask_c;     // 2-bit: bits 7-6, 5-4, 9-8 of each half;  4-bit: bits 7-4
-    uint32_t magic_a, magic_b, magic_c;  // 16.0, 64.0, 4.0 in both halves
+    uint32_t mask_a, mask_b, mask_c, mask_d, mask_e;
+    uint32_t magic_a, magic_b, magic_c, magic_d, magic_e;
 };
 static inline FieldConsts field_consts(int nbits) {
-    if (nbits == 2) return FieldConsts{0x00C000C0u, 0x00300030u, 0x03000300u, 0x4C004C00u, 0x54005400u, 0x44004400u};
-    return FieldConsts{0x00F000F0u, 0u, 0u, 0x54005400u, 0u, 0u};
+    if (nbits == 2)   // bits 7-6 -> 16 + c, 5-4 -> 64 + c, 9-8 -> 4 + c, 3-2 -> 256 + c, 1-0 -> 1024 + c
+        return FieldConsts{0x00C000C0u, 0x00300030u, 0x03000300u, 0x000C000Cu, 0x00030003u,
+                           0x4C004C00u, 0x54005400u, 0x44004400u, 0x5C005C00u, 0x64006400u};
+    // 4 bit: bits 7-4 -> 64 + c, bits 3-0 -> 1024 + c
+    return FieldConsts{0x00F000F0u, 0x000F000Fu, 0u, 0u, 0u, 0x54005400u, 0x64006400u, 0u, 0u, 0u};
 }
 
 template <int NBITS> struct Fields;
 
 template <> struct Fields<2> {
     static constexpr int PER = 4;
-    uint32_t v0, v1, v2, v3;
-    __device__ __forceinline__ explicit Fields(uint32_t u) : v0(u), v1(u << 4), v2(u >> 4), v3(u >> 8) {}
+    uint32_t v0, v2, v3;
+    __device__ __forceinline__ explicit Fields(uint32_t u) : v0(u), v2(u >> 4), v3(u >> 8) {}
     template <int S> __device__ __forceinline__ uint32_t lo(const FieldConsts& c) const {
         if (S == 0) return and_or(v0, c.mask_a, c.magic_a);     // bits 7-6            -> 16 + code
         if (S == 1) return and_or(v0, c.mask_b, c.magic_b);     // bits 5-4            -> 64 + code
-        if (S == 2) return and_or(v1, c.mask_a, c.magic_a);     // bits 3-2 moved to 7-6
-        return and_or(v1, c.mask_b, c.magic_b);                 // bits 1-0 moved to 5-4
+        if (S == 2) return and_or(v0, c.mask_d, c.magic_d);     // bits 3-2            -> 256 + code
+        return and_or(v0, c.mask_e, c.magic_e);                 // bits 1-0            -> 1024 + code
     }
     template <int S> __device__ __forceinline__ uint32_t hi(const FieldConsts& c) const {
-        if (S == 0) return and_or(v3, c.mask_a, c.magic_a);     // bits 15-14 moved to 7-6
+        if (S == 0) return and_or(v3, c.mask_a, c.magic_a);     // bits 15-14 moved to 7-6 -> 16 + code
         if (S == 1) return and_or(v2, c.mask_c, c.magic_c);     // bits 13-12 moved to 9-8 -> 4 + code
-        if (S == 2) return and_or(v2, c.mask_a, c.magic_a);     // bits 11-10 moved to 7-6
-        return and_or(v0, c.mask_c, c.magic_c);                 // bits 9-8
+        if (S == 2) return and_or(v2, c.mask_a, c.magic_a);     // bits 11-10 moved to 7-6 -> 16 + code
+        return and_or(v0, c.mask_c, c.magic_c);                 // bits 9-8                -> 4 + code
     }
-    __host__ __device__ static constexpr uint32_t off_lo(int s) { return (s & 1) ? 0x5400u : 0x4C00u; }
+    __host__ __device__ static constexpr uint32_t off_lo(int s) {
+        return s == 0 ? 0x4C00u : (s == 1 ? 0x5400u : (s == 2 ? 0x5C00u : 0x6400u));
+    }
     __host__ __device__ static constexpr uint32_t off_hi(int s) { return (s & 1) ? 0x4400u : 0x4C00u; }
 };
 
 template <> struct Fields<4> {
     static constexpr int PER = 2;
-    uint32_t v0, v1, v2, v3;
-    __device__ __forceinline__ explicit Fields(uint32_t u) : v0(u), v1(u << 4), v2(u >> 4), v3(u >> 8) {}
+    uint32_t v0, v2, v3;
+    __device__ __forceinline__ explicit Fields(uint32_t u) : v0(u), v2(u >> 4), v3(u >> 8) {}
     template <int S> __device__ __forceinline__ uint32_t lo(const FieldConsts& c) const {
-        return and_or(S == 0 ? v0 : v1, c.mask_a, c.magic_a);   // nibble at bits 7-4 -> 64 + code
+        return S == 0 ? and_or(v0, c.mask_a, c.magic_a)         // bits 7-4 -> 64 + code
+                      : and_or(v0, c.mask_b, c.magic_b);        // bits 3-0 -> 1024 + code
     }
     template <int S> __device__ __forceinline__ uint32_t hi(const FieldConsts& c) const {
-        return and_or(S == 0 ? v3 : v2, c.mask_a, c.magic_a);
+        return and_or(S == 0 ? v3 : v2, c.mask_a, c.magic_a);   // bits 15-12 / 11-8 moved to 7-4 -> 64 + code
     }
-    __host__ __device__ static constexpr uint32_t off_lo(int) { return 0x5400u; }
+    __host__ __device__ static constexpr uint32_t off_lo(int s) { return s == 0 ? 0x5400u : 0x6400u; }
     __host__ __device__ static constexpr uint32_t off_hi(int) { return 0x5400u; }
 };
 
@@ -265,8 +273,8 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
     const int sa = (2 * t) % PER;                   // first of the two slots whose columns this lane reads back
     const uint32_t keep = (g < PER) ? 0xffffffffu : 0u;
     const int zrow = (g < PER ? g : PER) * ROW + 16 * t;      // this lane's row of the z tile (row PER is zero)
-    const uint32_t olo = ((g & 1) ? F::off_lo(1) : F::off_lo(0)) * 0x00010001u & keep;
-    const uint32_t ohi = ((g & 1) ? F::off_hi(1) : F::off_hi(0)) * 0x00010001u & keep;
+    const uint32_t olo = F::off_lo(g & 3) * 0x00010001u & keep;   // row 8 + g of the correction tile: slot g's offsets
+    const uint32_t ohi = F::off_hi(g & 3) * 0x00010001u & keep;
 
     const int gw = blockIdx.x * NW + wi;                                           // this warp in the grid
     const uint32_t L_begin = sp.begin(gw), L_end = sp.begin(gw + 1);
