@@ -34,6 +34,7 @@ if ROOT not in sys.path:
 HIDDEN, FFN = 4096, 14336
 NBITS, GROUP = 2, 16
 POOL = 8                                     # distinct experts rotated through: 8 x 66.4 MB = 531 MB > 126 MB L2
+NCU_DRAM_BYTES_PER_LAUNCH = 22164480          # ncu: DRAM bytes of one 14336x4096 2-bit g16 streaming launch
 METRIC = "decode_tokens_per_s_expert_ffn"
 UNIT = "tok/s"
 
@@ -357,7 +358,7 @@ def run_decode(args):
     measured token.  Before timing, one step is also computed with torch ops around the library's linears
     (rms_norm, RoPE tables, scaled_dot_product_attention) and the logits of the two are compared."""
     from mixtral_offloading_b200 import (AttentionDecode, BaseQuantizeConfig, DecoderLayerDecode, HQQLinearTritonSavable,
-                                         ResidentMoe, add_rmsnorm)
+                                         MixtralDecodeModel, ResidentMoe, add_rmsnorm)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -414,8 +415,8 @@ def run_decode(args):
         ly["fused"] = DecoderLayerDecode(ly["attn"], ly["moe"], layers[i + 1]["ln1"] if i + 1 < L else ln_f)
     inv_freq = 1.0 / (1e6 ** (torch.arange(0, HD, 2, device=dev, dtype=torch.float32) / HD))
     pos = torch.full((1,), args.context, dtype=torch.int64, device=dev)     # position of the token being decoded
-    pos32 = torch.full((1,), args.context, dtype=torch.int32, device=dev)
-    tok = torch.zeros((1,), dtype=torch.int64, device=dev)
+    model = MixtralDecodeModel(embed, [ly["fused"] for ly in layers], layers[0]["ln1"], lm_head)   # the public API
+    pos32, tok = model.position.fill_(args.context), model.token
     positions = torch.arange(max_len, device=dev)
 
     F = torch.nn.functional
@@ -431,15 +432,7 @@ def run_decode(args):
         rot = torch.cat([-t[..., HD // 2:], t[..., :HD // 2]], -1)
         return (t.float() * cos + rot.float() * sin).to(torch.bfloat16)
 
-    def step():
-        h = embed[tok]                                                     # (1, H), a fresh tensor
-        x = add_rmsnorm(h, None, layers[0]["ln1"], 1e-5)
-        for ly in layers:
-            ly["fused"](h, x, pos32)                                       # h and x updated in place
-        logits = torch.matmul(x, lm_head.t())                              # x = final norm of h after the last layer
-        tok.copy_(logits.argmax(-1))
-        pos32.add_(1)
-        return logits
+    step = model.step
 
     trace = []                                   # per layer: (input h, output h, router logits) of the torch-glue step
 
@@ -494,9 +487,8 @@ def run_decode(args):
         tok.zero_()
         pos32.fill_(args.context)
         launches0 = lib.hqm_launch_count()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step()
+        model.capture(warmup=0)
+        graph = model._graph
         launches_per_step = lib.hqm_launch_count() - launches0
         for _ in range(args.warmup):
             graph.replay()
@@ -582,7 +574,10 @@ def run_decode(args):
         "hbm_gbs_per_gpu_step": step_bytes / (ms * 1e-3) / 1e9, "algorithmic_bytes_per_step": step_bytes,
         "hbm_frac_per_gpu_step": step_bytes / (ms * 1e-3) / 1e9 / peak,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "kernel": "quantized linear 14336x4096 2-bit g16 (w1/w3 of layer 0's experts, "
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+                     "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this "
+                     "kernel and shape (profiles/gemv_stream_2bit_g16_14336x4096_m1.md); not re-measured by this run",
+                     "kernel": "quantized linear 14336x4096 2-bit g16 (w1/w3 of layer 0's experts, "
                      f"354 MB rotated), fastest of 3 runs of {reps} launches, CUDA events", "algorithmic_bytes": lin_bytes,
                      "us_per_launch": kernel_ms * 1e3, "peak_kind": f"{peak_kind} HBM copy bandwidth",
                      "frac_of_8tbs": achieved / 8000.0},

@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(NORM_THREADS) finalize_add_rmsnorm_kernel(uint
         const int i = first + j * stride;
         v[j] = 0.f;
         if (i < H) {
-            const float y = round_bf16(partial_sum(partial, sp, cm, 0, i, H, H));
+            const float y = round_bf16(partial_sum<true>(partial, sp, cm, 0, i, H, H));
             v[j] = round_bf16(bf16_bits_to_float(h[i]) + y);
             h[i] = float_to_bf16_bits(v[j]);
         }
@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(NORM_THREADS) finalize_add_rmsnorm_router_kern
         const int i = first + j * stride;
         v[j] = 0.f;
         if (i < H) {
-            const float y = round_bf16(partial_sum(partial, sp, cm, 0, i, H, H));
+            const float y = round_bf16(partial_sum<true>(partial, sp, cm, 0, i, H, H));
             v[j] = round_bf16(bf16_bits_to_float(h[i]) + y);
             h[i] = float_to_bf16_bits(v[j]);
         }
@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(NORM_THREADS) finalize_scatter_add_rmsnorm_ker
         if (i < H) {
             // the launch holds the token's two experts: both sums are requested together
             float s0, s1;
-            partial_sum_pair(partial, sp, cm, 0, cm.col0[0] + i, cm.col0[1] + i, row, row, s0, s1);
+            partial_sum_pair<true>(partial, sp, cm, 0, cm.col0[0] + i, cm.col0[1] + i, row, row, s0, s1);
             const float y = round_bf16(round_bf16(round_bf16(s0) * route_w[0]) + round_bf16(round_bf16(s1) * route_w[1]));
             v[j] = round_bf16(bf16_bits_to_float(h[i]) + y);
             h[i] = float_to_bf16_bits(v[j]);
@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(64) finalize_qkv_rope_kernel(uint16_t* __restr
     }
     const int col = head * HEAD_DIM + d;                 // q heads, then k heads, then v heads: the row's order
     float a, b;
-    partial_sum_pair(partial, sp, cm, 0, col, col + HEAD_DIM / 2, row, row, a, b);
+    partial_sum_pair<true>(partial, sp, cm, 0, col, col + HEAD_DIM / 2, row, row, a, b);
     a = round_bf16(a);
     b = round_bf16(b);
     float o0 = a, o1 = b;
@@ -350,7 +350,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(uint16_t* __restrict__
         if (which < 3) {
             const int col = (which == 0 ? head : (which == 1 ? src.n_heads + kvh : src.n_heads + src.n_kv + kvh)) * HEAD_DIM + d;
             float a, b;
-            partial_sum_pair(src.partial, src.sp, src.cm, 0, col, col + HEAD_DIM / 2, src.row, src.row, a, b);
+            partial_sum_pair<true>(src.partial, src.sp, src.cm, 0, col, col + HEAD_DIM / 2, src.row, src.row, a, b);
             a = round_bf16(a);
             b = round_bf16(b);
             float o0 = a, o1 = b;

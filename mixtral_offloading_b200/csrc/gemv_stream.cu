@@ -568,7 +568,7 @@ __global__ void finalize_linear_kernel(uint16_t* __restrict__ y, const float* __
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < MR; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t m = i / row;
         const int n = (int)(i - m * row);
-        float v = partial_sum(partial, sp, cm, m, n, row, MR);
+        float v = partial_sum<false>(partial, sp, cm, m, n, row, MR);
         if (bias) v += bf16_bits_to_float(bias[n]);
         y[i] = float_to_bf16_bits(v);
     }
@@ -588,7 +588,7 @@ __global__ void finalize_silu_mul_kernel(uint16_t* __restrict__ h, const float* 
         const int64_t m = (i - p * MF) / F;
         const int f = (int)(i - p * MF - m * F);
         float a, b;
-        partial_sum_pair(partial, sp, cm, m, layer_col0(cm, 2 * p) + f, layer_col0(cm, 2 * p + 1) + f, row, MR, a, b);
+        partial_sum_pair<false>(partial, sp, cm, m, layer_col0(cm, 2 * p) + f, layer_col0(cm, 2 * p + 1) + f, row, MR, a, b);
         a = round_bf16(a);
         b = round_bf16(b);
         const float act = round_bf16(a / (1.f + __expf(-a)));
@@ -615,7 +615,7 @@ __global__ void finalize_scatter_kernel(uint16_t* __restrict__ out, const float*
         for (int l = 0; l < STREAM_MAX_LAYERS; ++l) {
             if (l < cm.count) {
                 const float wgt = route_w ? route_w[l * M + m] : 1.f;
-                const float v = round_bf16(round_bf16(partial_sum(partial, sp, cm, m, cm.col0[l] + n, row, MR)) * wgt);
+                const float v = round_bf16(round_bf16(partial_sum<false>(partial, sp, cm, m, cm.col0[l] + n, row, MR)) * wgt);
                 acc = (l == 0 && !accumulate) ? v : round_bf16(acc + v);
             }
         }

@@ -52,24 +52,33 @@ __device__ __forceinline__ int partial_count(const Split& sp, const ColMap& cm, 
     return sp.owner(rho_g * sp.PT + sp.PT - 1) - sp.owner(rho_g * sp.PT) + 1;
 }
 
-// Sum of the partial row-sets of element (m, col); `row` is the row length, MR = rows * row.  The row-sets
-// are read eight at a time (independent loads in flight together) and added in a fixed order.
+// Sum of the partial row-sets of element (m, col), added in a fixed order; `row` is the row length,
+// MR = rows * row.  BATCHED = false is a plain loop (the compiler groups its loads): best when a residue has
+// few row-sets (the kernels behind hqm_linear / hqm_expert_ffn).  BATCHED = true keeps eight loads in flight at
+// a time: best for the decode step's small layers, whose K dimension is cut into about twenty pieces.  (Each
+// measured a few percent slower in the other's place.)
+template <bool BATCHED>
 __device__ __forceinline__ float partial_sum(const float* __restrict__ partial, const Split& sp, const ColMap& cm,
                                              int64_t m, int col, int row, int64_t MR) {
     const int cnt = partial_count(sp, cm, col);
     const float* p = partial + m * row + col;
     float v = 0.f;
-    for (int s = 0; s < cnt; s += 8) {
-        float a[8];
+    if constexpr (!BATCHED) {
+        for (int s = 0; s < cnt; ++s) v += p[(int64_t)s * MR];
+    } else {
+        for (int s = 0; s < cnt; s += 8) {
+            float a[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) a[j] = (s + j < cnt) ? p[(int64_t)(s + j) * MR] : 0.f;
-        v += ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
+            for (int j = 0; j < 8; ++j) a[j] = (s + j < cnt) ? p[(int64_t)(s + j) * MR] : 0.f;
+            v += ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
+        }
     }
     return v;
 }
 
 // Two elements of the same row at once (a rotation pair, the gate and up halves of an FFN, the two experts of a
 // token): the row-sets of both are requested together, so the pair costs the round trips of one.
+template <bool BATCHED>
 __device__ __forceinline__ void partial_sum_pair(const float* __restrict__ partial, const Split& sp, const ColMap& cm,
                                                  int64_t m, int col_a, int col_b, int row, int64_t MR, float& out_a,
                                                  float& out_b) {
@@ -77,16 +86,26 @@ __device__ __forceinline__ void partial_sum_pair(const float* __restrict__ parti
     const float* pa = partial + m * row + col_a;
     const float* pb = partial + m * row + col_b;
     float va = 0.f, vb = 0.f;
-    const int cnt = cnt_a > cnt_b ? cnt_a : cnt_b;
-    for (int s = 0; s < cnt; s += 8) {
-        float a[8], b[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            a[j] = (s + j < cnt_a) ? pa[(int64_t)(s + j) * MR] : 0.f;
-            b[j] = (s + j < cnt_b) ? pb[(int64_t)(s + j) * MR] : 0.f;
+    if constexpr (!BATCHED) {
+        const int both = cnt_a < cnt_b ? cnt_a : cnt_b;
+        for (int s = 0; s < both; ++s) {
+            va += pa[(int64_t)s * MR];
+            vb += pb[(int64_t)s * MR];
         }
-        va += ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
-        vb += ((b[0] + b[1]) + (b[2] + b[3])) + ((b[4] + b[5]) + (b[6] + b[7]));
+        for (int s = both; s < cnt_a; ++s) va += pa[(int64_t)s * MR];
+        for (int s = both; s < cnt_b; ++s) vb += pb[(int64_t)s * MR];
+    } else {
+        const int cnt = cnt_a > cnt_b ? cnt_a : cnt_b;
+        for (int s = 0; s < cnt; s += 8) {
+            float a[8], b[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                a[j] = (s + j < cnt_a) ? pa[(int64_t)(s + j) * MR] : 0.f;
+                b[j] = (s + j < cnt_b) ? pb[(int64_t)(s + j) * MR] : 0.f;
+            }
+            va += ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
+            vb += ((b[0] + b[1]) + (b[2] + b[3])) + ((b[4] + b[5]) + (b[6] + b[7]));
+        }
     }
     out_a = va;
     out_b = vb;

@@ -1,0 +1,93 @@
+"""Greedy single-sequence decoding on top of DecoderLayerDecode: embedding lookup, the decoder layers (one
+library call each), lm_head and argmax, with the step optionally replayed from a CUDA graph.
+
+The reference generates through Hugging Face's `generate` on the model that src/build_model.py:166-241
+assembles (notebooks/demo.ipynb).  Here a token is one fixed sequence of launches: the position lives in
+device memory, the experts are picked on the device, nothing returns to the host inside a step.  The prompt is
+fed through the same single-token step (no separate prefill path).
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import torch
+from torch import nn
+
+from .decoder import DecoderLayerDecode, add_rmsnorm
+
+
+class MixtralDecodeModel(nn.Module):
+    """embed: (vocab, hidden) bf16; layers: DecoderLayerDecode, each built with next_ln = the following layer's
+    input norm weight (the last one with the final norm weight); first_ln: layer 0's input norm weight;
+    lm_head: (vocab, hidden) bf16."""
+
+    def __init__(self, embed: torch.Tensor, layers: Sequence[DecoderLayerDecode], first_ln: torch.Tensor,
+                 lm_head: torch.Tensor, rms_eps: float = 1e-5):
+        super().__init__()
+        self.embed, self.first_ln, self.lm_head, self.rms_eps = embed, first_ln, lm_head, rms_eps
+        self.layers = nn.ModuleList(layers)
+        dev = embed.device
+        self.token = torch.zeros((1,), dtype=torch.int64, device=dev)     # the token being fed
+        self.position = torch.zeros((1,), dtype=torch.int32, device=dev)   # its position
+        self.router_logits: List[torch.Tensor] = []
+        self._graph = None
+        self._logits = None
+
+    @property
+    def max_len(self) -> int:
+        return min(l.attention.max_len for l in self.layers)
+
+    @torch.inference_mode()
+    def step(self) -> torch.Tensor:
+        """Feeds self.token at self.position through the model; afterwards self.token is the greedy next token
+        and self.position has advanced.  Returns the logits (1, vocab)."""
+        h = self.embed[self.token]                                         # (1, hidden), a fresh tensor
+        x = add_rmsnorm(h, None, self.first_ln, self.rms_eps)
+        self.router_logits = [layer(h, x, self.position) for layer in self.layers]
+        logits = torch.matmul(x, self.lm_head.t())     # x is the final norm of h after the last layer
+        self.token.copy_(logits.argmax(-1))
+        self.position.add_(1)
+        return logits
+
+    @torch.inference_mode()
+    def capture(self, warmup: int = 2) -> None:
+        """Records step() into a CUDA graph; replay() then runs a whole token with one launch from the host."""
+        tok, pos = self.token.clone(), self.position.clone()
+        side = torch.cuda.Stream(self.embed.device)
+        side.wait_stream(torch.cuda.current_stream(self.embed.device))
+        with torch.cuda.stream(side):
+            for _ in range(warmup):                                        # settle allocations and scratch sizes
+                self.step()
+        torch.cuda.current_stream(self.embed.device).wait_stream(side)
+        self.token.copy_(tok)
+        self.position.copy_(pos)
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._logits = self.step()
+        self.token.copy_(tok)                                              # capture does not execute, but keep it explicit
+        self.position.copy_(pos)
+
+    def replay(self) -> torch.Tensor:
+        if self._graph is None:
+            raise RuntimeError("capture() has not been called")
+        self._graph.replay()
+        return self._logits
+
+    @torch.inference_mode()
+    def generate(self, prompt_ids: Sequence[int], new_tokens: int, use_graph: bool = True) -> List[int]:
+        """Greedy continuation of prompt_ids (fed token by token from position 0)."""
+        if len(prompt_ids) == 0 or len(prompt_ids) + new_tokens > self.max_len:
+            raise ValueError(f"prompt of {len(prompt_ids)} + {new_tokens} new tokens does not fit a cache of {self.max_len}")
+        if use_graph and self._graph is None:
+            self.capture()
+        run = self.replay if use_graph else self.step
+        self.position.zero_()
+        out: List[int] = []
+        for i, t in enumerate(prompt_ids):
+            self.token.fill_(int(t))
+            run()
+        out.append(int(self.token.item()))
+        for _ in range(new_tokens - 1):
+            run()
+            out.append(int(self.token.item()))
+        return out

@@ -5,7 +5,8 @@ import math
 import pytest
 import torch
 
-from mixtral_offloading_b200 import AttentionDecode, DecoderLayerDecode, ResidentMoe, add_rmsnorm
+from mixtral_offloading_b200 import (AttentionDecode, DecoderLayerDecode, MixtralDecodeModel, ResidentMoe,
+                                     add_rmsnorm)
 from oracle import hqq_oracle as O
 from tests.helpers import layer_from_oracle, random_layer
 
@@ -201,3 +202,33 @@ def test_fused_decoder_layer_matches_the_two_separate_calls():
         assert rel(mod2.k_cache[:, step], mod.k_cache[:, step].float().cpu()) < 1e-2
         assert rel(mod2.v_cache[:, step], mod.v_cache[:, step].float().cpu()) < 1e-2
         pos += 1
+
+
+def test_generate_graph_and_eager_agree_and_repeat():
+    """Two small layers, greedy generation: replaying the captured step gives the tokens of the eager step, twice."""
+    from tests.test_gpu_parity import make_expert
+    n_heads, n_kv, ffn, E, max_len, vocab, L = 4, 2, 1792, 8, 64, 500, 2
+    hidden = n_heads * HD
+    g = torch.Generator().manual_seed(12)
+    lns = [(1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16).to(DEV) for _ in range(L + 1)]
+    layers = []
+    for l in range(L):
+        attn, _, _ = build(n_heads, n_kv, max_len, seed=31 + 7 * l)
+        experts = [make_expert(hidden, ffn, (random_layer(ffn, hidden, 2, 16, 300 + 30 * l + 3 * e),
+                                             random_layer(hidden, ffn, 2, 16, 301 + 30 * l + 3 * e),
+                                             random_layer(ffn, hidden, 2, 16, 302 + 30 * l + 3 * e))) for e in range(E)]
+        gate = torch.nn.Linear(hidden, E, bias=False, dtype=torch.bfloat16, device=DEV)
+        gate.weight.data.copy_((0.5 * torch.randn(E, hidden, generator=g)).to(torch.bfloat16))
+        layers.append(DecoderLayerDecode(attn, ResidentMoe(_Cfg(hidden, ffn, E), l, gate, experts), lns[l + 1]))
+    embed = torch.randn(vocab, hidden, generator=g).to(torch.bfloat16).to(DEV)
+    head = (0.05 * torch.randn(vocab, hidden, generator=g)).to(torch.bfloat16).to(DEV)
+    model = MixtralDecodeModel(embed, layers, lns[0], head)
+    prompt = [3, 141, 59, 26, 5]
+    eager = model.generate(prompt, 12, use_graph=False)
+    graphed = model.generate(prompt, 12, use_graph=True)
+    again = model.generate(prompt, 12, use_graph=True)
+    assert len(eager) == 12 and all(0 <= t < vocab for t in eager)
+    assert graphed == eager and again == eager
+    assert int(model.position.item()) == len(prompt) + 11
+    with pytest.raises(ValueError):
+        model.generate(prompt, max_len)
