@@ -64,20 +64,6 @@ struct Cfg {
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-// bf16 pairs 128 + code of the ten slots for two adjacent columns (words w0, w1).  lo holds the low halves of
-// both words (slots 9..5 at bits 0, 3, .., 12 of each half), hi the same of the words >> 15 (slots 4..0).
-__device__ __forceinline__ void ten_bf16_pairs(uint32_t w0, uint32_t w1, uint32_t mask, uint32_t magic,
-                                               uint32_t (&out)[10]) {
-    uint32_t lo, hi;
-    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(lo) : "r"(w0), "r"(w1));
-    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(hi) : "r"(w0 >> 15), "r"(w1 >> 15));
-#pragma unroll
-    for (int j = 0; j < 5; ++j) {
-        out[9 - j] = lop_and_or(lo >> (3 * j), mask, magic);
-        out[4 - j] = lop_and_or(hi >> (3 * j), mask, magic);
-    }
-}
-
 template <int NTOK>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc3_kernel(Params prm) {
@@ -141,50 +127,84 @@ gemm_tc3_kernel(Params prm) {
             unsigned char* sA = tiles + (size_t)s * CF::STAGE_BYTES;
             unsigned char* sB = sA + CF::A_BYTES;
             const int k0 = it * BK;
-            // ---- the tokens' 64 columns of x (requested first: their latency overlaps the dequantisation)
-            constexpr int XT = NTOK * 8 / PRODUCERS;
+            // ---- every load a thread can hold is requested before anything is computed: the packed words, the
+            // (S, T) rows of five slots at a time, and (64-token tile only) the x chunks
+            constexpr bool X_EARLY = NTOK <= 64;
+            constexpr int XT = X_EARLY ? NTOK * 8 / PRODUCERS : 1;
             uint4 xv[XT];
+            if constexpr (X_EARLY) {
 #pragma unroll
-            for (int q = 0; q < XT; ++q) {
-                const int task = tid + q * PRODUCERS;
-                const int tok = task >> 3, ch = task & 7;
-                xv[q] = make_uint4(0u, 0u, 0u, 0u);
-                if (tok < prm.M) {
-                    const int mm = prm.m_base + tok;
-                    const int64_t xrow = prm.x_idx ? prm.x_idx[mm] : mm;
-                    xv[q] = *reinterpret_cast<const uint4*>(prm.x + xrow * K + k0 + 8 * ch);
+                for (int q = 0; q < XT; ++q) {
+                    const int task = tid + q * PRODUCERS;
+                    const int tok = task >> 3, ch = task & 7;
+                    xv[q] = make_uint4(0u, 0u, 0u, 0u);
+                    if (tok < prm.M) {
+                        const int mm = prm.m_base + tok;
+                        const int64_t xrow = prm.x_idx ? prm.x_idx[mm] : mm;
+                        xv[q] = *reinterpret_cast<const uint4*>(prm.x + xrow * K + k0 + 8 * ch);
+                    }
                 }
             }
             // ---- dequantise 10 rows x 8 columns
             if (has_task) {
                 const uint32_t* src = Wq + (int64_t)R * K + k0 + 8 * c;
                 const uint4 pa = ld_stream_16(src), pb = ld_stream_16(src + 4);
-                uint32_t code[4][10];                                   // [column pair][slot]
-                ten_bf16_pairs(pa.x, pa.y, mask, magic, code[0]);
-                ten_bf16_pairs(pa.z, pa.w, mask, magic, code[1]);
-                ten_bf16_pairs(pb.x, pb.y, mask, magic, code[2]);
-                ten_bf16_pairs(pb.z, pb.w, mask, magic, code[3]);
-                uint32_t r = r_first;
+                // two adjacent columns per register: lo = low halves of both words (slots 9..5 at bits 0, 3, .., 12 of
+                // each half), hi = the same of the words >> 15 (slots 4..0)
+                const uint32_t w[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+                uint32_t lo[4], hi[4];
 #pragma unroll
-                for (int sl = 0; sl < 10; ++sl) {
-                    if (n_first + sl < N) {
+                for (int cp = 0; cp < 4; ++cp) {
+                    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(lo[cp]) : "r"(w[2 * cp]), "r"(w[2 * cp + 1]));
+                    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(hi[cp]) : "r"(w[2 * cp] >> 15), "r"(w[2 * cp + 1] >> 15));
+                }
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {                  // slots 0..4 (from hi), then 5..9 (from lo)
+                    uint4 sv[5], tv[5];
+#pragma unroll
+                    for (int q = 0; q < 5; ++q) {
+                        const int sl = 5 * half + q;
+                        uint32_t r = r_first + (uint32_t)sl;
+                        r = r >= (uint32_t)G ? r - (uint32_t)G : r;
+                        if (r >= (uint32_t)G) r %= (uint32_t)G;         // only layers with fewer than ten groups
                         const size_t off = (size_t)r * K + k0 + 8 * c;
-                        const uint4 sv = *reinterpret_cast<const uint4*>(prm.S + off);
-                        const uint4 tv = *reinterpret_cast<const uint4*>(prm.T + off);
-                        uint4 o;
-                        o.x = bf2_fma(bf2_sub(code[0][sl], magic), sv.x, tv.x);
-                        o.y = bf2_fma(bf2_sub(code[1][sl], magic), sv.y, tv.y);
-                        o.z = bf2_fma(bf2_sub(code[2][sl], magic), sv.z, tv.z);
-                        o.w = bf2_fma(bf2_sub(code[3][sl], magic), sv.w, tv.w);
-                        *reinterpret_cast<uint4*>(sA + sw128(10 * i + sl, c)) = o;
+                        const bool ok = n_first + sl < N;
+                        sv[q] = ok ? *reinterpret_cast<const uint4*>(prm.S + off) : make_uint4(0u, 0u, 0u, 0u);
+                        tv[q] = ok ? *reinterpret_cast<const uint4*>(prm.T + off) : make_uint4(0u, 0u, 0u, 0u);
                     }
-                    r = (r + 1 == (uint32_t)G) ? 0u : r + 1;
+#pragma unroll
+                    for (int q = 0; q < 5; ++q) {
+                        const int sl = 5 * half + q;
+                        const int sh = 3 * ((half ? 9 : 4) - sl);       // slot 4 / 9 sits at bit 0 of its half
+                        const uint32_t* from = half ? lo : hi;
+                        uint4 o;
+                        o.x = bf2_fma(bf2_sub(lop_and_or(from[0] >> sh, mask, magic), magic), sv[q].x, tv[q].x);
+                        o.y = bf2_fma(bf2_sub(lop_and_or(from[1] >> sh, mask, magic), magic), sv[q].y, tv[q].y);
+                        o.z = bf2_fma(bf2_sub(lop_and_or(from[2] >> sh, mask, magic), magic), sv[q].z, tv[q].z);
+                        o.w = bf2_fma(bf2_sub(lop_and_or(from[3] >> sh, mask, magic), magic), sv[q].w, tv[q].w);
+                        if (n_first + sl < N) *reinterpret_cast<uint4*>(sA + sw128(10 * i + sl, c)) = o;
+                    }
                 }
             }
+            // ---- the tokens' 64 columns of x
+            if constexpr (X_EARLY) {
 #pragma unroll
-            for (int q = 0; q < XT; ++q) {
-                const int task = tid + q * PRODUCERS;
-                *reinterpret_cast<uint4*>(sB + sw128(task >> 3, task & 7)) = xv[q];
+                for (int q = 0; q < XT; ++q) {
+                    const int task = tid + q * PRODUCERS;
+                    *reinterpret_cast<uint4*>(sB + sw128(task >> 3, task & 7)) = xv[q];
+                }
+            } else {
+#pragma unroll 4
+                for (int task = tid; task < NTOK * 8; task += PRODUCERS) {
+                    const int tok = task >> 3, ch = task & 7;
+                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                    if (tok < prm.M) {
+                        const int mm = prm.m_base + tok;
+                        const int64_t xrow = prm.x_idx ? prm.x_idx[mm] : mm;
+                        v = *reinterpret_cast<const uint4*>(prm.x + xrow * K + k0 + 8 * ch);
+                    }
+                    *reinterpret_cast<uint4*>(sB + sw128(tok, ch)) = v;
+                }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor core
             mbar_arrive(full + s);
