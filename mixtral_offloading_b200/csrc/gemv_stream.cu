@@ -713,16 +713,16 @@ bool gemv_stream_plan(const hqm_weight* const* ws, int count, int64_t M, StreamP
     plan->PT = w->K / pw;
     const int64_t total = (int64_t)plan->rho0[count] * plan->PT;
     // Whole CTAs per SM, so that every SM carries the same load; fewer of them (and, for small layers,
-    // fewer SMs) rather than ranges shorter than ~3 passes, each of which costs a partial row-set.
+    // fewer SMs) rather than ranges shorter than ~2 passes, each of which costs a partial row-set.
     {
         int dev = 0, sms = 148;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         int per_sm = grid / sms;
-        const int64_t want = total / ((int64_t)sms * 8 * 3);
+        const int64_t want = total / ((int64_t)sms * 8 * 2);
         if (per_sm > want) per_sm = (int)(want < 1 ? 1 : want);
         grid = per_sm * sms;
-        if ((int64_t)grid * 8 * 3 > total) grid = (int)(total / (8 * 3));
+        if ((int64_t)grid * 8 * 2 > total) grid = (int)(total / (8 * 2));
         if (grid < 1) grid = 1;
         if ((int64_t)grid * 8 > total) return false;
     }
