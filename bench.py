@@ -12,7 +12,7 @@ sequence on its own replica (no data-path collective) and the value is the sum o
 --workload expert is BASELINE.json configs[1] (one expert FFN per step, --tokens rows), --workload moe one
 expert-parallel MoE block per step, --workload offload the ExpertCache with half the experts in host memory.
 
-One JSON line is printed by rank 0; see DESIGN.md for the meaning of each key.
+One JSON line is printed by rank 0.
 """
 from __future__ import annotations
 
@@ -576,7 +576,7 @@ def run_decode(args):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
                      "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this "
-                     "kernel and shape (profiles/gemv_stream_2bit_g16_14336x4096_m1.md); not re-measured by this run",
+                     "kernel and shape (the committed ncu summary under profiles/); not re-measured by this run",
                      "kernel": "quantized linear 14336x4096 2-bit g16 (w1/w3 of layer 0's experts, "
                      f"354 MB rotated), fastest of 3 runs of {reps} launches, CUDA events", "algorithmic_bytes": lin_bytes,
                      "us_per_launch": kernel_ms * 1e3, "peak_kind": f"{peak_kind} HBM copy bandwidth",

@@ -33,7 +33,9 @@ from torch import nn
 from torch.nn import functional as F
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: python make_golden.py <path of the dvmazur/mixtral-offloading checkout>")
+REF = sys.argv[1]
 sys.path.insert(0, HERE)
 sys.path.insert(0, REF)
 
