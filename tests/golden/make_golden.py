@@ -2,7 +2,7 @@
 
 Run where the reference tree is available (it is not on the GPU box):
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 It imports the reference's src/packing.py, src/custom_layers.py,
 src/expert_cache.py and src/expert_wrapper.py on the CPU under ref_shim.py
