@@ -261,6 +261,21 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
         grid_dependency_wait();
         synced = true;
     }
+    // Table mode: the (up to four) descriptors the router's choice points at are fetched once per CTA into
+    // shared memory, so that a warp starting a segment does not sit through an index load and a dependent
+    // descriptor load before it can request its first weights.
+    __shared__ hqm_weight s_desc[STREAM_MAX_LAYERS];
+    if (ly.table) {
+        constexpr int WORDS = (int)(sizeof(hqm_weight) / sizeof(uint32_t));
+        if ((int)threadIdx.x < ly.count * WORDS) {
+            const int l = threadIdx.x / WORDS, i = threadIdx.x % WORDS;
+            // (__ldcg: the index may have been written by a kernel that finished while an earlier kernel on this
+            // SM still had the previous value in L1)
+            const hqm_weight* src = ly.table + 3 * __ldcg(ly.sel[l]) + ly.which[l];
+            reinterpret_cast<uint32_t*>(s_desc)[threadIdx.x] = reinterpret_cast<const uint32_t*>(src)[i];
+        }
+        __syncthreads();
+    }
 
     // token rows that exist only to fill a column tile, and the extra z row, stay zero for the whole kernel
     for (int i = lane; i < S::WARP_HALFS / 2; i += 32) reinterpret_cast<uint32_t*>(xs_w)[i] = 0u;
@@ -288,9 +303,7 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
         for (int l = 1; l < STREAM_MAX_LAYERS; ++l) layer += (l < ly.count && rho_g >= ly.rho0[l]) ? 1 : 0;
         const int rho = rho_g - ly.rho0[layer];
         const int P = ly.rho0[layer + 1] - ly.rho0[layer], G = ly.G[layer], C = ly.C[layer];
-        // (__ldcg: the index may have been written by a kernel that finished while an earlier kernel on this SM
-        // still had the previous value in L1)
-        const hqm_weight w = ly.table ? ly.table[3 * __ldcg(ly.sel[layer]) + ly.which[layer]] : ly.w[layer];
+        const hqm_weight w = ly.table ? s_desc[layer] : ly.w[layer];
         uint32_t qoff[NB];                          // this lane's weight rows, bytes from W_q + rho*K + k0
 #pragma unroll
         for (int b = 0; b < NB; ++b) qoff[b] = (uint32_t)(16 * b + g) * (uint32_t)P * (uint32_t)K + 16u * t;
