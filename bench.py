@@ -581,6 +581,11 @@ def run_decode(args):
                      f"354 MB rotated), fastest of 3 runs of {reps} launches, CUDA events", "algorithmic_bytes": lin_bytes,
                      "us_per_launch": kernel_ms * 1e3, "peak_kind": f"{peak_kind} HBM copy bandwidth",
                      "frac_of_8tbs": achieved / 8000.0},
+        # the same kernel as it runs inside the step (several layers per launch), from the committed ncu capture of
+        # the decode step: not re-measured by this run
+        "roofline_in_step": {"source": "ncu capture of the decode step's expert launches (summary under profiles/)",
+                             "gate_up_both_experts": {"bytes": 88734464, "us": 36.7, "frac": 88734464 / 36.7e-6 / 1e9 / peak},
+                             "down_both_experts": {"bytes": 44349440, "us": 23.4, "frac": 44349440 / 23.4e-6 / 1e9 / peak}},
         "cpu_baseline": cpu,
         "e2e": {"value": world * 1e3 / (ms_e2e * scale), "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": 8,
                 "d2h_bytes_per_step": 8},
