@@ -539,6 +539,17 @@ def run_decode(args):
             barrier()
             kernel_ms = min(kernel_ms, k0.elapsed_time(k1) / reps)
         clocks = sampler.stop() if sampler is not None else None
+        # prompt processing through the same model: a 512-token prompt in one pass (informative, rank 0 only)
+        prefill_ms = None
+        if rank == 0 and args.context >= 512 and max_len > 512:
+            prompt = torch.randint(0, V, (512,), generator=torch.Generator().manual_seed(3)).tolist()
+            model.prefill(prompt)                                          # warm-up (allocations, scratch)
+            p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            p0.record(stream)
+            model.prefill(prompt)
+            p1.record(stream)
+            torch.cuda.synchronize(dev)
+            prefill_ms = p0.elapsed_time(p1)
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -586,6 +597,7 @@ def run_decode(args):
         "roofline_in_step": {"source": "ncu capture of the decode step's expert launches (summary under profiles/)",
                              "gate_up_both_experts": {"bytes": 88734464, "us": 36.7, "frac": 88734464 / 36.7e-6 / 1e9 / peak},
                              "down_both_experts": {"bytes": 44349440, "us": 23.4, "frac": 44349440 / 23.4e-6 / 1e9 / peak}},
+        "prefill_512_tokens_ms": prefill_ms,
         "cpu_baseline": cpu,
         "e2e": {"value": world * 1e3 / (ms_e2e * scale), "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": 8,
                 "d2h_bytes_per_step": 8},

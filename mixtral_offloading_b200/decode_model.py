@@ -4,7 +4,8 @@ library call each), lm_head and argmax, with the step optionally replayed from a
 The reference generates through Hugging Face's `generate` on the model that src/build_model.py:166-241
 assembles (notebooks/demo.ipynb).  Here a token is one fixed sequence of launches: the position lives in
 device memory, the experts are picked on the device, nothing returns to the host inside a step.  The prompt is
-fed through the same single-token step (no separate prefill path).
+either fed through the same single-token step or processed in one pass (prefill(): the quantized linears on
+their many-row path, torch's attention over the prompt).
 """
 from __future__ import annotations
 
@@ -73,19 +74,77 @@ class MixtralDecodeModel(nn.Module):
         self._graph.replay()
         return self._logits
 
+    # ---- prompt processing: all prompt tokens at once --------------------------------------------------
+    def _rms(self, h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        v = h.float()
+        v = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.rms_eps)).to(torch.bfloat16)
+        return w * v
+
+    @staticmethod
+    def _rope(t: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor:
+        """t: (T, heads, head_dim) bf16; rotate-half RoPE with bf16 cos / sin, as the decode kernel applies it."""
+        hd = t.shape[-1]
+        inv = theta ** (-torch.arange(0, hd, 2, dtype=torch.float32, device=t.device) / hd)
+        ang = positions.float()[:, None] * inv[None, :]
+        cos = torch.cat([ang.cos(), ang.cos()], -1).to(torch.bfloat16)[:, None, :]
+        sin = torch.cat([ang.sin(), ang.sin()], -1).to(torch.bfloat16)[:, None, :]
+        rot = torch.cat([-t[..., hd // 2:], t[..., :hd // 2]], -1)
+        return t * cos + rot * sin
+
     @torch.inference_mode()
-    def generate(self, prompt_ids: Sequence[int], new_tokens: int, use_graph: bool = True) -> List[int]:
-        """Greedy continuation of prompt_ids (fed token by token from position 0)."""
+    def prefill(self, prompt_ids: Sequence[int]) -> torch.Tensor:
+        """Runs the whole prompt through the model in one pass (the quantized linears take the many-row
+        tensor-core path, attention over the prompt is torch's scaled_dot_product_attention, the MoE block
+        groups the tokens per expert), fills the KV caches for positions 0..T-1, leaves self.position = T and
+        self.token = the greedy next token.  Returns the logits of the last prompt position (1, vocab)."""
+        T = len(prompt_ids)
+        if T == 0 or T >= self.max_len:
+            raise ValueError(f"a prompt of {T} tokens does not fit a cache of {self.max_len}")
+        dev = self.embed.device
+        ids = torch.tensor(list(prompt_ids), dtype=torch.int64, device=dev)
+        positions = torch.arange(T, device=dev)
+        h = self.embed[ids]                                                # (T, hidden)
+        hidden = h.shape[-1]
+        for li, layer in enumerate(self.layers):
+            a = layer.attention
+            # the norm in front of a layer is what the decode step applies: first_ln, then each layer's next_ln
+            x = self._rms(h, self.first_ln if li == 0 else self.layers[li - 1].next_ln)
+            q = a.q_proj(x).view(T, a.n_heads, a.head_dim)
+            k = a.k_proj(x).view(T, a.n_kv_heads, a.head_dim)
+            v = a.v_proj(x).view(T, a.n_kv_heads, a.head_dim)
+            q, k = self._rope(q, positions, a.rope_theta), self._rope(k, positions, a.rope_theta)
+            a.k_cache[:, :T] = k.transpose(0, 1)
+            a.v_cache[:, :T] = v.transpose(0, 1)
+            ctx = torch.nn.functional.scaled_dot_product_attention(
+                q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0), v.transpose(0, 1).unsqueeze(0),
+                is_causal=True, enable_gqa=True)                           # (1, heads, T, head_dim)
+            h = h + a.o_proj(ctx[0].transpose(0, 1).reshape(T, hidden))
+            y, _ = layer.moe(self._rms(h, a.ln_post).view(1, T, hidden))
+            h = h + y.view(T, hidden)
+        last_ln = self.layers[-1].next_ln
+        logits = torch.matmul(self._rms(h[-1:], last_ln), self.lm_head.t())
+        self.token.copy_(logits.argmax(-1))
+        self.position.fill_(T)
+        return logits
+
+    @torch.inference_mode()
+    def generate(self, prompt_ids: Sequence[int], new_tokens: int, use_graph: bool = True,
+                 prefill: bool = False) -> List[int]:
+        """Greedy continuation of prompt_ids.  The prompt is fed token by token through the decode step, or,
+        with prefill=True, in one pass through prefill()."""
         if len(prompt_ids) == 0 or len(prompt_ids) + new_tokens > self.max_len:
             raise ValueError(f"prompt of {len(prompt_ids)} + {new_tokens} new tokens does not fit a cache of {self.max_len}")
         if use_graph and self._graph is None:
             self.capture()
         run = self.replay if use_graph else self.step
-        self.position.zero_()
         out: List[int] = []
-        for i, t in enumerate(prompt_ids):
-            self.token.fill_(int(t))
-            run()
+        if prefill:
+            self.prefill(prompt_ids)
+        else:
+            self.position.zero_()
+            for t in prompt_ids:
+                self.token.fill_(int(t))
+                run()
         out.append(int(self.token.item()))
         for _ in range(new_tokens - 1):
             run()

@@ -232,3 +232,39 @@ def test_generate_graph_and_eager_agree_and_repeat():
     assert int(model.position.item()) == len(prompt) + 11
     with pytest.raises(ValueError):
         model.generate(prompt, max_len)
+
+
+def test_prefill_matches_feeding_the_prompt_token_by_token():
+    """prefill() fills the caches and predicts the next token like the single-token step fed with the prompt."""
+    from tests.test_gpu_parity import make_expert
+    n_heads, n_kv, ffn, E, max_len, vocab, L = 4, 2, 1792, 8, 64, 300, 2
+    hidden = n_heads * HD
+    g = torch.Generator().manual_seed(77)
+    lns = [(1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16).to(DEV) for _ in range(L + 1)]
+    layers = []
+    for l in range(L):
+        attn, _, _ = build(n_heads, n_kv, max_len, seed=51 + 7 * l)
+        experts = [make_expert(hidden, ffn, (random_layer(ffn, hidden, 2, 16, 500 + 30 * l + 3 * e),
+                                             random_layer(hidden, ffn, 2, 16, 501 + 30 * l + 3 * e),
+                                             random_layer(ffn, hidden, 2, 16, 502 + 30 * l + 3 * e))) for e in range(E)]
+        gate = torch.nn.Linear(hidden, E, bias=False, dtype=torch.bfloat16, device=DEV)
+        gate.weight.data.copy_((0.5 * torch.randn(E, hidden, generator=g)).to(torch.bfloat16))
+        layers.append(DecoderLayerDecode(attn, ResidentMoe(_Cfg(hidden, ffn, E), l, gate, experts), lns[l + 1]))
+    embed = torch.randn(vocab, hidden, generator=g).to(torch.bfloat16).to(DEV)
+    head = (0.05 * torch.randn(vocab, hidden, generator=g)).to(torch.bfloat16).to(DEV)
+    model = MixtralDecodeModel(embed, layers, lns[0], head)
+    prompt = [int(v) for v in torch.randint(0, vocab, (20,), generator=g)]
+    # token by token
+    model.position.zero_()
+    for tkn in prompt:
+        model.token.fill_(tkn)
+        logits_step = model.step().float().cpu()
+    caches_step = [(l.attention.k_cache[:, :20].float().cpu(), l.attention.v_cache[:, :20].float().cpu()) for l in layers]
+    # one pass
+    logits_pre = model.prefill(prompt).float().cpu()
+    assert int(model.position.item()) == 20
+    # bf16 noise compounds through the layers and a router near-tie may flip for some token: compare loosely
+    assert rel(caches_step[0][0], layers[0].attention.k_cache[:, :20].float().cpu()) < 2e-2   # layer 0 sees equal inputs
+    assert rel(caches_step[0][1], layers[0].attention.v_cache[:, :20].float().cpu()) < 2e-2
+    assert rel(logits_pre, logits_step) < 0.15
+    assert len(model.generate(prompt, 5, prefill=True)) == 5
