@@ -21,14 +21,23 @@ from . import _cabi, packing
 from .quantize import affine_quantize, meta_template
 
 _SCRATCH: Dict[Any, torch.Tensor] = {}
+_SCRATCH_RETIRED: list = []
 
 
 def _scratch(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Grow-only per-device workspace handed to the library (which never allocates)."""
+    """Grow-only per-device workspace handed to the library (which never allocates).
+
+    A buffer that has been outgrown is kept alive, not freed: a captured CUDA graph may still hold its address
+    (a decode step captured before a larger request, e.g. a long prompt, arrives).  Growth is geometric, so the
+    retired buffers together stay below the size of the current one."""
     key = (device.type, device.index)
     buf = _SCRATCH.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        size = max(nbytes, 1 << 20, 0 if buf is None else 2 * buf.numel())
+        if buf is not None:
+            _SCRATCH_RETIRED.append(buf)
+        with torch.inference_mode(False):
+            buf = torch.empty(size, dtype=torch.uint8, device=device)
         _SCRATCH[key] = buf
     return buf
 

@@ -226,6 +226,13 @@ def test_generate_graph_and_eager_agree_and_repeat():
     prompt = [3, 141, 59, 26, 5]
     eager = model.generate(prompt, 12, use_graph=False)
     graphed = model.generate(prompt, 12, use_graph=True)
+    # a larger workspace request after the capture (a long prompt, say) must not pull the captured step's
+    # workspace from under it: the outgrown buffer stays alive
+    from mixtral_offloading_b200.custom_layers import _SCRATCH, _scratch
+    old_buf = _SCRATCH[("cuda", 0)]
+    new_buf = _scratch(DEV, 4 * old_buf.numel())
+    assert new_buf.data_ptr() != old_buf.data_ptr() and new_buf.numel() >= 4 * old_buf.numel()
+    new_buf.fill_(0xFF)
     again = model.generate(prompt, 12, use_graph=True)
     assert len(eager) == 12 and all(0 <= t < vocab for t in eager)
     assert graphed == eager and again == eager
