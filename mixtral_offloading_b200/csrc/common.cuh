@@ -44,6 +44,14 @@ void count_launch();
         }                                                                                 \
     } while (0)
 
+// Index of the current device for per-device caches (function attributes and occupancy are per device).
+constexpr int MAX_DEVICES = 64;
+inline int current_device_slot() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return (dev >= 0 && dev < MAX_DEVICES) ? dev : 0;
+}
+
 __host__ __device__ constexpr int codes_per_word(int nbits) { return nbits == 2 ? 4 : (nbits == 4 ? 2 : 10); }
 
 // Storage rows of W_q for N output rows.

@@ -346,7 +346,8 @@ static inline bool tc_aligned16(const void* p) { return (reinterpret_cast<uintpt
 // Device-side failure flag of the bounded waits (read by hqm_device_error()).
 static __device__ int g_tc_error = 0;
 int* tc_error_ptr() {
-    static int* ptr = nullptr;
+    static int* ptrs[MAX_DEVICES];                 // the flag of the current device (one copy per device)
+    int*& ptr = ptrs[current_device_slot()];
     if (!ptr) {
         void* p = nullptr;
         if (cudaGetSymbolAddress(&p, g_tc_error) == cudaSuccess) ptr = (int*)p;
@@ -380,7 +381,8 @@ template <int NBITS, int NB, int NTOK>
 static int launch_tc(const tc::Params& p, int grid, cudaStream_t st) {
     using CF = tc::Cfg<NBITS, NB, NTOK>;
     auto kern = tc::gemm_tc_kernel<NBITS, NB, NTOK>;
-    static bool attr_set = false;
+    static bool attr_done[MAX_DEVICES];
+    bool& attr_set = attr_done[current_device_slot()];
     if (!attr_set) {
         HQM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CF::SMEM));
         attr_set = true;

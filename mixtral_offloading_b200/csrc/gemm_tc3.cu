@@ -300,7 +300,8 @@ template <int NTOK>
 static int launch_tc3(const tc3::Params& p, int grid, cudaStream_t st) {
     using CF = tc3::Cfg<NTOK>;
     auto kern = tc3::gemm_tc3_kernel<NTOK>;
-    static bool attr_set = false;
+    static bool attr_done[MAX_DEVICES];
+    bool& attr_set = attr_done[current_device_slot()];
     if (!attr_set) {
         HQM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CF::SMEM));
         attr_set = true;

@@ -639,29 +639,32 @@ __global__ void finalize_scatter_kernel(uint16_t* __restrict__ out, const float*
 // --------------------------------------------------------------------------- host side
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Resident CTAs per SM of an instantiation, times the SM count (queried once).
+// Resident CTAs per SM of an instantiation, times the SM count (queried once per device).
 template <int NBITS, int NB, int TOKS>
 static int resident_grid() {
     using S = Shape<NBITS, NB, TOKS>;
-    static int cached = -1;
-    if (cached >= 0) return cached;
-    cached = 0;
-    auto kern = gemv_stream_kernel<NBITS, NB, TOKS>;
-    const size_t smem = S::smem_bytes();
-    if (smem > 227 * 1024) return 0;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-        cudaGetLastError();
-        return 0;
-    }
-    int per_sm = 0, dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 256, smem) != cudaSuccess || per_sm < 1) {
-        cudaGetLastError();
-        return 0;
-    }
-    cached = per_sm * sms;
-    return cached;
+    static int per_device[MAX_DEVICES];          // 0: not queried yet, otherwise grid + 1
+    int& slot = per_device[current_device_slot()];
+    if (slot > 0) return slot - 1;
+    const int grid = [] {
+        auto kern = gemv_stream_kernel<NBITS, NB, TOKS>;
+        const size_t smem = S::smem_bytes();
+        if (smem > 227 * 1024) return 0;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            cudaGetLastError();
+            return 0;
+        }
+        int per_sm = 0, dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 256, smem) != cudaSuccess || per_sm < 1) {
+            cudaGetLastError();
+            return 0;
+        }
+        return per_sm * sms;
+    }();
+    slot = grid + 1;
+    return grid;
 }
 
 // Rows of x one launch decodes for `tokens` pending rows.

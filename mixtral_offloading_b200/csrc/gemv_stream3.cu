@@ -260,7 +260,9 @@ bool gemv_stream3_plan(const hqm_weight* w, int G, int C, int64_t M, Stream3Plan
     const void* ptrs[] = {w->W_q, w->scale_q, w->zero_q, w->ms_scale, w->mz_scale, w->ms_zero, w->mz_zero};
     for (const void* p : ptrs)
         if ((reinterpret_cast<uintptr_t>(p) & 15u) != 0) return false;
-    static int resident = -1;
+    static int resident_dev[MAX_DEVICES];         // 0: not queried yet, otherwise CTAs per SM + 1
+    int& res_slot = resident_dev[current_device_slot()];
+    int resident = res_slot - 1;
     const size_t smem = (size_t)s3::NW * s3::WARP_HALFS * sizeof(__half);
     if (resident < 0) {
         resident = 0;
@@ -270,6 +272,7 @@ bool gemv_stream3_plan(const hqm_weight* w, int G, int C, int64_t M, Stream3Plan
             resident = per_sm;
         else
             cudaGetLastError();
+        res_slot = resident + 1;
     }
     if (resident < 1) return false;
     int dev = 0, sms = 148;

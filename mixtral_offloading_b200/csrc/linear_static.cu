@@ -26,7 +26,6 @@ namespace hqm {
 constexpr size_t STATIC_SCRATCH_BYTES = 2u << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
 
-constexpr int MAX_DEVICES = 64;
 static void* g_static_ptr[MAX_DEVICES] = {};
 static std::mutex g_static_mutex;
 
