@@ -338,6 +338,10 @@ class ResidentMoe(nn.Module):
     def _ffn(expert):
         return expert._expert if hasattr(expert, "_expert") else expert
 
+    def invalidate(self):
+        """Forget the device-side descriptor table (call after the experts' tensors were replaced or moved)."""
+        self._table = None
+
     def _descriptor_table(self, device):
         """3 * E struct hqm_weight in device memory: (w1, w2, w3) of expert 0, 1, ..."""
         if self._table is None:

@@ -53,10 +53,15 @@ class AttentionDecode(nn.Module):
         dev = ln_in.device
         self.k_cache = torch.zeros((n_kv_heads, max_len, head_dim), dtype=torch.bfloat16, device=dev)
         self.v_cache = torch.zeros((n_kv_heads, max_len, head_dim), dtype=torch.bfloat16, device=dev)
-        self._layer = None
+        self._layer, self._layer_key = None, None
 
     def _descriptor(self) -> _cabi.HqmAttnLayer:
-        if self._layer is None:
+        """struct hqm_attn_layer for the tensors the block currently points at (rebuilt when one of them moved)."""
+        projs = [p.descriptor() for p in (self.q_proj, self.k_proj, self.v_proj, self.o_proj)]
+        key = tuple(d.W_q for d in projs) + (self.ln_in.data_ptr(), self.ln_post.data_ptr(), self.k_cache.data_ptr(),
+                                             self.v_cache.data_ptr())
+        if self._layer is None or self._layer_key != key:
+            self._layer_key = key
             hidden = self.n_heads * self.head_dim
             self._layer = _cabi.HqmAttnLayer(
                 q=self.q_proj.descriptor(), k=self.k_proj.descriptor(), v=self.v_proj.descriptor(),
@@ -100,17 +105,23 @@ class DecoderLayerDecode(nn.Module):
     def __init__(self, attention: AttentionDecode, moe: ResidentMoe, next_ln: torch.Tensor):
         super().__init__()
         self.attention, self.moe, self.next_ln = attention, moe, next_ln
-        self._layer = None
+        self._layer, self._layer_key = None, None
         self._gate_w = None
 
     def _descriptor(self, device) -> _cabi.HqmDecoderLayer:
-        if self._layer is None:
+        """struct hqm_decoder_layer; rebuilt when the attention block's tensors, the gate or the norm weight moved.
+        (The expert table is built once by ResidentMoe; call moe.invalidate() after replacing expert tensors.)"""
+        attn_desc = self.attention._descriptor()
+        key = (self.attention._layer_key, self.moe.gate.weight.data_ptr(), self.next_ln.data_ptr(),
+               self.moe._descriptor_table(device).data_ptr())
+        if self._layer is None or self._layer_key != key:
+            self._layer_key = key
             hidden = self.attention.n_heads * self.attention.head_dim
             gate = self.moe.gate.weight
             self._gate_w = gate if gate.dtype == torch.bfloat16 else gate.to(torch.bfloat16)
             f0 = self.moe._ffn(self.moe._experts[0])
             self._layer = _cabi.HqmDecoderLayer(
-                attn=self.attention._descriptor(), gate_w=self._gate_w.data_ptr(),
+                attn=attn_desc, gate_w=self._gate_w.data_ptr(),
                 table=self.moe._descriptor_table(device).data_ptr(), w1=f0.w1.descriptor(), w2=f0.w2.descriptor(),
                 w3=f0.w3.descriptor(), next_ln=_bf16_vec(self.next_ln, hidden).data_ptr(),
                 n_experts=self.moe.num_experts, reserved=0)
