@@ -101,8 +101,10 @@ gemv_stream3_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x,
     __half* xs_w = reinterpret_cast<__half*>(smem_raw) + wi * WARP_HALFS;   // [10][ROW]
     __half* zz_w = xs_w + 10 * ROW;                                          // [11][ROW], row 10 stays zero
     __half* xh = zz_w + 11 * ROW;                                            // [XPASS * 64]
+    grid_launch_dependents();                       // overlapped launch: set-up runs under the kernel in front
     for (int i = lane; i < 21 * ROW / 2; i += 32) reinterpret_cast<uint32_t*>(xs_w)[i] = 0u;
     __syncwarp();
+    grid_dependency_wait();                         // x, the row index and the partial buffer belong to earlier kernels
 
     const uint16_t* xr = x + (int64_t)(x_idx ? x_idx[m] : m) * K;
     const uint32_t* Wq = reinterpret_cast<const uint32_t*>(w.W_q);
@@ -235,6 +237,8 @@ gemv_stream3_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x,
 // y[m, n] = bf16( sum of the partial row-sets of row n's storage-row class + bias )
 __global__ void finalize3_kernel(uint16_t* __restrict__ y, const float* __restrict__ partial,
                                  const uint16_t* __restrict__ bias, int64_t MN, int N, Split3 sp) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < MN; i += (int64_t)gridDim.x * blockDim.x) {
         const int n = (int)(i % N);
         const uint32_t rho = (uint32_t)((n / 10) % sp.P3);
@@ -309,13 +313,14 @@ int launch_gemv_stream3(uint16_t* y, float* partial, const uint16_t* x, const in
     const s3::Consts cc{0x00380038u, 0x01C001C0u, 0x58005800u, 0x4C004C00u};
     const size_t smem = (size_t)s3::NW * s3::WARP_HALFS * sizeof(__half);
     for (int m = 0; m < (int)M; ++m) {
-        s3::gemv_stream3_kernel<<<plan.grid, 256, smem, st>>>(partial, x, x_idx, m, (int)M, *w, G, C, plan.rows, sp, cc);
+        launch_overlapped(s3::gemv_stream3_kernel, plan.grid, 256, smem, st, partial, x, x_idx, m, (int)M, *w, G, C,
+                          plan.rows, sp, cc);
         HQM_LAUNCH_CHECK();
     }
     const int64_t MN = M * w->N;
     int64_t blocks = (MN + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
-    s3::finalize3_kernel<<<(int)blocks, 256, 0, st>>>(y, partial, bias, MN, w->N, sp);
+    launch_overlapped(s3::finalize3_kernel, (int)blocks, 256, 0, st, y, (const float*)partial, bias, MN, w->N, sp);
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }
