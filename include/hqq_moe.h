@@ -147,15 +147,26 @@ int hqm_router_top2(uint16_t* router_logits, float* topk_w, int32_t* topk_idx, i
                     int32_t* token_idx, float* token_w, const uint16_t* x, const uint16_t* gate_w, int64_t M,
                     int64_t K, int32_t E, void* stream);
 
+/* No counterpart in the reference (its experts are Python modules picked on the host,
+ * custom_layers.py:295-312).  The device-side expert table that hqm_moe_decode / hqm_decode_layer pick the
+ * router's experts from: one 512-byte entry per weight, holding the descriptor and the three TMA tensor maps
+ * (packed codes, scale bytes, zero bytes) the streaming kernel copies its tiles with.  hqm_expert_table_build
+ * fills `host_out` (hqm_expert_table_bytes(n_weights) bytes, 64-byte aligned) on the HOST from n_weights
+ * descriptors, ordered expert 0's w1, w2, w3, expert 1's w1, ...; the caller copies the bytes to device memory
+ * (128-byte aligned) and passes that pointer as `table`.  The entries hold device addresses: rebuild the
+ * table when a weight tensor moves.  Needs a CUDA driver (the tensor maps are encoded by it). */
+size_t hqm_expert_table_bytes(int32_t n_weights);
+int hqm_expert_table_build(void* host_out, const hqm_weight* weights, int32_t n_weights);
+
 /* The whole of SparseMoeWrapper.forward (custom_layers.py:272-314) for ONE token when every expert is
  * resident on the device: router, then the two chosen experts' FFNs, weighted and summed into out (1, hidden).
  * Which experts run is decided on the device (the FFN kernels read the router's choice and fetch that
- * expert's descriptors from `table`), so nothing is copied back to the host and the call can be captured in a
- * CUDA graph.  table: 3*E descriptors in DEVICE memory, expert e at [3e] = w1, [3e+1] = w2, [3e+2] = w3.
+ * expert's entries from `table`), so nothing is copied back to the host and the call can be captured in a
+ * CUDA graph.  table: the 3*E entries hqm_expert_table_build made, in DEVICE memory.
  * w1 / w2 / w3: host descriptors giving the (common) shapes and format.  router_logits: (1, E) bf16. */
 size_t hqm_moe_decode_scratch_bytes(int32_t E, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3);
 int hqm_moe_decode(uint16_t* out, uint16_t* router_logits, const uint16_t* x, const uint16_t* gate_w, int32_t E,
-                   const hqm_weight* table, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3,
+                   const void* table, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3,
                    void* scratch, size_t scratch_bytes, void* stream);
 
 /* ---- the attention half of a decoder layer, one token ---------------------- */
@@ -192,11 +203,11 @@ int hqm_attn_decode(uint16_t* h, uint16_t* x_out, const uint16_t* delta, const h
  *       input_layernorm weight, or the model's final norm weight after the last layer).
  *   h   (hidden) bf16 residual stream, updated in place by both halves.
  *   router_logits (1, n_experts) bf16 out.  attn.ln_in is not used (x arrives normalised).
- *   table: 3 * n_experts descriptors in DEVICE memory as for hqm_moe_decode; w1 / w2 / w3 give the shapes. */
+ *   table: the expert table in DEVICE memory as for hqm_moe_decode; w1 / w2 / w3 give the shapes. */
 typedef struct {
     hqm_attn_layer attn;
     const uint16_t* gate_w;   /* bf16 (n_experts, hidden) */
-    const hqm_weight* table;
+    const void* table;
     hqm_weight w1, w2, w3;
     const uint16_t* next_ln;  /* bf16 (hidden) */
     int32_t n_experts, reserved;

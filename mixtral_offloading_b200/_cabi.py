@@ -70,6 +70,8 @@ SIGNATURES = {
     "hqm_linear_static_scratch": (C.c_int, [_P, _P, _I64, _WP, _P, _P]),
     "hqm_expert_ffn_scratch_bytes": (C.c_size_t, [_I64, _WP, _WP, _WP]),
     "hqm_expert_ffn": (C.c_int, [_P, _P, _I64, _P, _P, C.c_int, _WP, _WP, _WP, _P, C.c_size_t, _P]),
+    "hqm_expert_table_bytes": (C.c_size_t, [_I32]),
+    "hqm_expert_table_build": (C.c_int, [_P, _WP, _I32]),
     "hqm_moe_decode_scratch_bytes": (C.c_size_t, [_I32, _WP, _WP, _WP]),
     "hqm_moe_decode": (C.c_int, [_P, _P, _P, _P, _I32, _P, _WP, _WP, _WP, _P, C.c_size_t, _P]),
     "hqm_attn_decode_scratch_bytes": (C.c_size_t, [C.POINTER(HqmAttnLayer)]),

@@ -653,7 +653,7 @@ int hqm_decode_layer(uint16_t* h, uint16_t* x, uint16_t* router_logits, const hq
     HQM_LAUNCH_CHECK();
     // 5.-7. both chosen experts: [w1; w3] x 2, silu * mul, w2 x 2
     StreamJob gate_up{}, down_proj{};
-    gate_up.table = down_proj.table = L->table;
+    gate_up.table = down_proj.table = static_cast<const StreamEntry*>(L->table);
     for (int slot = 0; slot < 2; ++slot) {
         gate_up.w[2 * slot] = &L->w1;
         gate_up.w[2 * slot + 1] = &L->w3;

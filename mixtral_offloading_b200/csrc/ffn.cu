@@ -209,7 +209,7 @@ size_t hqm_moe_decode_scratch_bytes(int32_t E, const hqm_weight* w1, const hqm_w
 }
 
 int hqm_moe_decode(uint16_t* out, uint16_t* router_logits, const uint16_t* x, const uint16_t* gate_w, int32_t E,
-                   const hqm_weight* table, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3,
+                   const void* table, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3,
                    void* scratch, size_t scratch_bytes, void* stream) {
     using namespace hqm;
     HQM_CHECK_ARG(out && router_logits && x && gate_w && table && w1 && w2 && w3, "moe_decode: null pointer");
@@ -235,7 +235,7 @@ int hqm_moe_decode(uint16_t* out, uint16_t* router_logits, const uint16_t* x, co
     float* down = (float*)(p + mp.up_bytes + mp.h_bytes);
     // the experts are whatever the router wrote to topk_idx[0..1]; their descriptors come from the table
     StreamJob gate_up{}, down_proj{};
-    gate_up.table = down_proj.table = table;
+    gate_up.table = down_proj.table = static_cast<const StreamEntry*>(table);
     for (int slot = 0; slot < 2; ++slot) {
         gate_up.w[2 * slot] = w1;
         gate_up.w[2 * slot + 1] = w3;

@@ -224,7 +224,7 @@ struct Layers {
     int col0[STREAM_MAX_LAYERS + 1];
     int G[STREAM_MAX_LAYERS], C[STREAM_MAX_LAYERS];
     int xrow[STREAM_MAX_LAYERS];
-    const hqm_weight* table;
+    const StreamEntry* table;
     const int32_t* sel[STREAM_MAX_LAYERS];
     int which[STREAM_MAX_LAYERS];
     int sel_settled;    // the indices behind `sel` were complete before this kernel could start (see StreamJob)
@@ -271,7 +271,7 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
             const int l = threadIdx.x / WORDS, i = threadIdx.x % WORDS;
             // (__ldcg: the index may have been written by a kernel that finished while an earlier kernel on this
             // SM still had the previous value in L1)
-            const hqm_weight* src = ly.table + 3 * __ldcg(ly.sel[l]) + ly.which[l];
+            const hqm_weight* src = &(ly.table + 3 * __ldcg(ly.sel[l]) + ly.which[l])->w;
             reinterpret_cast<uint32_t*>(s_desc)[threadIdx.x] = reinterpret_cast<const uint32_t*>(src)[i];
         }
         __syncthreads();
@@ -691,6 +691,9 @@ static int dispatch(int nbits, int nb, int toks, Fn&& fn) {
 
 bool gemv_stream_plan(const hqm_weight* const* ws, int count, int64_t M, StreamPlan* plan) {
     if (count < 1 || count > STREAM_MAX_LAYERS || force_generic()) return false;
+    plan->tma = 0;
+    if (M == 1 && gemv_tma_plan(ws, count, plan)) return true;
+    plan->tma = 0;
     const hqm_weight* w = ws[0];
     if (w->nbits != 2 && w->nbits != 4) return false;
     const int per = codes_per_word(w->nbits);
@@ -759,6 +762,7 @@ size_t gemv_stream_scratch_bytes(const StreamPlan& plan, int64_t M) {
 
 int launch_gemv_stream(float* partial, const uint16_t* x, const int32_t* x_idx, int64_t M, const StreamJob& job,
                        const StreamPlan& plan, cudaStream_t st) {
+    if (plan.tma) return launch_gemv_tma(partial, x, x_idx, M, job, plan, st);
     Layers ly{};
     ly.count = plan.count;
     for (int l = 0; l < plan.count; ++l) {

@@ -12,11 +12,20 @@ int launch_linear_generic(uint16_t* y, const uint16_t* x, const int32_t* x_idx, 
 constexpr int STREAM_MAX_LAYERS = 4;
 // What one launch multiplies: up to four layers of the same K, bit width and group size (N may differ).
 // Layer l reads rows x_idx?[m] + xrow[l] of x.  With `table` set, layer l's descriptor is read on the
-// device: table[3 * *sel[l] + which[l]] (3 descriptors per expert: w1, w2, w3), and w[l] only gives the shape.
+// device: table[3 * *sel[l] + which[l]] (3 entries per expert: w1, w2, w3), and w[l] only gives the shape.
+// One entry of the device-side expert table (hqm_expert_table_build): the layer's descriptor and the three
+// tensor maps (packed codes, scale bytes, zero bytes) the TMA-staged kernel copies its tiles with.
+struct alignas(128) StreamEntry {
+    hqm_weight w;
+    unsigned char pad[128 - sizeof(hqm_weight)];
+    unsigned char maps[3][128];
+};
+static_assert(sizeof(StreamEntry) == 512, "table entries are 512 bytes");
+
 struct StreamJob {
     const hqm_weight* w[STREAM_MAX_LAYERS];
     int xrow[STREAM_MAX_LAYERS];
-    const hqm_weight* table;
+    const StreamEntry* table;
     const int32_t* sel[STREAM_MAX_LAYERS];
     int which[STREAM_MAX_LAYERS];
     // Set only when the kernel launched in front of this one lets its successor start after everything
@@ -35,6 +44,8 @@ struct StreamPlan {
     int warps;   // warps of that grid: the units the passes are split over
     int toks;    // rows of x decoded per launch
     int slots;   // upper bound on the warps contributing to one residue: fp32 partials [slots][M][row length]
+    int tma;     // 1: the TMA-staged single-row kernel (gemv_tma.cu): units are (residue, block of 16 members),
+                 // rho0 counts those units, and `warps` counts CTAs
 };
 // False when the layers / row count are outside what the streaming kernels cover.
 bool gemv_stream_plan(const hqm_weight* const* ws, int count, int64_t M, StreamPlan* plan);
@@ -51,6 +62,10 @@ int launch_finalize_silu_mul(uint16_t* h, const float* partial, int64_t M, const
 int launch_finalize_scatter(uint16_t* out, const float* partial, const int32_t* token_idx, const float* route_w,
                             int accumulate, int64_t M, const StreamPlan& plan, cudaStream_t st);
 bool force_generic();
+// gemv_tma.cu — the same for ONE row of x, tiles staged by TMA.
+bool gemv_tma_plan(const hqm_weight* const* ws, int count, StreamPlan* plan);
+int launch_gemv_tma(float* partial, const uint16_t* x, const int32_t* x_idx, int64_t M, const StreamJob& job,
+                    const StreamPlan& plan, cudaStream_t st);
 
 // router.cu — logits, top-2 indices and weights of M tokens (no per-expert lists).
 int launch_router_top2(uint16_t* router_logits, float* topk_w, int32_t* topk_idx, const uint16_t* x,

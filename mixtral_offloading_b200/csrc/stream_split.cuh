@@ -25,6 +25,7 @@ struct Split {
 // Where the columns of a partial row come from: the layers of the launch side by side.
 struct ColMap {
     int count, per;
+    int nb;          // blocks of 16 group members that are separate units of the split (1: a unit is a whole residue)
     int col0[STREAM_MAX_LAYERS + 1];
     int rho0[STREAM_MAX_LAYERS];
     int G[STREAM_MAX_LAYERS];
@@ -48,7 +49,8 @@ __device__ __forceinline__ int partial_count(const Split& sp, const ColMap& cm, 
         r0 = in ? cm.rho0[l] : r0;
         G = in ? cm.G[l] : G;
     }
-    const uint32_t rho_g = (uint32_t)(r0 + ((col - c0) % G) / cm.per);
+    const int rel = col - c0;
+    const uint32_t rho_g = (uint32_t)(r0 + ((rel % G) / cm.per) * cm.nb + ((rel / G) >> 4) % cm.nb);
     return sp.owner(rho_g * sp.PT + sp.PT - 1) - sp.owner(rho_g * sp.PT) + 1;
 }
 
@@ -116,6 +118,7 @@ inline ColMap colmap_of(const StreamPlan& plan) {
     ColMap cm{};
     cm.count = plan.count;
     cm.per = codes_per_word(plan.nbits);
+    cm.nb = plan.tma ? plan.nb : 1;
     for (int l = 0; l < plan.count; ++l) {
         cm.col0[l] = plan.col0[l];
         cm.rho0[l] = plan.rho0[l];

@@ -343,15 +343,21 @@ class ResidentMoe(nn.Module):
         self._table = None
 
     def _descriptor_table(self, device):
-        """3 * E struct hqm_weight in device memory: (w1, w2, w3) of expert 0, 1, ..."""
+        """The device-side expert table (hqm_expert_table_build): (w1, w2, w3) of expert 0, 1, ..."""
         if self._table is None:
-            raw = bytearray()
-            for ex in self._experts:
+            lib = _cabi.lib()
+            n = 3 * len(self._experts)
+            descs = (_cabi.HqmWeight * n)()
+            for e, ex in enumerate(self._experts):
                 f = self._ffn(ex)
-                for lyr in (f.w1, f.w2, f.w3):
-                    raw += bytes(lyr.descriptor())
+                for i, lyr in enumerate((f.w1, f.w2, f.w3)):
+                    descs[3 * e + i] = lyr.descriptor()
+            nbytes = lib.hqm_expert_table_bytes(n)
             with torch.inference_mode(False):
-                self._table = torch.frombuffer(raw, dtype=torch.uint8).clone().to(device)
+                host = torch.empty(nbytes + 64, dtype=torch.uint8)
+                off = (-host.data_ptr()) % 64
+                _cabi.check(lib.hqm_expert_table_build(C.c_void_p(host.data_ptr() + off), descs, n))
+                self._table = host[off:off + nbytes].to(device)
         return self._table
 
     @torch.inference_mode()

@@ -114,3 +114,30 @@ def test_lru_known_answer_table(golden_dir):
         assert [u[1] for u in step["order"]] == order
         assert [u[1] for u in step["resident"]] == resident
         assert (step["hits"], step["misses"]) == (hits, misses)
+
+
+# ---- the attention oracle against the installed transformers' Mixtral layer pieces (fp32, CPU) -------------
+def test_attention_oracle_matches_transformers(golden_dir):
+    from oracle import attention_oracle as A
+    z = np.load(os.path.join(golden_dir, "attention_hf.npz"))
+    t = lambda k: torch.from_numpy(z[k])
+    nh, nkv, hd, T = int(z["n_heads"]), int(z["n_kv"]), int(z["head_dim"]), int(z["tokens"])
+    theta, eps = float(z["theta"]), float(z["eps"])
+    h = t("h")
+    # RMSNorm and the rotation tables
+    x = A.rms_norm(h, t("ln_in"), eps)
+    assert torch.allclose(x, t("x"), atol=1e-6, rtol=1e-5)
+    cos, sin = A.rope_cos_sin(torch.arange(T), hd, theta)
+    assert torch.allclose(cos, t("cos"), atol=1e-6) and torch.allclose(sin, t("sin"), atol=1e-6)
+    q = (x @ t("Wq").t()).view(T, nh, hd)
+    q_rot = A.apply_rope(q, cos[:, None, :], sin[:, None, :]).transpose(0, 1)
+    assert torch.allclose(q_rot, t("q_rot"), atol=1e-5, rtol=1e-5)
+    # token by token against a cache == the causal pass over the whole sequence
+    attn = A.AttentionOracle(t("Wq"), t("Wk"), t("Wv"), t("Wo"), nh, nkv, hd, max_len=T, theta=theta, round_to=None)
+    for pos in range(T):
+        o = attn.step(x[pos:pos + 1], pos)
+        assert torch.allclose(o[0], t("attn_out")[pos], atol=2e-5, rtol=1e-4), pos
+        h_mid = h[pos:pos + 1] + o
+        assert torch.allclose(h_mid[0], t("h_mid")[pos], atol=2e-5, rtol=1e-4)
+        assert torch.allclose(A.rms_norm(h_mid, t("ln_post"), eps)[0], t("x_post")[pos], atol=5e-5, rtol=1e-4)
+    assert torch.allclose(attn.kc[:, :T], t("k_rot"), atol=1e-5, rtol=1e-5)
