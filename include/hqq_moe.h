@@ -18,7 +18,8 @@
  *   scale/zero: one pair per (n % G, k), G = N / group_size
  *   (src/triton_kernels.py:86-88,110-118); they are stored 8-bit (scale_q,
  *   zero_q: G*K bytes each) and decoded as (q - mz[c]) * ms[c] with
- *   c = (flat index) % (G*K / meta_group), ms/mz fp16 (src/custom_layers.py:62-66).
+ *   c = (flat index) % (G*K / meta_group), ms/mz fp16 (src/custom_layers.py:62-66);
+ *   scale and zero may use different meta_group sizes.
  */
 #ifndef HQQ_MOE_H
 #define HQQ_MOE_H
@@ -44,14 +45,16 @@ typedef struct hqm_weight {
     int32_t N, K;             /* meta['shape'] */
     int32_t nbits;            /* 2, 3 or 4 */
     int32_t group_size;       /* rows per quantisation group (axis 0) */
-    int32_t meta_group;       /* group size of the 8-bit scale/zero quantisation (256) */
-    int32_t reserved;
+    int32_t meta_group;       /* group size of the 8-bit quantisation of scale (256) */
+    int32_t meta_group_zero;  /* the same for zero; 0 = as meta_group.  (hqq's configs may differ between the two:
+                                 the reference's notebook overrides the scale's only.)  Layers whose two sizes
+                                 differ are computed by the shape-agnostic kernel, not the streaming ones. */
     const void* W_q;          /* packed codes, device pointer, 16-byte aligned */
     const uint8_t* scale_q;   /* G*K */
     const uint8_t* zero_q;    /* G*K */
     const uint16_t* ms_scale; /* fp16, G*K/meta_group: meta_scale.scale */
     const uint16_t* mz_scale; /* fp16: meta_scale.zero */
-    const uint16_t* ms_zero;  /* fp16: meta_zero.scale */
+    const uint16_t* ms_zero;  /* fp16, G*K/meta_group_zero: meta_zero.scale */
     const uint16_t* mz_zero;  /* fp16: meta_zero.zero */
 } hqm_weight;
 
@@ -60,7 +63,8 @@ int hqm_version(void);
 /* Number of CUDA kernels this library has launched in the process so far (for benchmarks). */
 int64_t hqm_launch_count(void);
 /* 1 if a bounded wait inside a tensor-core GEMM launch ever ran out (that launch skipped its work),
- * 2 if hqm_attn_decode was given a position outside its cache, 0 otherwise, -1 on a CUDA error.  Reading a
+ * 2 if hqm_attn_decode was given a position outside its cache, 3 if a streaming launch found the header of its
+ * scratch buffer not zeroed (see hqm_scratch_init; its result is then incomplete), 0 otherwise, -1 on a CUDA error.  Reading a
  * non-zero value clears it.  Synchronises the device; meant for tests and start-up checks. */
 int hqm_device_error(void);
 /* No counterpart in the reference.  The streaming kernels and their reductions are launched so that a
@@ -73,6 +77,13 @@ int hqm_device_error(void);
  * HQM_NO_OVERLAP=1 in the environment at load time), hqm_set_overlap(1) switches back; returns the previous
  * setting.  Process wide. */
 int hqm_set_overlap(int on);
+
+/* No counterpart in the reference.  Which single-row launches use the TMA-staged streaming kernel (tiled
+ * cp.async.bulk.tensor copies of the packed tiles into per-warp stage rings, rows finished inside the kernel):
+ * 0 = none, 1 = a linear that stands alone (hqm_linear, the default), 2 = also the multi-layer and table-driven
+ * launches of hqm_expert_ffn / hqm_moe_decode / hqm_attn_decode / hqm_decode_layer.  HQM_TMA=0|1|2 in the
+ * environment sets the initial value.  Returns the previous mode.  Process wide. */
+int hqm_set_tma_mode(int mode);
 
 /* ---- bit packing: src/packing.py --------------------------------------- */
 /* pack_4bit_u8_common, packing.py:10-17.  codes (N, K) uint8 -> packed (N/2, K). */
@@ -92,6 +103,16 @@ int hqm_unpack_3bit_i32(uint8_t* codes, const int32_t* packed, int64_t rows, int
 /* HQQLinearTritonSavable.dequantize, custom_layers.py:95-116: the full (N, K)
  * weight.  out_dtype: 0 = bf16, 1 = fp16, 2 = fp32. */
 int hqm_dequantize(void* W_out, int out_dtype, const hqm_weight* w, void* stream);
+
+/* No counterpart in the reference.  Every `scratch` buffer this library is given starts with
+ * hqm_scratch_header_bytes() (64 KiB) of library state: arrival counters with which the CTAs of a streaming launch
+ * that share a group of output rows decide which of them adds the parts up (so that no separate reduction launch
+ * is needed).  The header must be zero the first time a buffer is used; hqm_scratch_init queues that memset on
+ * `stream`.  Every call leaves the header zero again, so one initialisation per buffer is enough.  The sizes the
+ * *_scratch_bytes functions return include the header.  Calls that share a scratch buffer must not overlap on
+ * the GPU (they would also overwrite each other's partial sums). */
+size_t hqm_scratch_header_bytes(void);
+int hqm_scratch_init(void* scratch, void* stream);
 
 /* Bytes of scratch hqm_linear needs for M rows of this layer (0 if none). */
 size_t hqm_linear_scratch_bytes(int64_t M, const hqm_weight* w);

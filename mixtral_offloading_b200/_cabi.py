@@ -20,7 +20,7 @@ class HqmWeight(C.Structure):
     """struct hqm_weight."""
     _fields_ = [
         ("N", C.c_int32), ("K", C.c_int32), ("nbits", C.c_int32), ("group_size", C.c_int32),
-        ("meta_group", C.c_int32), ("reserved", C.c_int32),
+        ("meta_group", C.c_int32), ("meta_group_zero", C.c_int32),
         ("W_q", C.c_void_p), ("scale_q", C.c_void_p), ("zero_q", C.c_void_p),
         ("ms_scale", C.c_void_p), ("mz_scale", C.c_void_p), ("ms_zero", C.c_void_p), ("mz_zero", C.c_void_p),
     ]
@@ -57,6 +57,7 @@ SIGNATURES = {
     "hqm_launch_count": (C.c_int64, []),
     "hqm_device_error": (C.c_int, []),
     "hqm_set_overlap": (C.c_int, [C.c_int]),
+    "hqm_set_tma_mode": (C.c_int, [C.c_int]),
     "hqm_pack_4bit_u8": (C.c_int, [_P, _P, _I64, _I64, _P]),
     "hqm_unpack_4bit_u8": (C.c_int, [_P, _P, _I64, _I64, _P]),
     "hqm_pack_2bit_u8": (C.c_int, [_P, _P, _I64, _I64, _P]),
@@ -64,6 +65,8 @@ SIGNATURES = {
     "hqm_pack_3bit_i32": (C.c_int, [_P, _P, _I64, _I64, _P]),
     "hqm_unpack_3bit_i32": (C.c_int, [_P, _P, _I64, _I64, _P]),
     "hqm_dequantize": (C.c_int, [_P, C.c_int, _WP, _P]),
+    "hqm_scratch_header_bytes": (C.c_size_t, []),
+    "hqm_scratch_init": (C.c_int, [_P, _P]),
     "hqm_linear_scratch_bytes": (C.c_size_t, [_I64, _WP]),
     "hqm_linear": (C.c_int, [_P, _P, _I64, _WP, _P, _P, C.c_size_t, _P]),
     "hqm_static_scratch_capacity": (C.c_size_t, []),

@@ -36,6 +36,8 @@ int check_weight(const hqm_weight* w, int* G, int* C) {
     HQM_CHECK_ARG(w->meta_group > 0 && L % w->meta_group == 0,
                   "scale/zero length %lld is not a multiple of meta_group = %d", (long long)L, w->meta_group);
     HQM_CHECK_ARG(L / w->meta_group <= INT32_MAX, "scale/zero vector too long");
+    HQM_CHECK_ARG(w->meta_group_zero >= 0 && (w->meta_group_zero == 0 || L % w->meta_group_zero == 0),
+                  "zero length %lld is not a multiple of meta_group_zero = %d", (long long)L, w->meta_group_zero);
     HQM_CHECK_ARG(w->W_q && w->scale_q && w->zero_q && w->ms_scale && w->mz_scale && w->ms_zero && w->mz_zero,
                   "weight descriptor holds a null tensor pointer");
     *G = (int)g;
@@ -79,12 +81,12 @@ size_t linear_scratch_bytes(int64_t M, const hqm_weight* w) {
     Stream3Plan plan3;
     if (gemv_stream3_plan(w, G, C, M, &plan3)) return gemv_stream3_scratch_bytes(plan3, M, w->N);
     const hqm_weight* one[1] = {w};
-    if (!gemv_stream_plan(one, 1, M, &plan)) return 0;
+    if (!gemv_stream_plan(one, 1, M, &plan, /*chained=*/false)) return 0;
     return (gemv_stream_scratch_bytes(plan, M) + 255) / 256 * 256;
 }
 
 int launch_linear(uint16_t* y, const uint16_t* x, const int32_t* x_idx, int64_t M, const hqm_weight* w,
-                  const uint16_t* bias, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+                  const uint16_t* bias, uint32_t* counters, void* scratch, size_t scratch_bytes, cudaStream_t st) {
     int G, C;
     int rc = check_weight(w, &G, &C);
     if (rc != HQM_OK) return rc;
@@ -119,10 +121,11 @@ int launch_linear(uint16_t* y, const uint16_t* x, const int32_t* x_idx, int64_t 
             set_error("linear: scratch of %zu bytes given, %zu needed", scratch_bytes, need);
             return HQM_ERR_SCRATCH;
         }
+        HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 15u) == 0, "linear: scratch must be 16-byte aligned");
         return launch_gemv_stream3(y, (float*)scratch, x, x_idx, M, w, bias, G, C, plan3, st);
     }
     const hqm_weight* one[1] = {w};
-    if (gemv_stream_plan(one, 1, M, &plan)) {
+    if (gemv_stream_plan(one, 1, M, &plan, /*chained=*/false)) {
         const size_t need = gemv_stream_scratch_bytes(plan, M);
         if (scratch == nullptr || scratch_bytes < need) {
             set_error("linear: scratch of %zu bytes given, %zu needed", scratch_bytes, need);
@@ -131,6 +134,12 @@ int launch_linear(uint16_t* y, const uint16_t* x, const int32_t* x_idx, int64_t 
         HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 15u) == 0, "linear: scratch must be 16-byte aligned");
         StreamJob job{};
         job.w[0] = w;
+        job.counters = counters;
+        if (plan.tma) {                      // the launch finishes the row itself: bf16, bias added
+            job.y_out = y;
+            job.bias = bias;
+            return launch_gemv_stream((float*)scratch, x, x_idx, M, job, plan, st);
+        }
         rc = launch_gemv_stream((float*)scratch, x, x_idx, M, job, plan, st);
         if (rc != HQM_OK) return rc;
         return launch_finalize_linear(y, (const float*)scratch, bias, M, plan, st);
@@ -147,14 +156,30 @@ int hqm_version(void) { return 1; }
 int64_t hqm_launch_count(void) { return (int64_t)hqm::launches(); }
 int hqm_set_overlap(int on) { return hqm::set_overlap(on); }
 
-size_t hqm_linear_scratch_bytes(int64_t M, const hqm_weight* w) { return hqm::linear_scratch_bytes(M, w); }
+size_t hqm_scratch_header_bytes(void) { return hqm::SCRATCH_HEADER; }
+
+int hqm_scratch_init(void* scratch, void* stream) {
+    using namespace hqm;
+    HQM_CHECK_ARG(scratch != nullptr, "scratch_init: null pointer");
+    HQM_CUDA(cudaMemsetAsync(scratch, 0, SCRATCH_HEADER, (cudaStream_t)stream));
+    return HQM_OK;
+}
+
+size_t hqm_linear_scratch_bytes(int64_t M, const hqm_weight* w) {
+    const size_t inner = hqm::linear_scratch_bytes(M, w);
+    return inner ? inner + hqm::SCRATCH_HEADER : 0;
+}
 
 int hqm_linear(uint16_t* y, const uint16_t* x, int64_t M, const hqm_weight* w, const uint16_t* bias, void* scratch,
                size_t scratch_bytes, void* stream) {
     using namespace hqm;
     HQM_CHECK_ARG(M >= 0 && M <= INT32_MAX, "linear: bad row count %lld", (long long)M);
     HQM_CHECK_ARG(M == 0 || (y && x), "linear: null activation pointer");
-    return launch_linear(y, x, nullptr, M, w, bias, scratch, scratch_bytes, (cudaStream_t)stream);
+    if (scratch == nullptr || scratch_bytes <= SCRATCH_HEADER)
+        return launch_linear(y, x, nullptr, M, w, bias, nullptr, nullptr, 0, (cudaStream_t)stream);
+    HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "linear: scratch must be 256-byte aligned");
+    return launch_linear(y, x, nullptr, M, w, bias, (uint32_t*)scratch, (uint8_t*)scratch + SCRATCH_HEADER,
+                         scratch_bytes - SCRATCH_HEADER, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -61,8 +61,15 @@ __host__ __device__ inline int64_t storage_rows(int64_t N, int nbits) {
 }
 
 // Validates a weight descriptor; fills G (groups along N) and C (columns of the
-// (meta_group, C) view of the flat scale/zero vector).
+// (meta_group, C) view of the flat scale vector; zero_meta_cols() gives the zero vector's).
 int check_weight(const hqm_weight* w, int* G, int* C);
+// The streaming and tensor-core kernels track ONE meta column for scale and zero: they take layers whose two
+// meta group sizes are equal; the others go to the shape-agnostic kernel.
+inline bool meta_uniform(const hqm_weight* w) { return w->meta_group_zero == 0 || w->meta_group_zero == w->meta_group; }
+__host__ __device__ inline int64_t zero_meta_cols(const hqm_weight& w, int G) {
+    const int64_t mg = w.meta_group_zero > 0 ? w.meta_group_zero : w.meta_group;
+    return (int64_t)G * w.K / mg;
+}
 
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }
 __device__ __forceinline__ float f16_bits_to_float(uint16_t b) { return __half2float(__ushort_as_half(b)); }

@@ -524,7 +524,7 @@ int hqm_add_rmsnorm(uint16_t* h, const uint16_t* delta, const uint16_t* weight, 
 size_t hqm_attn_decode_scratch_bytes(const hqm_attn_layer* L) {
     hqm::AttnPlan ap;
     if (hqm::attn_plan(L, &ap) != HQM_OK) return 0;
-    return ap.total();
+    return hqm::SCRATCH_HEADER + ap.total();
 }
 
 int hqm_attn_decode(uint16_t* h, uint16_t* x_out, const uint16_t* delta, const hqm_attn_layer* L, const int32_t* pos,
@@ -534,14 +534,15 @@ int hqm_attn_decode(uint16_t* h, uint16_t* x_out, const uint16_t* delta, const h
     AttnPlan ap;
     int rc = attn_plan(L, &ap);
     if (rc != HQM_OK) return rc;
-    if (scratch == nullptr || scratch_bytes < ap.total()) {
-        set_error("attn_decode: scratch of %zu bytes given, %zu needed", scratch_bytes, ap.total());
+    if (scratch == nullptr || scratch_bytes < SCRATCH_HEADER + ap.total()) {
+        set_error("attn_decode: scratch of %zu bytes given, %zu needed", scratch_bytes, SCRATCH_HEADER + ap.total());
         return HQM_ERR_SCRATCH;
     }
     HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "attn_decode: scratch must be 256-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
     const int hidden = L->q.K;
-    uint8_t* p = (uint8_t*)scratch;
+    uint32_t* counters = (uint32_t*)scratch;
+    uint8_t* p = (uint8_t*)scratch + SCRATCH_HEADER;
     uint16_t* x = (uint16_t*)p;
     float* qkv_part = (float*)(p + ap.x_bytes);
     uint16_t* qbuf = (uint16_t*)(p + ap.x_bytes + ap.qkv_bytes);
@@ -556,6 +557,7 @@ int hqm_attn_decode(uint16_t* h, uint16_t* x_out, const uint16_t* delta, const h
     qkv.w[1] = &L->k;
     qkv.w[2] = &L->v;
     oj.w[0] = &L->o;
+    qkv.counters = oj.counters = counters;
     rc = launch_gemv_stream(qkv_part, x, nullptr, 1, qkv, ap.qkv, st);
     if (rc != HQM_OK) return rc;
     const int heads = L->n_heads + 2 * L->n_kv_heads;
@@ -595,7 +597,7 @@ size_t hqm_decode_layer_scratch_bytes(const hqm_decoder_layer* L) {
     hqm::AttnPlan ap;
     hqm::MoeDecodePlan mp;
     if (decoder_layer_plan(L, &ap, &mp) != HQM_OK) return 0;
-    return ap.total() + mp.router_bytes + mp.up_bytes + mp.h_bytes + mp.down_bytes;
+    return hqm::SCRATCH_HEADER + ap.total() + mp.router_bytes + mp.up_bytes + mp.h_bytes + mp.down_bytes;
 }
 
 int hqm_decode_layer(uint16_t* h, uint16_t* x, uint16_t* router_logits, const hqm_decoder_layer* L, const int32_t* pos,
@@ -607,7 +609,7 @@ int hqm_decode_layer(uint16_t* h, uint16_t* x, uint16_t* router_logits, const hq
     MoeDecodePlan mp;
     int rc = decoder_layer_plan(L, &ap, &mp);
     if (rc != HQM_OK) return rc;
-    const size_t need = ap.total() + mp.router_bytes + mp.up_bytes + mp.h_bytes + mp.down_bytes;
+    const size_t need = SCRATCH_HEADER + ap.total() + mp.router_bytes + mp.up_bytes + mp.h_bytes + mp.down_bytes;
     if (scratch == nullptr || scratch_bytes < need) {
         set_error("decode_layer: scratch of %zu bytes given, %zu needed", scratch_bytes, need);
         return HQM_ERR_SCRATCH;
@@ -616,7 +618,8 @@ int hqm_decode_layer(uint16_t* h, uint16_t* x, uint16_t* router_logits, const hq
     cudaStream_t st = (cudaStream_t)stream;
     const hqm_attn_layer* A = &L->attn;
     const int hidden = A->q.K, E = L->n_experts;
-    uint8_t* p = (uint8_t*)scratch;
+    uint32_t* counters = (uint32_t*)scratch;
+    uint8_t* p = (uint8_t*)scratch + SCRATCH_HEADER;
     uint16_t* x2 = (uint16_t*)p;                                   // the MoE block's input
     float* qkv_part = (float*)(p + ap.x_bytes);
     uint16_t* ctx = (uint16_t*)(p + ap.x_bytes + ap.qkv_bytes + ap.q_bytes);
@@ -634,6 +637,7 @@ int hqm_decode_layer(uint16_t* h, uint16_t* x, uint16_t* router_logits, const hq
     qkv.w[1] = &A->k;
     qkv.w[2] = &A->v;
     oj.w[0] = &A->o;
+    qkv.counters = oj.counters = counters;
     rc = launch_gemv_stream(qkv_part, x, nullptr, 1, qkv, ap.qkv, st);
     if (rc != HQM_OK) return rc;
     // 2. RoPE, cache append and attention
@@ -654,6 +658,7 @@ int hqm_decode_layer(uint16_t* h, uint16_t* x, uint16_t* router_logits, const hq
     // 5.-7. both chosen experts: [w1; w3] x 2, silu * mul, w2 x 2
     StreamJob gate_up{}, down_proj{};
     gate_up.table = down_proj.table = static_cast<const StreamEntry*>(L->table);
+    gate_up.counters = down_proj.counters = counters;
     for (int slot = 0; slot < 2; ++slot) {
         gate_up.w[2 * slot] = &L->w1;
         gate_up.w[2 * slot + 1] = &L->w3;

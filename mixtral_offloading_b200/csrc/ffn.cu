@@ -90,17 +90,18 @@ extern "C" {
 
 size_t hqm_expert_ffn_scratch_bytes(int64_t M, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3) {
     if (!w1 || !w2 || !w3 || M <= 0) return 0;
+    const size_t H = hqm::SCRATCH_HEADER;
     hqm::TcPlan tp;
-    if (hqm::tc_plan(M, w1, w2, w3, nullptr, &tp)) return tp.up_bytes + tp.h_bytes + tp.down_bytes;
+    if (hqm::tc_plan(M, w1, w2, w3, nullptr, &tp)) return H + tp.up_bytes + tp.h_bytes + tp.down_bytes;
     hqm::FusedPlan fp;
-    if (hqm::fused_plan(M, w1, w2, w3, nullptr, &fp)) return fp.up_bytes + fp.h_bytes + fp.down_bytes;
+    if (hqm::fused_plan(M, w1, w2, w3, nullptr, &fp)) return H + fp.up_bytes + fp.h_bytes + fp.down_bytes;
     const size_t a = hqm::align_up((size_t)M * (size_t)w1->N * 2, 256);
     const size_t b = hqm::align_up((size_t)M * (size_t)w3->N * 2, 256);
     const size_t c = hqm::align_up((size_t)M * (size_t)w2->N * 2, 256);
     size_t lin = hqm::linear_scratch_bytes(M, w1);
     lin = lin > hqm::linear_scratch_bytes(M, w3) ? lin : hqm::linear_scratch_bytes(M, w3);
     lin = lin > hqm::linear_scratch_bytes(M, w2) ? lin : hqm::linear_scratch_bytes(M, w2);
-    return a + b + c + lin;
+    return H + a + b + c + lin;
 }
 
 int hqm_expert_ffn(uint16_t* out, const uint16_t* x, int64_t M, const int32_t* token_idx, const float* route_w,
@@ -122,7 +123,8 @@ int hqm_expert_ffn(uint16_t* out, const uint16_t* x, int64_t M, const int32_t* t
     HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "expert_ffn: scratch must be 256-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
     const int F = w1->N, H = w2->N;
-    uint8_t* p = (uint8_t*)scratch;
+    uint32_t* counters = (uint32_t*)scratch;
+    uint8_t* p = (uint8_t*)scratch + SCRATCH_HEADER;
     TcPlan tp;
     if (tc_plan(M, w1, w2, w3, x, &tp)) {
         float* up = (float*)p;
@@ -146,6 +148,7 @@ int hqm_expert_ffn(uint16_t* out, const uint16_t* x, int64_t M, const int32_t* t
         gate_up.w[0] = w1;
         gate_up.w[1] = w3;
         down_proj.w[0] = w2;
+        gate_up.counters = down_proj.counters = counters;
         int rc = launch_gemv_stream(up, x, token_idx, M, gate_up, fp.up, st);
         if (rc != HQM_OK) return rc;
         rc = launch_finalize_silu_mul(h, up, M, fp.up, st);
@@ -163,14 +166,14 @@ int hqm_expert_ffn(uint16_t* out, const uint16_t* x, int64_t M, const int32_t* t
     void* lin = p;
     const size_t lin_bytes = scratch_bytes - (size_t)(p - (uint8_t*)scratch);
 
-    int rc = launch_linear(a, x, token_idx, M, w1, nullptr, lin, lin_bytes, st);
+    int rc = launch_linear(a, x, token_idx, M, w1, nullptr, counters, lin, lin_bytes, st);
     if (rc != HQM_OK) return rc;
-    rc = launch_linear(b, x, token_idx, M, w3, nullptr, lin, lin_bytes, st);
+    rc = launch_linear(b, x, token_idx, M, w3, nullptr, counters, lin, lin_bytes, st);
     if (rc != HQM_OK) return rc;
     const int64_t nf = M * F;
     silu_mul_kernel<<<(int)((nf + 255) / 256 > 148 * 8 ? 148 * 8 : (nf + 255) / 256), 256, 0, st>>>(a, b, nf);
     HQM_LAUNCH_CHECK();
-    rc = launch_linear(c, a, nullptr, M, w2, nullptr, lin, lin_bytes, st);
+    rc = launch_linear(c, a, nullptr, M, w2, nullptr, counters, lin, lin_bytes, st);
     if (rc != HQM_OK) return rc;
     const int64_t nh = M * H;
     scale_scatter_kernel<<<(int)((nh + 255) / 256 > 148 * 8 ? 148 * 8 : (nh + 255) / 256), 256, 0, st>>>(
@@ -205,7 +208,7 @@ size_t hqm_moe_decode_scratch_bytes(int32_t E, const hqm_weight* w1, const hqm_w
     if (!w1 || !w2 || !w3 || E < 2) return 0;
     hqm::MoeDecodePlan mp;
     if (!hqm::moe_decode_plan(E, w1, w2, w3, &mp)) return 0;
-    return mp.router_bytes + mp.up_bytes + mp.h_bytes + mp.down_bytes;
+    return hqm::SCRATCH_HEADER + mp.router_bytes + mp.up_bytes + mp.h_bytes + mp.down_bytes;
 }
 
 int hqm_moe_decode(uint16_t* out, uint16_t* router_logits, const uint16_t* x, const uint16_t* gate_w, int32_t E,
@@ -217,14 +220,16 @@ int hqm_moe_decode(uint16_t* out, uint16_t* router_logits, const uint16_t* x, co
     HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(x) & 15u) == 0, "moe_decode: x must be 16-byte aligned");
     MoeDecodePlan mp;
     HQM_CHECK_ARG(moe_decode_plan(E, w1, w2, w3, &mp), "moe_decode: these expert shapes are outside the streaming path");
-    const size_t need = mp.router_bytes + mp.up_bytes + mp.h_bytes + mp.down_bytes;
+    const size_t need = SCRATCH_HEADER + mp.router_bytes + mp.up_bytes + mp.h_bytes + mp.down_bytes;
     if (scratch == nullptr || scratch_bytes < need) {
         set_error("moe_decode: scratch of %zu bytes given, %zu needed", scratch_bytes, need);
         return HQM_ERR_SCRATCH;
     }
     HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 255u) == 0, "moe_decode: scratch must be 256-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
-    // router outputs live at the head of the scratch buffer
+    // router outputs live at the head of the scratch buffer (behind the library's header)
+    uint32_t* counters = (uint32_t*)scratch;
+    scratch = (uint8_t*)scratch + SCRATCH_HEADER;
     float* topk_w = (float*)scratch;                    // [2] (+2 pad)
     int32_t* topk_idx = (int32_t*)(topk_w + 4);         // [2] (+2 pad)
     int rc = launch_router_top2(router_logits, topk_w, topk_idx, x, gate_w, 1, w1->K, E, st);
@@ -236,6 +241,7 @@ int hqm_moe_decode(uint16_t* out, uint16_t* router_logits, const uint16_t* x, co
     // the experts are whatever the router wrote to topk_idx[0..1]; their descriptors come from the table
     StreamJob gate_up{}, down_proj{};
     gate_up.table = down_proj.table = static_cast<const StreamEntry*>(table);
+    gate_up.counters = down_proj.counters = counters;
     for (int slot = 0; slot < 2; ++slot) {
         gate_up.w[2 * slot] = w1;
         gate_up.w[2 * slot + 1] = w3;

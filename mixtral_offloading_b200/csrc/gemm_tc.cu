@@ -356,7 +356,7 @@ int* tc_error_ptr() {
 }
 
 bool gemm_tc_supported(const hqm_weight* w, int G, int C, int64_t M) {
-    if (w->nbits != 2 && w->nbits != 4) return false;
+    if ((w->nbits != 2 && w->nbits != 4) || !meta_uniform(w)) return false;
     const int per = codes_per_word(w->nbits);
     const int g = w->group_size;
     if (!((w->nbits == 2 && (g == 16 || g == 32)) || (w->nbits == 4 && (g == 32 || g == 64)))) return false;

@@ -286,7 +286,7 @@ bool gemm_tc3_supported(const hqm_weight* w, int G, int C, int64_t M) {
     (void)C;
     // up to 4 rows the streaming kernel (one launch per row) is faster than decoding the tables and
     // dequantising whole tiles
-    if (w->nbits != 3 || M < 5 || w->K % 64 != 0) return false;
+    if (w->nbits != 3 || M < 5 || w->K % 64 != 0 || !meta_uniform(w)) return false;
     if ((int64_t)G * w->K >= ((int64_t)1 << 31)) return false;
     return (reinterpret_cast<uintptr_t>(w->W_q) & 15u) == 0;
 }

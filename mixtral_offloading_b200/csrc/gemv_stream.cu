@@ -37,6 +37,8 @@
 //
 // HBM traffic per launch is the packed codes + scale_q + zero_q once (the meta and x
 // stay in L1/L2), which is the algorithmic minimum.
+#include <stdlib.h>
+
 #include <map>
 #include <type_traits>
 
@@ -689,10 +691,10 @@ static int dispatch(int nbits, int nb, int toks, Fn&& fn) {
     return -1;
 }
 
-bool gemv_stream_plan(const hqm_weight* const* ws, int count, int64_t M, StreamPlan* plan) {
+bool gemv_stream_plan(const hqm_weight* const* ws, int count, int64_t M, StreamPlan* plan, bool chained) {
     if (count < 1 || count > STREAM_MAX_LAYERS || force_generic()) return false;
     plan->tma = 0;
-    if (M == 1 && gemv_tma_plan(ws, count, plan)) return true;
+    if (M == 1 && gemv_tma_plan(ws, count, chained, plan)) return true;
     plan->tma = 0;
     const hqm_weight* w = ws[0];
     if (w->nbits != 2 && w->nbits != 4) return false;
@@ -710,7 +712,7 @@ bool gemv_stream_plan(const hqm_weight* const* ws, int count, int64_t M, StreamP
     for (int l = 0; l < count; ++l) {
         const hqm_weight* v = ws[l];
         int G, C;
-        if (check_weight(v, &G, &C) != HQM_OK) return false;
+        if (check_weight(v, &G, &C) != HQM_OK || !meta_uniform(v)) return false;
         if (v->nbits != w->nbits || v->group_size != g || v->K != w->K || v->meta_group != w->meta_group) return false;
         if (G % per != 0 || C % dk != 0) return false;
         if ((int64_t)G * v->K >= (int64_t)1 << 31 || (int64_t)(v->N / per) * v->K >= (int64_t)1 << 31) return false;
@@ -756,7 +758,9 @@ bool gemv_stream_plan(const hqm_weight* const* ws, int count, int64_t M, StreamP
     return true;
 }
 
+size_t gemv_tma_scratch_bytes(const StreamPlan& plan, int64_t M);
 size_t gemv_stream_scratch_bytes(const StreamPlan& plan, int64_t M) {
+    if (plan.tma) return gemv_tma_scratch_bytes(plan, M);
     return (size_t)plan.slots * (size_t)M * (size_t)plan.col0[plan.count] * sizeof(float);
 }
 
@@ -779,7 +783,7 @@ int launch_gemv_stream(float* partial, const uint16_t* x, const int32_t* x_idx, 
     ly.col0[plan.count] = plan.col0[plan.count];
     ly.table = job.table;
     ly.sel_settled = job.sel_settled;
-    const Split sp = split_of(plan);
+    const Split sp = work_split_of(plan);
     // rows beyond one launch's tokens go in further launches over the same split
     for (int m0 = 0; m0 < (int)M; m0 += plan.toks) {
         const int take = ((int)M - m0 < plan.toks) ? (int)M - m0 : plan.toks;

@@ -255,7 +255,7 @@ __global__ void finalize3_kernel(uint16_t* __restrict__ y, const float* __restri
 static int gcd_int(int a, int b) { return b == 0 ? a : gcd_int(b, a % b); }
 
 bool gemv_stream3_plan(const hqm_weight* w, int G, int C, int64_t M, Stream3Plan* plan) {
-    if (w->nbits != 3 || M < 1 || M > 16) return false;
+    if (w->nbits != 3 || M < 1 || M > 16 || !meta_uniform(w)) return false;
     if (w->K % 64 != 0 || C % 8 != 0) return false;
     const int rows = (w->N + 9) / 10;
     const int P3 = G / gcd_int(G, 10);

@@ -32,7 +32,16 @@ struct StreamJob {
     // before it has completed (launch_finalize_silu_mul(..., late_trigger = true)) and the indices behind
     // `sel` are older than that: the launch then reads them, and starts on the weights, without waiting.
     int sel_settled;
+    // TMA-staged launches (plan.tma) only.  counters: the zeroed header of the caller's scratch buffer (arrival
+    // counters of units split over several CTAs; left zero again).  y_out: when set, the launch writes the finished
+    // row as bf16 (+ bias) there itself, and no finalize launch follows.
+    uint32_t* counters;
+    uint16_t* y_out;
+    const uint16_t* bias;
 };
+// Every scratch buffer handed to the library starts with this many bytes of library state, zero when the buffer is
+// first used (hqm_scratch_init) and zero again after every call.
+constexpr size_t SCRATCH_HEADER = 64 * 1024;
 struct StreamPlan {
     int count;                          // layers in the launch
     int nbits, nb;                      // bit width, group size / 16
@@ -47,8 +56,9 @@ struct StreamPlan {
     int tma;     // 1: the TMA-staged single-row kernel (gemv_tma.cu): units are (residue, block of 16 members),
                  // rho0 counts those units, and `warps` counts CTAs
 };
-// False when the layers / row count are outside what the streaming kernels cover.
-bool gemv_stream_plan(const hqm_weight* const* ws, int count, int64_t M, StreamPlan* plan);
+// False when the layers / row count are outside what the streaming kernels cover.  `chained`: the launch is a
+// link of the decode step's launch chain (its consumers read the sums); false for a linear that stands alone.
+bool gemv_stream_plan(const hqm_weight* const* ws, int count, int64_t M, StreamPlan* plan, bool chained = true);
 size_t gemv_stream_scratch_bytes(const StreamPlan& plan, int64_t M);
 int launch_gemv_stream(float* partial, const uint16_t* x, const int32_t* x_idx, int64_t M, const StreamJob& job,
                        const StreamPlan& plan, cudaStream_t st);
@@ -63,7 +73,7 @@ int launch_finalize_scatter(uint16_t* out, const float* partial, const int32_t* 
                             int accumulate, int64_t M, const StreamPlan& plan, cudaStream_t st);
 bool force_generic();
 // gemv_tma.cu — the same for ONE row of x, tiles staged by TMA.
-bool gemv_tma_plan(const hqm_weight* const* ws, int count, StreamPlan* plan);
+bool gemv_tma_plan(const hqm_weight* const* ws, int count, bool chained, StreamPlan* plan);
 int launch_gemv_tma(float* partial, const uint16_t* x, const int32_t* x_idx, int64_t M, const StreamJob& job,
                     const StreamPlan& plan, cudaStream_t st);
 
@@ -110,8 +120,9 @@ bool moe_decode_plan(int E, const hqm_weight* w1, const hqm_weight* w2, const hq
 
 // Dispatcher used by hqm_linear and by the expert FFN: picks the streaming
 // kernel when the layer's shape allows it, the generic one otherwise.
+// (scratch excludes the header; counters points at it)
 size_t linear_scratch_bytes(int64_t M, const hqm_weight* w);
 int launch_linear(uint16_t* y, const uint16_t* x, const int32_t* x_idx, int64_t M, const hqm_weight* w,
-                  const uint16_t* bias, void* scratch, size_t scratch_bytes, cudaStream_t st);
+                  const uint16_t* bias, uint32_t* counters, void* scratch, size_t scratch_bytes, cudaStream_t st);
 
 }  // namespace hqm

@@ -9,11 +9,13 @@
 
 namespace hqm {
 
-__device__ __forceinline__ void decode_scale_zero(const hqm_weight& w, int64_t idx, int C, float& s, float& z) {
+__device__ __forceinline__ void decode_scale_zero(const hqm_weight& w, int64_t idx, int C, int64_t Cz, float& s,
+                                                  float& z) {
     const int col = (int)(idx % C);
+    const int64_t colz = (Cz == C) ? col : idx % Cz;
     // explicit rounding steps (no fused multiply-add) so the fp32 result equals the CPU restatement bit for bit
     s = __fmul_rn(__fsub_rn((float)w.scale_q[idx], f16_bits_to_float(w.mz_scale[col])), f16_bits_to_float(w.ms_scale[col]));
-    z = __fmul_rn(__fsub_rn((float)w.zero_q[idx], f16_bits_to_float(w.mz_zero[col])), f16_bits_to_float(w.ms_zero[col]));
+    z = __fmul_rn(__fsub_rn((float)w.zero_q[idx], f16_bits_to_float(w.mz_zero[colz])), f16_bits_to_float(w.ms_zero[colz]));
 }
 
 template <int NBITS>
@@ -36,6 +38,7 @@ linear_generic_kernel(uint16_t* __restrict__ y, const uint16_t* __restrict__ x, 
     if (R >= rows) return;
     const int m0 = blockIdx.y * MT;
     const int K = w.K;
+    const int64_t Cz = zero_meta_cols(w, G);
 
     const uint16_t* xr[MT];
 #pragma unroll
@@ -60,7 +63,7 @@ linear_generic_kernel(uint16_t* __restrict__ y, const uint16_t* __restrict__ x, 
             if (n < w.N) {
                 const float code = (float)((word >> (NBITS * (PER - 1 - s))) & MASK);
                 float sc, zr;
-                decode_scale_zero(w, (n % G) * K + k, C, sc, zr);
+                decode_scale_zero(w, (n % G) * K + k, C, Cz, sc, zr);
                 const float wv = (code - zr) * sc;
 #pragma unroll
                 for (int m = 0; m < MT; ++m) acc[s][m] = fmaf(wv, xv[m], acc[s][m]);
@@ -107,6 +110,7 @@ __global__ void dequantize_kernel(T* __restrict__ out, hqm_weight w, int G, int 
     constexpr uint32_t MASK = (1u << NBITS) - 1u;
     const int64_t rows = storage_rows(w.N, NBITS);
     const int64_t total = rows * w.K;
+    const int64_t Cz = zero_meta_cols(w, G);
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t R = i / w.K, k = i % w.K;
         const uint32_t word = load_word<NBITS>(w, R, k);
@@ -116,7 +120,7 @@ __global__ void dequantize_kernel(T* __restrict__ out, hqm_weight w, int G, int 
             if (n < w.N) {
                 const float code = (float)((word >> (NBITS * (PER - 1 - s))) & MASK);
                 float sc, zr;
-                decode_scale_zero(w, (n % G) * w.K + k, C, sc, zr);
+                decode_scale_zero(w, (n % G) * w.K + k, C, Cz, sc, zr);
                 out[n * w.K + k] = cast_out<T>(__fmul_rn(__fsub_rn(code, zr), sc));
             }
         }

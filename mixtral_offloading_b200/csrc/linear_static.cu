@@ -56,7 +56,8 @@ int hqm_linear_static_scratch(uint16_t* y, const uint16_t* x, int64_t M, const h
     using namespace hqm;
     HQM_CHECK_ARG(M >= 0 && M <= INT32_MAX, "linear: bad row count %lld", (long long)M);
     HQM_CHECK_ARG(M == 0 || (y && x), "linear: null activation pointer");
-    const size_t need = linear_scratch_bytes(M, w);
+    const size_t inner = linear_scratch_bytes(M, w);
+    const size_t need = inner ? inner + SCRATCH_HEADER : 0;
     if (need > STATIC_SCRATCH_BYTES) {
         set_error("linear_static_scratch: this call needs %zu bytes of workspace but the built-in one holds %zu; "
                   "use hqm_linear with a caller-provided buffer", need, (size_t)STATIC_SCRATCH_BYTES);
@@ -67,9 +68,13 @@ int hqm_linear_static_scratch(uint16_t* y, const uint16_t* x, int64_t M, const h
         const int rc = static_scratch_ptr(&ws);
         if (rc != HQM_OK) return rc;
     }
-    // Every partial sum the finalize step reads is written earlier in the same call, so the
-    // workspace needs no clearing although it still holds the previous call's contents.
-    return launch_linear(y, x, nullptr, M, w, bias, ws, need, (cudaStream_t)stream);
+    // Every partial sum that is read was written earlier in the same call, so the workspace needs no
+    // clearing although it still holds the previous call's contents.  The only part that must start at
+    // zero is the header (arrival counters); the array is zero when the library is loaded and every call
+    // leaves the header zero again.
+    if (ws == nullptr) return launch_linear(y, x, nullptr, M, w, bias, nullptr, nullptr, 0, (cudaStream_t)stream);
+    return launch_linear(y, x, nullptr, M, w, bias, (uint32_t*)ws, (uint8_t*)ws + SCRATCH_HEADER, inner,
+                         (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -113,7 +113,13 @@ __device__ __forceinline__ void partial_sum_pair(const float* __restrict__ parti
     out_b = vb;
 }
 
-inline Split split_of(const StreamPlan& plan) { return Split{plan.rho0[plan.count], plan.PT, plan.warps}; }
+// The split the CONSUMERS of a launch's sums see.  A TMA-staged launch finishes its sums itself (one fp32 row-set,
+// `grid` = 1: every element has exactly one part); the other kernel leaves one row-set per warp that touched a residue.
+inline Split split_of(const StreamPlan& plan) {
+    return Split{plan.rho0[plan.count], plan.PT, plan.tma ? 1 : plan.warps};
+}
+// The split of the passes over the launch's CTAs / warps.
+inline Split work_split_of(const StreamPlan& plan) { return Split{plan.rho0[plan.count], plan.PT, plan.warps}; }
 inline ColMap colmap_of(const StreamPlan& plan) {
     ColMap cm{};
     cm.count = plan.count;

@@ -29,7 +29,8 @@ def _scratch(device: torch.device, nbytes: int) -> torch.Tensor:
 
     A buffer that has been outgrown is kept alive, not freed: a captured CUDA graph may still hold its address
     (a decode step captured before a larger request, e.g. a long prompt, arrives).  Growth is geometric, so the
-    retired buffers together stay below the size of the current one."""
+    retired buffers together stay below the size of the current one.  The first hqm_scratch_header_bytes() bytes
+    of every buffer are library state that has to start at zero (hqm_scratch_init)."""
     key = (device.type, device.index)
     buf = _SCRATCH.get(key)
     if buf is None or buf.numel() < nbytes:
@@ -38,6 +39,7 @@ def _scratch(device: torch.device, nbytes: int) -> torch.Tensor:
             _SCRATCH_RETIRED.append(buf)
         with torch.inference_mode(False):
             buf = torch.empty(size, dtype=torch.uint8, device=device)
+        _cabi.check(_cabi.lib().hqm_scratch_init(_cabi.ptr(buf), _cabi.stream_ptr(device)))
         _SCRATCH[key] = buf
     return buf
 
@@ -121,20 +123,36 @@ class HQQLinearTritonSavable(nn.Module):
     def descriptor(self) -> _cabi.HqmWeight:
         """The struct hqm_weight for the tensors this layer currently points at."""
         m = self.meta
-        key = (self.W_q.data_ptr(), m["scale_q"].data_ptr(), m["zero_q"].data_ptr())
+        ms, mz = m["meta_scale"], m["meta_zero"]
+        key = (self.W_q.data_ptr(), m["scale_q"].data_ptr(), m["zero_q"].data_ptr(), ms["scale"].data_ptr(),
+               ms["zero"].data_ptr(), mz["scale"].data_ptr(), mz["zero"].data_ptr())
         if self._desc is None or self._desc[0] != key:
-            _cabi.require_cuda(self.W_q, m["scale_q"], m["zero_q"])
+            _cabi.require_cuda(self.W_q, m["scale_q"], m["zero_q"], ms["scale"], ms["zero"], mz["scale"], mz["zero"])
             if not (m.get("quant_scale") and m.get("quant_zero")):
                 raise NotImplementedError("layer without 8-bit scale/zero")
-            assert m["meta_scale"]["group_size"] == m["meta_zero"]["group_size"]
-            for t in (m["meta_scale"]["scale"], m["meta_scale"]["zero"], m["meta_zero"]["scale"], m["meta_zero"]["zero"]):
-                assert t.dtype == torch.float16 and t.is_contiguous()
+            N, K = m["shape"]
+            L = (N // m["group_size"]) * K
+            # the meta group sizes are what the TENSORS say (a loaded checkpoint may differ from the template, and
+            # scale and zero may differ from each other): one fp16 (scale, zero) pair per column of the (group, L/group) view
+            groups = []
+            for name, q, mm in (("scale", m["scale_q"], ms), ("zero", m["zero_q"], mz)):
+                if q.numel() != L or q.dtype != torch.uint8 or not q.is_contiguous():
+                    raise ValueError(f"{name}_q holds {q.numel()} values of {q.dtype}, expected {L} contiguous uint8")
+                cols = mm["scale"].numel()
+                if cols == 0 or L % cols != 0 or mm["zero"].numel() != cols:
+                    raise ValueError(f"meta_{name}: {cols} scale and {mm['zero'].numel()} zero values do not divide "
+                                     f"the {L} {name} values into groups")
+                for t in (mm["scale"], mm["zero"]):
+                    if t.dtype != torch.float16 or not t.is_contiguous():
+                        raise ValueError(f"meta_{name} tensors must be contiguous float16")
+                groups.append(L // cols)
+                mm["group_size"] = L // cols
             d = _cabi.HqmWeight(
-                N=m["shape"][0], K=m["shape"][1], nbits=m["nbits"], group_size=m["group_size"],
-                meta_group=m["meta_scale"]["group_size"], reserved=0,
+                N=N, K=K, nbits=m["nbits"], group_size=m["group_size"],
+                meta_group=groups[0], meta_group_zero=0 if groups[1] == groups[0] else groups[1],
                 W_q=self.W_q.data_ptr(), scale_q=m["scale_q"].data_ptr(), zero_q=m["zero_q"].data_ptr(),
-                ms_scale=m["meta_scale"]["scale"].data_ptr(), mz_scale=m["meta_scale"]["zero"].data_ptr(),
-                ms_zero=m["meta_zero"]["scale"].data_ptr(), mz_zero=m["meta_zero"]["zero"].data_ptr())
+                ms_scale=ms["scale"].data_ptr(), mz_scale=ms["zero"].data_ptr(),
+                ms_zero=mz["scale"].data_ptr(), mz_zero=mz["zero"].data_ptr())
             self._desc = (key, d)
         return self._desc[1]
 
@@ -201,6 +219,8 @@ class HQQLinearTritonSavable(nn.Module):
             return
         self.W_q = state_dict.pop(prefix + "W_q")
         self.bias = state_dict.pop(prefix + "bias") if (prefix + "bias") in state_dict else None
+        if self.bias is not None and self.bias.dtype != torch.bfloat16:
+            self.bias = self.bias.to(torch.bfloat16)          # the kernels read the bias as bf16 (the reference's is fp16)
         for key, path in self._TENSOR_PATHS:
             node = self.meta
             for p in path[:-1]:

@@ -120,13 +120,14 @@ def _affine_quantize(t: torch.Tensor, nbits: int, group: int):
     return codes, (1.0 / q_scale), zero
 
 
-def quantize(W: torch.Tensor, nbits: int, group_size: int, meta_group: int = 256) -> dict:
+def quantize(W: torch.Tensor, nbits: int, group_size: int, meta_group: int = 256, meta_group_zero=None) -> dict:
     """Quantise a float (N, K) weight into the layer dictionary used everywhere here.
 
     Keys: N, K, nbits, group_size, meta_group, codes (uint8 (N,K)), W_q (packed),
     scale_q / zero_q (uint8 (G*K,)), ms_scale, mz_scale, ms_zero, mz_zero
     (fp16 (G*K/meta_group,)).  The tensor names follow custom_layers.py:139-162
-    (scale_q, meta_scale.{scale,zero}, zero_q, meta_zero.{scale,zero}).
+    (scale_q, meta_scale.{scale,zero}, zero_q, meta_zero.{scale,zero}).  meta_group_zero gives the zero vector its
+    own 8-bit group size (the reference's notebook overrides the scale's group size only, so the two can differ).
     """
     N, K = W.shape
     assert N % group_size == 0
@@ -136,9 +137,10 @@ def quantize(W: torch.Tensor, nbits: int, group_size: int, meta_group: int = 256
     codes, scale, zero = _affine_quantize(W, nbits, group_size)          # (g, G*K), (1, L), (1, L)
     codes = codes.reshape(N, K).contiguous()                             # custom_layers.py:44-45
     sq, ms_s, mz_s = _affine_quantize(scale, 8, meta_group)              # (meta_group, L/meta_group)
-    zq, ms_z, mz_z = _affine_quantize(zero, 8, meta_group)
+    zq, ms_z, mz_z = _affine_quantize(zero, 8, meta_group_zero or meta_group)
     return dict(
         N=N, K=K, nbits=nbits, group_size=group_size, meta_group=meta_group,
+        **({"meta_group_zero": meta_group_zero} if meta_group_zero and meta_group_zero != meta_group else {}),
         codes=codes.numpy(),
         W_q=PACK[nbits](codes.numpy()),
         scale_q=sq.reshape(-1).contiguous().numpy(), zero_q=zq.reshape(-1).contiguous().numpy(),
@@ -168,7 +170,8 @@ def scale_zero(layer: dict):
     """fp32 (G, K) scale and zero of a layer (custom_layers.py:83-84 views them (-1, K))."""
     K = layer["K"]
     s = meta_dequant(layer["scale_q"], layer["ms_scale"], layer["mz_scale"], layer["meta_group"]).reshape(-1, K)
-    z = meta_dequant(layer["zero_q"], layer["ms_zero"], layer["mz_zero"], layer["meta_group"]).reshape(-1, K)
+    z = meta_dequant(layer["zero_q"], layer["ms_zero"], layer["mz_zero"],
+                     layer.get("meta_group_zero") or layer["meta_group"]).reshape(-1, K)
     return s, z
 
 

@@ -17,14 +17,17 @@ def quant_config(nbits, group_size):
 
 def fill_layer(layer, od, device):
     """Point a product layer at the tensors of an oracle layer dictionary."""
-    C_ = (od["N"] // od["group_size"]) * od["K"] // od["meta_group"]
+    L = (od["N"] // od["group_size"]) * od["K"]
+    C_ = L // od["meta_group"]
+    gz = od.get("meta_group_zero") or od["meta_group"]
+    Cz = L // gz
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
     layer.W_q = t(od["W_q"])
     m = layer.meta
     m["scale_q"] = t(od["scale_q"]).reshape(od["meta_group"], C_)
-    m["zero_q"] = t(od["zero_q"]).reshape(od["meta_group"], C_)
+    m["zero_q"] = t(od["zero_q"]).reshape(gz, Cz)
     m["meta_scale"]["scale"], m["meta_scale"]["zero"] = t(od["ms_scale"]).reshape(1, C_), t(od["mz_scale"]).reshape(1, C_)
-    m["meta_zero"]["scale"], m["meta_zero"]["zero"] = t(od["ms_zero"]).reshape(1, C_), t(od["mz_zero"]).reshape(1, C_)
+    m["meta_zero"]["scale"], m["meta_zero"]["zero"] = t(od["ms_zero"]).reshape(1, Cz), t(od["mz_zero"]).reshape(1, Cz)
     layer.ready = True
     layer._desc = None
     return layer

@@ -233,6 +233,8 @@ def test_generate_graph_and_eager_agree_and_repeat():
     new_buf = _scratch(DEV, 4 * old_buf.numel())
     assert new_buf.data_ptr() != old_buf.data_ptr() and new_buf.numel() >= 4 * old_buf.numel()
     new_buf.fill_(0xFF)
+    _cabi_lib = __import__("mixtral_offloading_b200")._cabi
+    _cabi_lib.check(_cabi_lib.lib().hqm_scratch_init(_cabi_lib.ptr(new_buf), _cabi_lib.stream_ptr(DEV)))   # its header: zero again
     again = model.generate(prompt, 12, use_graph=True)
     assert len(eager) == 12 and all(0 <= t < vocab for t in eager)
     assert graphed == eager and again == eager

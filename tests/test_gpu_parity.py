@@ -178,7 +178,7 @@ def test_linear_shapes_and_dtypes():
 
 
 FULL = [(4, 64, 4096, 4096, (1, 16, 64)), (4, 64, 1024, 4096, (1,)), (2, 16, 14336, 4096, (1, 8, 64, 512)),
-        (2, 16, 4096, 14336, (1, 8, 64, 512)), (3, 64, 14336, 4096, (1, 16))]
+        (2, 16, 4096, 14336, (1, 8, 64, 512)), (3, 64, 14336, 4096, (1, 4, 16, 128, 300))]
 
 
 @pytest.mark.parametrize("nbits,group,N,K,Ms", FULL)
@@ -255,6 +255,19 @@ def test_expert_ffn_mid_size(M):
     x = torch.randn(M, hidden, generator=torch.Generator().manual_seed(M)).to(torch.bfloat16)
     y = ex(x.to(DEV)).cpu()
     assert O.rel_err(y, O.expert_ffn(x, *ods)) < TOL
+
+
+@pytest.mark.parametrize("M", [1, 8, 64, 512])
+def test_expert_ffn_full_size(M):
+    """BASELINE configs[1]: one Mixtral expert (w1, w3 14336 x 4096; w2 4096 x 14336), 2-bit g16, at its own token
+    counts; 512 rows cross the 256-row chunking of the tensor-core GEMM and its scatter epilogue."""
+    hidden, ffn = 4096, 14336
+    ods = (random_layer(ffn, hidden, 2, 16, 1), random_layer(hidden, ffn, 2, 16, 2), random_layer(ffn, hidden, 2, 16, 3))
+    ex = make_expert(hidden, ffn, ods)
+    x = torch.randn(M, hidden, generator=torch.Generator().manual_seed(M)).to(torch.bfloat16)
+    y = ex(x.to(DEV)).cpu()
+    assert O.rel_err(y, O.expert_ffn(x, *ods)) < TOL
+    assert _cabi.lib().hqm_device_error() == 0
 
 
 def test_overlapped_launches_give_the_same_bits():
@@ -472,3 +485,64 @@ def test_expert_cache_random_traffic_few_buffers():
             assert int(data.min()) == uid + 1 and int(data.max()) == uid + 1
             got.append(uid)
         assert sorted(got) == sorted(req)
+
+
+# ------------------------------------------------------------------ checkpoint format (state-dict hooks)
+def test_scale_and_zero_with_different_meta_groups():
+    """A checkpoint whose scale is 8-bit quantised in groups of 128 and whose zero is one group for the whole
+    tensor (the reference's notebook overrides only the scale's group size, so the two differ in real files): the
+    group sizes are read off the tensors, the layer is computed by the shape-agnostic kernel, fp32 decode exact."""
+    N, K = 256, 512
+    L = (N // 64) * K
+    g = torch.Generator().manual_seed(2)
+    W = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+    od = O.quantize(W, 4, 64, meta_group=128, meta_group_zero=L)
+    layer = layer_from_oracle(od, DEV)
+    d = layer.descriptor()
+    assert (d.meta_group, d.meta_group_zero) == (128, L)
+    assert torch.equal(layer.dequantize(torch.float32).cpu(), O.dequantize(od))
+    for M in (1, 5, 40):
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+        assert O.rel_err(layer(x.to(DEV)).cpu(), O.linear(x, od)) < TOL
+    # the same tensors through the state-dict hooks into a layer built from the 256 / 256 template
+    sd = {k: v.clone() for k, v in layer.state_dict().items()}
+    fresh = layer_from_oracle(random_layer(N, K, 4, 64, seed=1), DEV)
+    fresh.load_state_dict(sd)
+    d2 = fresh.descriptor()
+    assert (d2.meta_group, d2.meta_group_zero) == (128, L)
+    x = torch.randn(3, K, generator=g).to(torch.bfloat16)
+    assert torch.equal(fresh(x.to(DEV)), layer(x.to(DEV)))
+    # tensors that do not fit the layer are refused, not read out of bounds
+    bad = dict(sd)
+    bad["meta.meta_scale.scale"] = sd["meta.meta_scale.scale"].reshape(-1)[:-1].clone()
+    fresh.load_state_dict(bad)
+    with pytest.raises(ValueError):
+        fresh.descriptor()
+
+
+def test_state_dict_round_trip_of_layer_and_expert_slab():
+    """custom_layers.py:136-222 and expert_wrapper.py:23-30: a quantized layer and a whole expert slab saved and
+    reloaded give identical bytes and identical outputs."""
+    hidden, ffn = 256, 512
+    ods = (random_layer(ffn, hidden, 2, 16, 1), random_layer(hidden, ffn, 2, 16, 2), random_layer(ffn, hidden, 2, 16, 3))
+    src = MixtralExpertWrapper(make_expert(hidden, ffn, ods), device=DEV)
+    sd = src.state_dict()
+    assert set(sd) == {"storage"} and sd["storage"].dtype == torch.uint8
+    other = (random_layer(ffn, hidden, 2, 16, 11), random_layer(hidden, ffn, 2, 16, 12), random_layer(ffn, hidden, 2, 16, 13))
+    dst = MixtralExpertWrapper(make_expert(hidden, ffn, other), device=DEV)
+    x = torch.randn(4, hidden, generator=torch.Generator().manual_seed(0)).to(torch.bfloat16).to(DEV)
+    assert not torch.equal(dst(x), src(x))
+    dst.load_state_dict({k: v.cpu() for k, v in sd.items()})            # as read from a file
+    assert torch.equal(torch.as_tensor(dst.storage, dtype=torch.uint8, device=DEV), sd["storage"])
+    assert torch.equal(dst(x), src(x))
+    assert O.rel_err(dst(x).cpu(), O.expert_ffn(x.cpu(), *ods)) < TOL
+    # a single layer: W_q arriving in the (group_size, G*K)-packed form is repacked on load (custom_layers.py:222)
+    od = ods[0]
+    lay = layer_from_oracle(od, DEV)
+    sd1 = {k: v.clone() for k, v in lay.state_dict().items()}
+    codes = O.UNPACK[2](od["W_q"])[:od["N"]]
+    sd1["W_q"] = gpu(O.PACK[2](codes.reshape(od["group_size"], -1)))
+    fresh = layer_from_oracle(random_layer(ffn, hidden, 2, 16, 21), DEV)
+    fresh.load_state_dict(sd1)
+    assert np.array_equal(fresh.W_q.cpu().numpy(), od["W_q"])
+    assert torch.equal(fresh(x), lay(x))

@@ -25,6 +25,8 @@ def _both(layer, x):
     M, N = x.shape[0], layer.meta["shape"][0]
     need = lib.hqm_linear_scratch_bytes(M, C.byref(d))
     ws = torch.empty(max(need, 16), dtype=torch.uint8, device=DEV)
+    if need:
+        _cabi.check(lib.hqm_scratch_init(_cabi.ptr(ws), _cabi.stream_ptr(DEV)))
     y_ref = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
     y_new = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
     stream = _cabi.stream_ptr(DEV)
@@ -46,6 +48,23 @@ def test_static_scratch_matches_caller_scratch_twice(nbits, group, N, K):
         assert not torch.isnan(y_new.float()).any()
         assert O.rel_err(y_new.cpu(), y_ref.cpu()) < TOL, f"call {call}"
         assert O.rel_err(y_new.cpu(), O.linear(x, od)) < TOL, f"call {call}"
+
+
+@pytest.mark.parametrize("nbits,group,N,K,Ms", [(2, 16, 14336, 4096, (24, 17)), (3, 64, 1792, 512, (1, 4)),
+                                                 (3, 64, 1792, 512, (16, 5))])
+def test_static_scratch_other_kernels(nbits, group, N, K, Ms):
+    """The built-in workspace also serves the tensor-core path (M >= 17, 2-bit) and both 3-bit paths."""
+    od = random_layer(N, K, nbits, group, seed=7 * nbits)
+    layer = layer_from_oracle(od, DEV)
+    g = torch.Generator().manual_seed(1)
+    for call, M in enumerate(Ms):
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+        need, y_ref, y_new = _both(layer, x.to(DEV))
+        assert 0 < need <= _cabi.lib().hqm_static_scratch_capacity()
+        assert not torch.isnan(y_new.float()).any()
+        assert O.rel_err(y_new.cpu(), y_ref.cpu()) < TOL, f"call {call}"
+        assert O.rel_err(y_new.cpu(), O.linear(x, od)) < TOL, f"call {call}"
+    assert _cabi.lib().hqm_device_error() == 0
 
 
 def test_static_scratch_rejects_oversized_calls():
