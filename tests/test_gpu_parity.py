@@ -533,7 +533,7 @@ def test_state_dict_round_trip_of_layer_and_expert_slab():
     x = torch.randn(4, hidden, generator=torch.Generator().manual_seed(0)).to(torch.bfloat16).to(DEV)
     assert not torch.equal(dst(x), src(x))
     dst.load_state_dict({k: v.cpu() for k, v in sd.items()})            # as read from a file
-    assert torch.equal(torch.as_tensor(dst.storage, dtype=torch.uint8, device=DEV), sd["storage"])
+    assert torch.equal(torch.as_tensor(dst.storage, dtype=torch.uint8, device=DEV).cpu(), sd["storage"].cpu())
     assert torch.equal(dst(x), src(x))
     assert O.rel_err(dst(x).cpu(), O.expert_ffn(x.cpu(), *ods)) < TOL
     # a single layer: W_q arriving in the (group_size, G*K)-packed form is repacked on load (custom_layers.py:222)
