@@ -236,6 +236,24 @@ typedef struct {
 size_t hqm_decode_layer_scratch_bytes(const hqm_decoder_layer* layer);
 int hqm_decode_layer(uint16_t* h, uint16_t* x, uint16_t* router_logits, const hqm_decoder_layer* layer,
                      const int32_t* pos, void* scratch, size_t scratch_bytes, void* stream);
+/* No counterpart in the reference (which has no distributed code; the block being sharded is
+ * SparseMoeWrapper.forward, custom_layers.py:272-314).  hqm_decode_layer for ONE RANK of an expert-parallel group:
+ * attention, norms and router run replicated (every rank computes the same routing); the rank owns experts
+ * [expert_lo, expert_lo + n_local) of the layer's n_experts and `layer->table` holds only those (3 * n_local
+ * entries).  On the device the routed experts that the rank owns are packed into its launch slots (one slot when
+ * it owns a single expert, else two); a slot without an expert streams nothing and contributes zeros.  The
+ * residual stream h is updated by the attention half only, x is left untouched, and y_partial (hidden) receives
+ * the rank's fp32 share of the MoE block's output: sum over its slots of bf16(weight * bf16(expert output)).
+ * The caller adds the ranks' shares (an all-reduce on the same stream; every term is a bf16 value and at most two
+ * are non-zero, so the fp32 sum is exact) and finishes the layer with hqm_add_f32_rmsnorm(h, y_sum, next_ln, x),
+ * which gives bit for bit what hqm_decode_layer gives on one GPU. */
+size_t hqm_decode_layer_ep_scratch_bytes(const hqm_decoder_layer* layer, int32_t n_local);
+int hqm_decode_layer_ep(uint16_t* h, uint16_t* x, uint16_t* router_logits, float* y_partial,
+                        const hqm_decoder_layer* layer, int32_t expert_lo, int32_t n_local, const int32_t* pos,
+                        void* scratch, size_t scratch_bytes, void* stream);
+/* h = bf16(h + bf16(delta)) with delta in fp32; x_out = rmsnorm(h) * weight (see hqm_add_rmsnorm). */
+int hqm_add_f32_rmsnorm(uint16_t* h, const float* delta, const uint16_t* weight, uint16_t* x_out, int32_t hidden,
+                        float eps, void* stream);
 /* h = bf16(h + delta) when delta is given; x_out = bf16(weight * bf16(h * rsqrt(mean(h^2) + eps))): the RMSNorm
  * of the Hugging Face decoder with the preceding residual add (used for the last layer's output and the final norm). */
 int hqm_add_rmsnorm(uint16_t* h, const uint16_t* delta, const uint16_t* weight, uint16_t* x_out, int32_t hidden,

@@ -81,6 +81,9 @@ SIGNATURES = {
     "hqm_attn_decode": (C.c_int, [_P, _P, _P, C.POINTER(HqmAttnLayer), _P, _P, C.c_size_t, _P]),
     "hqm_decode_layer_scratch_bytes": (C.c_size_t, [C.POINTER(HqmDecoderLayer)]),
     "hqm_decode_layer": (C.c_int, [_P, _P, _P, C.POINTER(HqmDecoderLayer), _P, _P, C.c_size_t, _P]),
+    "hqm_decode_layer_ep_scratch_bytes": (C.c_size_t, [C.POINTER(HqmDecoderLayer), _I32]),
+    "hqm_decode_layer_ep": (C.c_int, [_P, _P, _P, _P, C.POINTER(HqmDecoderLayer), _I32, _I32, _P, _P, C.c_size_t, _P]),
+    "hqm_add_f32_rmsnorm": (C.c_int, [_P, _P, _P, _P, _I32, C.c_float, _P]),
     "hqm_add_rmsnorm": (C.c_int, [_P, _P, _P, _P, _I32, C.c_float, _P]),
     "hqm_router_top2": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),
     "hqm_cache_create": (C.c_int, [C.POINTER(_P), _I32, _I32, _I32, C.c_size_t, C.POINTER(_P), _I32]),

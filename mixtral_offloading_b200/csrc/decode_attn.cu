@@ -127,7 +127,8 @@ constexpr int ROUTER_EMAX = 8;
 __global__ void __launch_bounds__(NORM_THREADS) finalize_add_rmsnorm_router_kernel(
     uint16_t* __restrict__ h, const float* __restrict__ partial, const uint16_t* __restrict__ w, uint16_t* __restrict__ x,
     int H, float eps, Split sp, ColMap cm, const uint16_t* __restrict__ gate_w, int E, uint16_t* __restrict__ logits_out,
-    float* __restrict__ topk_w, int32_t* __restrict__ topk_idx) {
+    float* __restrict__ topk_w, int32_t* __restrict__ topk_idx, int ep_lo, int ep_n, int ep_slots,
+    float* __restrict__ local_w, int32_t* __restrict__ local_idx) {
     __shared__ float red[32];
     __shared__ float mine;
     __shared__ float s_part[NORM_THREADS / 32][ROUTER_EMAX];
@@ -208,10 +209,29 @@ __global__ void __launch_bounds__(NORM_THREADS) finalize_add_rmsnorm_router_kern
         }
         if (i1 < 0) { i1 = i0; p1 = 0.f; }
         const float norm = p0 + p1;
-        topk_w[0] = round_bf16(p0 / norm);
-        topk_w[1] = round_bf16(p1 / norm);
+        const float w0 = round_bf16(p0 / norm), w1 = round_bf16(p1 / norm);
+        topk_w[0] = w0;
+        topk_w[1] = w1;
         topk_idx[0] = i0;
         topk_idx[1] = i1;
+        if (local_idx) {
+            // expert-parallel rank owning experts [ep_lo, ep_lo + ep_n): the chosen experts it owns, in the router's
+            // order, packed into its `ep_slots` launch slots (index into the rank's own table); -1 = slot unused
+            int n = 0;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int e = c == 0 ? i0 : i1;
+                if (e >= ep_lo && e < ep_lo + ep_n && n < ep_slots) {
+                    local_idx[n] = e - ep_lo;
+                    local_w[n] = c == 0 ? w0 : w1;
+                    ++n;
+                }
+            }
+            for (; n < ep_slots; ++n) {
+                local_idx[n] = -1;
+                local_w[n] = 0.f;
+            }
+        }
     }
     cluster.sync();
 }
@@ -239,6 +259,58 @@ __global__ void __launch_bounds__(NORM_THREADS) finalize_scatter_add_rmsnorm_ker
             partial_sum_pair<true>(partial, sp, cm, 0, cm.col0[0] + i, cm.col0[1] + i, row, row, s0, s1);
             const float y = round_bf16(round_bf16(round_bf16(s0) * route_w[0]) + round_bf16(round_bf16(s1) * route_w[1]));
             v[j] = round_bf16(bf16_bits_to_float(h[i]) + y);
+            h[i] = float_to_bf16_bits(v[j]);
+        }
+        ss += v[j] * v[j];
+    }
+    const float rstd = rsqrtf(cluster_sum(ss, red, &mine) / (float)H + eps);
+#pragma unroll
+    for (int j = 0; j < NORM_PER_THREAD; ++j) {
+        const int i = first + j * stride;
+        if (i < H) x[i] = float_to_bf16_bits(bf16_bits_to_float(w[i]) * round_bf16(v[j] * rstd));
+    }
+}
+
+// y[i] = sum over the launch's layers l of bf16(route_w[l] * bf16(sums of layer l)), in fp32: what one expert-parallel
+// rank contributes to the MoE block's output.  Every term is a bf16 value and at most two ranks' terms are non-zero,
+// so adding the ranks' vectors in fp32 and rounding to bf16 gives exactly what finalize_scatter_add_rmsnorm_kernel
+// computes on one GPU.
+__global__ void __launch_bounds__(256) finalize_weighted_f32_kernel(float* __restrict__ y, const float* __restrict__ partial,
+                                                                    const float* __restrict__ route_w, int H, int row,
+                                                                    Split sp, ColMap cm) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < H; i += gridDim.x * blockDim.x) {
+        float acc = 0.f;
+#pragma unroll
+        for (int l = 0; l < STREAM_MAX_LAYERS; ++l) {
+            if (l < cm.count) {
+                const float v = round_bf16(round_bf16(partial_sum<true>(partial, sp, cm, 0, layer_col0(cm, l) + i, row, row)) * route_w[l]);
+                acc = (l == 0) ? v : round_bf16(acc + v);
+            }
+        }
+        y[i] = acc;
+    }
+}
+
+// h = bf16(h + bf16(delta)) with delta in fp32 (the all-reduced expert-parallel partials), x = rmsnorm(h) * w.
+__global__ void __launch_bounds__(NORM_THREADS) add_f32_rmsnorm_kernel(uint16_t* __restrict__ h,
+                                                                       const float* __restrict__ delta,
+                                                                       const uint16_t* __restrict__ w,
+                                                                       uint16_t* __restrict__ x, int H, float eps) {
+    __shared__ float red[32];
+    __shared__ float mine;
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int stride = NORM_CTAS * NORM_THREADS, first = blockIdx.x * NORM_THREADS + threadIdx.x;
+    float v[NORM_PER_THREAD];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NORM_PER_THREAD; ++j) {
+        const int i = first + j * stride;
+        v[j] = 0.f;
+        if (i < H) {
+            v[j] = round_bf16(bf16_bits_to_float(h[i]) + round_bf16(delta[i]));
             h[i] = float_to_bf16_bits(v[j]);
         }
         ss += v[j] * v[j];
@@ -579,7 +651,9 @@ int hqm_attn_decode(uint16_t* h, uint16_t* x_out, const uint16_t* delta, const h
 }
 
 // ---- a whole decoder layer for one token: 8 launches -------------------------------------------------
-static int decoder_layer_plan(const hqm_decoder_layer* L, hqm::AttnPlan* ap, hqm::MoeDecodePlan* mp) {
+// `slots` expert launch slots: 2 on one GPU (both routed experts); an expert-parallel rank has min(2, experts it
+// owns) and fills them on the device with the routed experts that are its own.
+static int decoder_layer_plan(const hqm_decoder_layer* L, int slots, hqm::AttnPlan* ap, hqm::MoeDecodePlan* mp) {
     using namespace hqm;
     HQM_CHECK_ARG(L != nullptr, "decode_layer: null layer");
     int rc = attn_plan(&L->attn, ap);
@@ -588,28 +662,28 @@ static int decoder_layer_plan(const hqm_decoder_layer* L, hqm::AttnPlan* ap, hqm
     HQM_CHECK_ARG(L->n_experts >= 2 && L->n_experts <= ROUTER_EMAX, "decode_layer: %d experts not supported (2..%d)",
                   L->n_experts, ROUTER_EMAX);
     HQM_CHECK_ARG(L->w1.K == L->attn.q.K && L->w2.N == L->attn.q.K, "decode_layer: expert shapes do not fit the hidden size");
-    HQM_CHECK_ARG(moe_decode_plan(L->n_experts, &L->w1, &L->w2, &L->w3, mp),
+    HQM_CHECK_ARG(moe_decode_plan_slots(L->n_experts, slots, &L->w1, &L->w2, &L->w3, mp),
                   "decode_layer: these expert shapes are outside the streaming path");
     return HQM_OK;
 }
 
-size_t hqm_decode_layer_scratch_bytes(const hqm_decoder_layer* L) {
-    hqm::AttnPlan ap;
-    hqm::MoeDecodePlan mp;
-    if (decoder_layer_plan(L, &ap, &mp) != HQM_OK) return 0;
+static size_t decoder_layer_bytes(const hqm::AttnPlan& ap, const hqm::MoeDecodePlan& mp) {
     return hqm::SCRATCH_HEADER + ap.total() + mp.router_bytes + mp.up_bytes + mp.h_bytes + mp.down_bytes;
 }
 
-int hqm_decode_layer(uint16_t* h, uint16_t* x, uint16_t* router_logits, const hqm_decoder_layer* L, const int32_t* pos,
-                     void* scratch, size_t scratch_bytes, void* stream) {
+// y_partial == nullptr: one GPU, the layer is finished (residual add, next norm).  Otherwise the rank's fp32
+// contribution to the MoE block's output goes to y_partial and h / x are left as they are after the attention half.
+static int decode_layer_run(uint16_t* h, uint16_t* x, uint16_t* router_logits, float* y_partial,
+                            const hqm_decoder_layer* L, int ep_lo, int ep_n, int slots, const int32_t* pos, void* scratch,
+                            size_t scratch_bytes, void* stream) {
     using namespace hqm;
     HQM_CHECK_ARG(h && x && router_logits && pos, "decode_layer: null pointer");
     HQM_CHECK_ARG((reinterpret_cast<uintptr_t>(x) & 15u) == 0, "decode_layer: x must be 16-byte aligned");
     AttnPlan ap;
     MoeDecodePlan mp;
-    int rc = decoder_layer_plan(L, &ap, &mp);
+    int rc = decoder_layer_plan(L, slots, &ap, &mp);
     if (rc != HQM_OK) return rc;
-    const size_t need = SCRATCH_HEADER + ap.total() + mp.router_bytes + mp.up_bytes + mp.h_bytes + mp.down_bytes;
+    const size_t need = decoder_layer_bytes(ap, mp);
     if (scratch == nullptr || scratch_bytes < need) {
         set_error("decode_layer: scratch of %zu bytes given, %zu needed", scratch_bytes, need);
         return HQM_ERR_SCRATCH;
@@ -626,9 +700,11 @@ int hqm_decode_layer(uint16_t* h, uint16_t* x, uint16_t* router_logits, const hq
     float* o_part = (float*)(p + ap.x_bytes + ap.qkv_bytes + ap.q_bytes + ap.ctx_bytes);
     uint8_t* m0 = p + ap.total();
     float* topk_w = (float*)m0;                                    // [2] (+2 pad)
-    int32_t* topk_idx = (int32_t*)(topk_w + 4);                    // [2]
+    int32_t* topk_idx = (int32_t*)(topk_w + 4);                    // [2] (+2 pad)
+    float* local_w = topk_w + 8;                                   // [slots] (+pad): the launch slots' routing weights
+    int32_t* local_idx = (int32_t*)(topk_w + 12);                  // [slots]: index into `table`, -1 = unused
     float* up = (float*)(m0 + mp.router_bytes);
-    uint16_t* hh = (uint16_t*)(m0 + mp.router_bytes + mp.up_bytes);    // [2][F]
+    uint16_t* hh = (uint16_t*)(m0 + mp.router_bytes + mp.up_bytes);    // [slots][F]
     float* down = (float*)(m0 + mp.router_bytes + mp.up_bytes + mp.h_bytes);
 
     // 1. q, k, v projections of x
@@ -650,23 +726,23 @@ int hqm_decode_layer(uint16_t* h, uint16_t* x, uint16_t* router_logits, const hq
     // 3. output projection
     rc = launch_gemv_stream(o_part, ctx, nullptr, 1, oj, ap.o, st);
     if (rc != HQM_OK) return rc;
-    // 4. residual add, post-attention norm, router
+    // 4. residual add, post-attention norm, router (and the rank's launch slots)
     launch_overlapped_cluster(finalize_add_rmsnorm_router_kernel, NORM_CTAS, NORM_THREADS, 0, NORM_CTAS, st, h,
                               (const float*)o_part, A->ln_post, x2, hidden, A->rms_eps, split_of(ap.o), colmap_of(ap.o),
-                              L->gate_w, E, router_logits, topk_w, topk_idx);
+                              L->gate_w, E, router_logits, topk_w, topk_idx, ep_lo, ep_n, slots, local_w, local_idx);
     HQM_LAUNCH_CHECK();
-    // 5.-7. both chosen experts: [w1; w3] x 2, silu * mul, w2 x 2
+    // 5.-7. the slots' experts: [w1; w3] per slot, silu * mul, w2 per slot
     StreamJob gate_up{}, down_proj{};
     gate_up.table = down_proj.table = static_cast<const StreamEntry*>(L->table);
     gate_up.counters = down_proj.counters = counters;
-    for (int slot = 0; slot < 2; ++slot) {
+    for (int slot = 0; slot < slots; ++slot) {
         gate_up.w[2 * slot] = &L->w1;
         gate_up.w[2 * slot + 1] = &L->w3;
-        gate_up.sel[2 * slot] = gate_up.sel[2 * slot + 1] = topk_idx + slot;
+        gate_up.sel[2 * slot] = gate_up.sel[2 * slot + 1] = local_idx + slot;
         gate_up.which[2 * slot] = 0;
         gate_up.which[2 * slot + 1] = 2;
         down_proj.w[slot] = &L->w2;
-        down_proj.sel[slot] = topk_idx + slot;
+        down_proj.sel[slot] = local_idx + slot;
         down_proj.which[slot] = 1;
         down_proj.xrow[slot] = slot;
     }
@@ -677,10 +753,62 @@ int hqm_decode_layer(uint16_t* h, uint16_t* x, uint16_t* router_logits, const hq
     if (rc != HQM_OK) return rc;
     rc = launch_gemv_stream(down, hh, nullptr, 1, down_proj, mp.down, st);
     if (rc != HQM_OK) return rc;
+    if (y_partial) {
+        // 8'. this rank's weighted share of the block's output, fp32; the caller adds the ranks' shares
+        launch_overlapped(finalize_weighted_f32_kernel, (hidden + 255) / 256, 256, 0, st, y_partial, (const float*)down,
+                          (const float*)local_w, hidden, mp.down.col0[slots], split_of(mp.down), colmap_of(mp.down));
+        HQM_LAUNCH_CHECK();
+        return HQM_OK;
+    }
     // 8. weighted sum of the two experts, residual add, the next layer's input norm
     launch_overlapped_cluster(finalize_scatter_add_rmsnorm_kernel, NORM_CTAS, NORM_THREADS, 0, NORM_CTAS, st, h,
-                              (const float*)down, (const float*)topk_w, L->next_ln, x, hidden, mp.down.col0[2],
+                              (const float*)down, (const float*)local_w, L->next_ln, x, hidden, mp.down.col0[2],
                               A->rms_eps, split_of(mp.down), colmap_of(mp.down));
+    HQM_LAUNCH_CHECK();
+    return HQM_OK;
+}
+
+size_t hqm_decode_layer_scratch_bytes(const hqm_decoder_layer* L) {
+    hqm::AttnPlan ap;
+    hqm::MoeDecodePlan mp;
+    if (decoder_layer_plan(L, 2, &ap, &mp) != HQM_OK) return 0;
+    return decoder_layer_bytes(ap, mp);
+}
+
+int hqm_decode_layer(uint16_t* h, uint16_t* x, uint16_t* router_logits, const hqm_decoder_layer* L, const int32_t* pos,
+                     void* scratch, size_t scratch_bytes, void* stream) {
+    return decode_layer_run(h, x, router_logits, nullptr, L, 0, L ? L->n_experts : 0, 2, pos, scratch, scratch_bytes,
+                            stream);
+}
+
+static int ep_slots(int n_local) { return n_local < 2 ? 1 : 2; }
+
+size_t hqm_decode_layer_ep_scratch_bytes(const hqm_decoder_layer* L, int32_t n_local) {
+    hqm::AttnPlan ap;
+    hqm::MoeDecodePlan mp;
+    if (n_local < 1 || decoder_layer_plan(L, ep_slots(n_local), &ap, &mp) != HQM_OK) return 0;
+    return decoder_layer_bytes(ap, mp);
+}
+
+int hqm_decode_layer_ep(uint16_t* h, uint16_t* x_moe_unused, uint16_t* router_logits, float* y_partial,
+                        const hqm_decoder_layer* L, int32_t expert_lo, int32_t n_local, const int32_t* pos, void* scratch,
+                        size_t scratch_bytes, void* stream) {
+    using namespace hqm;
+    HQM_CHECK_ARG(y_partial != nullptr, "decode_layer_ep: null output");
+    HQM_CHECK_ARG(L && n_local >= 1 && expert_lo >= 0 && expert_lo + n_local <= L->n_experts,
+                  "decode_layer_ep: experts [%d, %d) are not a range of the layer's experts", expert_lo, expert_lo + n_local);
+    return decode_layer_run(h, x_moe_unused, router_logits, y_partial, L, expert_lo, n_local, ep_slots(n_local), pos,
+                            scratch, scratch_bytes, stream);
+}
+
+int hqm_add_f32_rmsnorm(uint16_t* h, const float* delta, const uint16_t* weight, uint16_t* x_out, int32_t hidden,
+                        float eps, void* stream) {
+    using namespace hqm;
+    HQM_CHECK_ARG(h && delta && weight && x_out && hidden > 0 && hidden <= NORM_CTAS * NORM_THREADS * NORM_PER_THREAD,
+                  "add_f32_rmsnorm: null pointer or hidden size %d outside (0, %d]", hidden,
+                  NORM_CTAS * NORM_THREADS * NORM_PER_THREAD);
+    launch_overlapped_cluster(add_f32_rmsnorm_kernel, NORM_CTAS, NORM_THREADS, 0, NORM_CTAS, (cudaStream_t)stream, h, delta,
+                              weight, x_out, (int)hidden, eps);
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }

@@ -190,13 +190,18 @@ int hqm_expert_ffn(uint16_t* out, const uint16_t* x, int64_t M, const int32_t* t
 
 namespace hqm {
 bool moe_decode_plan(int E, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3, MoeDecodePlan* mp) {
+    return moe_decode_plan_slots(E, 2, w1, w2, w3, mp);
+}
+bool moe_decode_plan_slots(int E, int slots, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3,
+                           MoeDecodePlan* mp) {
     const hqm_weight* up[4] = {w1, w3, w1, w3};
     const hqm_weight* down[2] = {w2, w2};
-    if (!same_format(w1, w3) || !gemv_stream_plan(up, 4, 1, &mp->up) || !gemv_stream_plan(down, 2, 1, &mp->down))
+    if (slots < 1 || slots > 2) return false;
+    if (!same_format(w1, w3) || !gemv_stream_plan(up, 2 * slots, 1, &mp->up) || !gemv_stream_plan(down, slots, 1, &mp->down))
         return false;
     mp->router_bytes = align_up((size_t)(4 + 4 + 2 * E + 1 + 4) * 4, 256);
     mp->up_bytes = align_up(gemv_stream_scratch_bytes(mp->up, 1), 256);
-    mp->h_bytes = align_up((size_t)2 * w1->N * 2, 256);
+    mp->h_bytes = align_up((size_t)slots * w1->N * 2, 256);
     mp->down_bytes = align_up(gemv_stream_scratch_bytes(mp->down, 1), 256);
     return true;
 }

@@ -266,15 +266,22 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
     // Table mode: the (up to four) descriptors the router's choice points at are fetched once per CTA into
     // shared memory, so that a warp starting a segment does not sit through an index load and a dependent
     // descriptor load before it can request its first weights.
+    // A negative index means "this layer is not here" (an expert-parallel rank that does not own the routed
+    // expert): its passes are skipped and its sums are written as zeros.
     __shared__ hqm_weight s_desc[STREAM_MAX_LAYERS];
+    __shared__ int s_absent[STREAM_MAX_LAYERS];
     if (ly.table) {
         constexpr int WORDS = (int)(sizeof(hqm_weight) / sizeof(uint32_t));
         if ((int)threadIdx.x < ly.count * WORDS) {
             const int l = threadIdx.x / WORDS, i = threadIdx.x % WORDS;
             // (__ldcg: the index may have been written by a kernel that finished while an earlier kernel on this
             // SM still had the previous value in L1)
-            const hqm_weight* src = &(ly.table + 3 * __ldcg(ly.sel[l]) + ly.which[l])->w;
-            reinterpret_cast<uint32_t*>(s_desc)[threadIdx.x] = reinterpret_cast<const uint32_t*>(src)[i];
+            const int idx = __ldcg(ly.sel[l]);
+            if (i == 0) s_absent[l] = idx < 0 ? 1 : 0;
+            if (idx >= 0) {
+                const hqm_weight* src = &(ly.table + 3 * idx + ly.which[l])->w;
+                reinterpret_cast<uint32_t*>(s_desc)[threadIdx.x] = reinterpret_cast<const uint32_t*>(src)[i];
+            }
         }
         __syncthreads();
     }
@@ -298,11 +305,12 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
     for (uint32_t L = L_begin; L < L_end;) {
         // ---- one segment: passes [pa, pb) of residue rho of layer `layer`
         const int rho_g = (int)(L / (uint32_t)PT), pa = (int)(L - (uint32_t)rho_g * (uint32_t)PT);
-        const int pb = min(PT, pa + (int)(L_end - L));
-        L += (uint32_t)(pb - pa);
+        const int pb_all = min(PT, pa + (int)(L_end - L));
+        L += (uint32_t)(pb_all - pa);
         int layer = 0;
 #pragma unroll
         for (int l = 1; l < STREAM_MAX_LAYERS; ++l) layer += (l < ly.count && rho_g >= ly.rho0[l]) ? 1 : 0;
+        const int pb = (ly.table && s_absent[layer]) ? pa : pb_all;      // an absent layer: no passes, zero sums
         const int rho = rho_g - ly.rho0[layer];
         const int P = ly.rho0[layer + 1] - ly.rho0[layer], G = ly.G[layer], C = ly.C[layer];
         const hqm_weight w = ly.table ? s_desc[layer] : ly.w[layer];
@@ -522,7 +530,7 @@ gemv_stream_kernel(float* __restrict__ partial, const uint16_t* __restrict__ x, 
             Meta d;
             Rows r;
             int sl = 0;
-            load_meta(d);
+            if (pa < pb) load_meta(d);
             for (int p = pa; p < pb; ++p) {
                 cp_async_wait<S::DEPTH - 1>();
                 fetch(sl, p, d, r);

@@ -117,6 +117,9 @@ struct MoeDecodePlan {
     size_t router_bytes, up_bytes, h_bytes, down_bytes;
 };
 bool moe_decode_plan(int E, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3, MoeDecodePlan* mp);
+// `slots` (1 or 2) experts per launch instead of the two routed ones (an expert-parallel rank's share).
+bool moe_decode_plan_slots(int E, int slots, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3,
+                           MoeDecodePlan* mp);
 
 // Dispatcher used by hqm_linear and by the expert FFN: picks the streaming
 // kernel when the layer's shape allows it, the generic one otherwise.

@@ -362,22 +362,26 @@ class ResidentMoe(nn.Module):
         """Forget the device-side descriptor table (call after the experts' tensors were replaced or moved)."""
         self._table = None
 
+    @staticmethod
+    def _build_table(experts, device):
+        """The device-side expert table (hqm_expert_table_build): (w1, w2, w3) of experts[0], experts[1], ..."""
+        lib = _cabi.lib()
+        n = 3 * len(experts)
+        descs = (_cabi.HqmWeight * n)()
+        for e, ex in enumerate(experts):
+            f = ResidentMoe._ffn(ex)
+            for i, lyr in enumerate((f.w1, f.w2, f.w3)):
+                descs[3 * e + i] = lyr.descriptor()
+        nbytes = lib.hqm_expert_table_bytes(n)
+        with torch.inference_mode(False):
+            host = torch.empty(nbytes + 64, dtype=torch.uint8)
+            off = (-host.data_ptr()) % 64
+            _cabi.check(lib.hqm_expert_table_build(C.c_void_p(host.data_ptr() + off), descs, n))
+            return host[off:off + nbytes].to(device)
+
     def _descriptor_table(self, device):
-        """The device-side expert table (hqm_expert_table_build): (w1, w2, w3) of expert 0, 1, ..."""
         if self._table is None:
-            lib = _cabi.lib()
-            n = 3 * len(self._experts)
-            descs = (_cabi.HqmWeight * n)()
-            for e, ex in enumerate(self._experts):
-                f = self._ffn(ex)
-                for i, lyr in enumerate((f.w1, f.w2, f.w3)):
-                    descs[3 * e + i] = lyr.descriptor()
-            nbytes = lib.hqm_expert_table_bytes(n)
-            with torch.inference_mode(False):
-                host = torch.empty(nbytes + 64, dtype=torch.uint8)
-                off = (-host.data_ptr()) % 64
-                _cabi.check(lib.hqm_expert_table_build(C.c_void_p(host.data_ptr() + off), descs, n))
-                self._table = host[off:off + nbytes].to(device)
+            self._table = self._build_table(self._experts, device)
         return self._table
 
     @torch.inference_mode()

@@ -145,3 +145,69 @@ class DecoderLayerDecode(nn.Module):
         _cabi.check(lib.hqm_decode_layer(_cabi.ptr(h), _cabi.ptr(x), _cabi.ptr(logits), C.byref(layer), _cabi.ptr(pos),
                                          _cabi.ptr(ws), ws.numel(), _cabi.stream_ptr(h.device)))
         return logits
+
+
+class ExpertParallelDecoderLayer(nn.Module):
+    """DecoderLayerDecode for one rank of an expert-parallel group (torch.distributed): attention, norms and router
+    are replicated, the rank holds `experts` = the layer's experts [expert_lo, expert_lo + len(experts)) and runs
+    those of the routed pair that are its own, without the host learning the routing (hqm_decode_layer_ep).  The
+    ranks' fp32 shares of the block output are added by ONE all-reduce on the compute stream, then the residual
+    add and the next layer's norm follow (hqm_add_f32_rmsnorm).  The sequence is fixed, so a decode step with it
+    can be captured in a CUDA graph.  The reference has no distributed code; the block that is sharded is
+    src/custom_layers.py:272-314.
+
+    attention: AttentionDecode (same weights on every rank); gate: nn.Linear over ALL n_experts (same on every
+    rank); next_ln as for DecoderLayerDecode; group: the process group (None: no reduction, a single rank)."""
+
+    def __init__(self, attention: AttentionDecode, gate, experts, expert_lo: int, n_experts: int, next_ln: torch.Tensor,
+                 group=None):
+        super().__init__()
+        assert 0 <= expert_lo and expert_lo + len(experts) <= n_experts and len(experts) >= 1
+        self.attention, self.gate, self.next_ln, self.group = attention, gate, next_ln, group
+        self.expert_lo, self.n_experts = expert_lo, n_experts
+        self._experts = list(experts)
+        self._table = None
+        self._layer, self._layer_key, self._gate_w = None, None, None
+        hidden = attention.n_heads * attention.head_dim
+        self.y_partial = torch.zeros((1, hidden), dtype=torch.float32, device=next_ln.device)
+
+    def _descriptor(self, device) -> _cabi.HqmDecoderLayer:
+        attn_desc = self.attention._descriptor()
+        if self._table is None:
+            self._table = ResidentMoe._build_table(self._experts, device)
+        key = (self.attention._layer_key, self.gate.weight.data_ptr(), self.next_ln.data_ptr(), self._table.data_ptr())
+        if self._layer is None or self._layer_key != key:
+            self._layer_key = key
+            hidden = self.attention.n_heads * self.attention.head_dim
+            gate = self.gate.weight
+            self._gate_w = gate if gate.dtype == torch.bfloat16 else gate.to(torch.bfloat16)
+            f0 = ResidentMoe._ffn(self._experts[0])
+            self._layer = _cabi.HqmDecoderLayer(
+                attn=attn_desc, gate_w=self._gate_w.data_ptr(), table=self._table.data_ptr(), w1=f0.w1.descriptor(),
+                w2=f0.w2.descriptor(), w3=f0.w3.descriptor(), next_ln=_bf16_vec(self.next_ln, hidden).data_ptr(),
+                n_experts=self.n_experts, reserved=0)
+        return self._layer
+
+    @torch.inference_mode()
+    def forward(self, h: torch.Tensor, x: torch.Tensor, pos: torch.Tensor):
+        """Same contract as DecoderLayerDecode.forward."""
+        hidden = h.shape[-1]
+        _bf16_vec(h, hidden), _bf16_vec(x, hidden)
+        assert pos.is_cuda and pos.dtype == torch.int32 and pos.numel() == 1
+        lib = _cabi.lib()
+        layer = self._descriptor(h.device)
+        n_local = len(self._experts)
+        need = lib.hqm_decode_layer_ep_scratch_bytes(C.byref(layer), n_local)
+        if need == 0:
+            raise ValueError(lib.hqm_last_error().decode() or "decoder layer: unsupported shapes")
+        ws = _scratch(h.device, need)
+        logits = torch.empty((1, self.n_experts), dtype=torch.bfloat16, device=h.device)
+        _cabi.check(lib.hqm_decode_layer_ep(_cabi.ptr(h), _cabi.ptr(x), _cabi.ptr(logits), _cabi.ptr(self.y_partial),
+                                            C.byref(layer), self.expert_lo, n_local, _cabi.ptr(pos), _cabi.ptr(ws),
+                                            ws.numel(), _cabi.stream_ptr(h.device)))
+        if self.group is not None:
+            import torch.distributed as dist
+            dist.all_reduce(self.y_partial, group=self.group)
+        _cabi.check(lib.hqm_add_f32_rmsnorm(_cabi.ptr(h), _cabi.ptr(self.y_partial), _cabi.ptr(self.next_ln), _cabi.ptr(x),
+                                            hidden, self.attention.rms_eps, _cabi.stream_ptr(h.device)))
+        return logits

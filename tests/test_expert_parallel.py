@@ -1,5 +1,6 @@
 """Expert-parallel MoE block: partition and combine logic on CPU ranks (gloo, world size 2), and the
 real thing on 2 GPUs when they are there."""
+import ctypes as C
 import os
 import socket
 
@@ -149,3 +150,69 @@ def test_two_gpu_ranks_match_the_oracle(combine):
         p.join(300)
         assert p.exitcode == 0
     assert result.get(timeout=5) < 1e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ranks", [1, 2, 4, 8])
+def test_expert_parallel_decoder_layer_on_one_gpu(ranks):
+    """The expert-parallel decoder layer with its ranks emulated one after the other on ONE GPU (each "rank" holds
+    only its experts; the all-reduce is a sum of the ranks' fp32 shares): residual stream, next-layer input, router
+    logits and cache rows are bit for bit those of the single-GPU layer, for every partition of the 8 experts."""
+    from mixtral_offloading_b200 import (AttentionDecode, DecoderLayerDecode, ExpertParallelDecoderLayer, ResidentMoe,
+                                         _cabi, add_rmsnorm)
+    from tests.helpers import layer_from_oracle, random_layer
+    from tests.test_gpu_parity import Cfg, make_expert
+    dev = torch.device("cuda:0")
+    HD, n_heads, n_kv, ffn, E, max_len = 128, 8, 2, 3584, 8, 16
+    hidden = n_heads * HD
+    g = torch.Generator().manual_seed(ranks)
+    shapes = [(hidden, hidden), (n_kv * HD, hidden), (n_kv * HD, hidden), (hidden, hidden)]
+    attn_ods = [random_layer(N, K, 4, 64, 40 + i, std=0.05) for i, (N, K) in enumerate(shapes)]
+    lns = [(1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16).to(dev) for _ in range(3)]
+
+    def attention():
+        return AttentionDecode(*[layer_from_oracle(od, dev) for od in attn_ods], lns[0], lns[1], n_heads, n_kv, HD, max_len)
+    experts = [make_expert(hidden, ffn, (random_layer(ffn, hidden, 2, 16, 100 + 3 * e), random_layer(hidden, ffn, 2, 16, 101 + 3 * e),
+                                         random_layer(ffn, hidden, 2, 16, 102 + 3 * e))) for e in range(E)]
+    gate = torch.nn.Linear(hidden, E, bias=False, dtype=torch.bfloat16, device=dev)
+    gate.weight.data.copy_((0.5 * torch.randn(E, hidden, generator=g)).to(torch.bfloat16))
+    single = DecoderLayerDecode(attention(), ResidentMoe(Cfg(hidden, ffn, E), 0, gate, experts), lns[2])
+    per = E // ranks
+    parts = [ExpertParallelDecoderLayer(attention(), gate, experts[r * per:(r + 1) * per], r * per, E, lns[2])
+             for r in range(ranks)]
+    lib = _cabi.lib()
+    pos = torch.zeros(1, dtype=torch.int32, device=dev)
+    seen = set()
+    for step in range(6):
+        h0 = torch.randn(1, hidden, generator=g).to(torch.bfloat16).to(dev)
+        h_a = h0.clone()
+        x_a = add_rmsnorm(h_a, None, lns[0], 1e-5)
+        logits_a = single(h_a, x_a, pos)
+        seen.update(logits_a.float().view(-1).topk(2).indices.tolist())
+        # every rank: attention half + its experts' share; then the sum of the shares finishes the layer on each
+        states, shares = [], []
+        for layer in parts:
+            h = h0.clone()
+            x = add_rmsnorm(h, None, lns[0], 1e-5)
+            d = layer._descriptor(dev)
+            need = lib.hqm_decode_layer_ep_scratch_bytes(C.byref(d), per)
+            assert need > 0
+            from mixtral_offloading_b200.custom_layers import _scratch
+            ws = _scratch(dev, need)
+            logits = torch.empty((1, E), dtype=torch.bfloat16, device=dev)
+            _cabi.check(lib.hqm_decode_layer_ep(_cabi.ptr(h), _cabi.ptr(x), _cabi.ptr(logits), _cabi.ptr(layer.y_partial),
+                                                C.byref(d), layer.expert_lo, per, _cabi.ptr(pos), _cabi.ptr(ws), ws.numel(),
+                                                _cabi.stream_ptr(dev)))
+            states.append((h, x, logits))
+            shares.append(layer.y_partial.clone())
+        total = torch.stack(shares).sum(0)
+        assert sum(int((s != 0).any()) for s in shares) <= 2          # at most two ranks own a routed expert
+        for r, (h, x, logits) in enumerate(states):
+            _cabi.check(lib.hqm_add_f32_rmsnorm(_cabi.ptr(h), _cabi.ptr(total), _cabi.ptr(lns[2]), _cabi.ptr(x), hidden,
+                                                1e-5, _cabi.stream_ptr(dev)))
+            assert torch.equal(logits, logits_a), (step, r)
+            assert torch.equal(h, h_a) and torch.equal(x, x_a), (step, r)
+            assert torch.equal(parts[r].attention.k_cache[:, step], single.attention.k_cache[:, step])
+        pos += 1
+    assert len(seen) > 2
+    assert lib.hqm_device_error() == 0
