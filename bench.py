@@ -683,7 +683,7 @@ def run_decode_ep(args):
     captured, otherwise issued eagerly."""
     import torch.distributed as dist
     from mixtral_offloading_b200 import (AttentionDecode, BaseQuantizeConfig, ExpertParallelDecoderLayer,
-                                         HQQLinearTritonSavable, MixtralDecodeModel)
+                                         HQQLinearTritonSavable, MixtralDecodeModel, PeerExchange)
 
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -731,8 +731,19 @@ def run_decode_ep(args):
     embed = rnd(V, H, std=0.02).to(torch.bfloat16)
     lm_head = rnd(V, H, std=0.02).to(torch.bfloat16)
     ln_f = torch.ones(H, dtype=torch.bfloat16, device=dev)
+    exchange = None
+    if args.exchange == "peer":
+        try:
+            exchange = PeerExchange(dist.group.WORLD, H, dev)
+        except Exception as exc:                      # no symmetric memory on this box: the NCCL all-reduce serves
+            if rank == 0:
+                print(f"peer-memory exchange unavailable ({type(exc).__name__}: {exc}); using NCCL", file=sys.stderr)
+    ok = torch.tensor([1 if exchange is not None else 0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if int(ok.item()) == 0:
+        exchange = None
     layers = [ExpertParallelDecoderLayer(b["attn"], b["gate"], b["pool"], lo, E, built[i + 1]["ln1"] if i + 1 < L else ln_f,
-                                         group=dist.group.WORLD) for i, b in enumerate(built)]
+                                         group=dist.group.WORLD, exchange=exchange) for i, b in enumerate(built)]
     model = MixtralDecodeModel(embed, layers, built[0]["ln1"], lm_head)
     tok, pos32 = model.token, model.position
     lib = __import__("mixtral_offloading_b200")._cabi.lib()
@@ -824,12 +835,13 @@ def run_decode_ep(args):
             "config": {"workload": decode_workload_name(L, args.context).replace("on one GPU", f"expert-parallel over {world} GPUs")
                        + ("" if L == 32 else f"; value scales the measured step time by 32/{L}"),
                        "parallelism": f"ep{world}", "per_gpu": f"{per} of 8 experts of every layer; attention, norms, router, "
-                       "embeddings and lm_head replicated; one sequence", "collective": "one fp32 all-reduce of (1, 4096) per "
-                       "layer on the compute stream (NCCL)", "step_in_cuda_graph": graphed,
+                       "embeddings and lm_head replicated; one sequence", "collective": ("per layer every rank's kernel stores its fp32 share of the "
+                       "block output (1, 4096) into all ranks' buffers over NVLink (peer stores + flags), the next kernel adds them: "
+                       "no collective call") if exchange is not None else "one fp32 NCCL all-reduce of (1, 4096) per layer on the compute stream", "step_in_cuda_graph": graphed,
                        "l2": f"a rank's step touches up to {crit_bytes / 1e9:.2f} GB of weights and cache (> 126 MB L2)",
                        "ranks_decoded_the_same_tokens": ranks_agree},
             "critical_path_bytes_per_step": crit_bytes, "hbm_frac_of_critical_path": crit_bytes / (ms * scale / 32 * L * 1e-3) / 1e9 / peak,
-            "allreduce_us": allreduce_us, "allreduce_share_of_step": L * allreduce_us * 1e-3 / ms,
+            "nccl_allreduce_us": allreduce_us, "nccl_allreduce_x_layers_over_step": L * allreduce_us * 1e-3 / ms,
             "roofline": roofline_of_linear(kernel_ms), "cpu_baseline": None,
             "e2e": {"value": 1e3 / (ms_e2e * scale), "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": 8,
                     "d2h_bytes_per_step": 8},
@@ -1134,6 +1146,9 @@ def main():
                          "configs[4](b)); expert: one expert FFN per step (configs[1]); moe: one MoE block per step, "
                          "expert-parallel over the ranks; offload: ExpertCache with half the experts in host memory")
     ap.add_argument("--combine", default="all_reduce", choices=["all_reduce", "all_to_all"])
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="expert-parallel decode: how the ranks' shares of a MoE block's output meet (peer: stores into "
+                         "peer memory from inside the kernels; nccl: an all-reduce)")
     ap.add_argument("--replicas", action="store_true",
                     help="with --gpus N > 1: N independent replicas, one sequence each (no data-path collective), instead "
                          "of ONE sequence with the experts sharded over the ranks")

@@ -64,7 +64,8 @@ int hqm_version(void);
 int64_t hqm_launch_count(void);
 /* 1 if a bounded wait inside a tensor-core GEMM launch ever ran out (that launch skipped its work),
  * 2 if hqm_attn_decode was given a position outside its cache, 3 if a streaming launch found the header of its
- * scratch buffer not zeroed (see hqm_scratch_init; its result is then incomplete), 0 otherwise, -1 on a CUDA error.  Reading a
+ * scratch buffer not zeroed (see hqm_scratch_init; its result is then incomplete), 4 if an expert-parallel
+ * exchange gave up waiting for a peer, 0 otherwise, -1 on a CUDA error.  Reading a
  * non-zero value clears it.  Synchronises the device; meant for tests and start-up checks. */
 int hqm_device_error(void);
 /* No counterpart in the reference.  The streaming kernels and their reductions are launched so that a
@@ -246,11 +247,31 @@ int hqm_decode_layer(uint16_t* h, uint16_t* x, uint16_t* router_logits, const hq
  * the rank's fp32 share of the MoE block's output: sum over its slots of bf16(weight * bf16(expert output)).
  * The caller adds the ranks' shares (an all-reduce on the same stream; every term is a bf16 value and at most two
  * are non-zero, so the fp32 sum is exact) and finishes the layer with hqm_add_f32_rmsnorm(h, y_sum, next_ln, x),
- * which gives bit for bit what hqm_decode_layer gives on one GPU. */
+ * which gives bit for bit what hqm_decode_layer gives on one GPU.
+ *
+ * With `comm` set the exchange needs no collective library: the kernel that forms the rank's share stores it
+ * straight into EVERY rank's exchange buffer over NVLink (plain peer stores, then one flag per 256 elements), and
+ * hqm_ep_combine_add_rmsnorm waits for all ranks' flags, adds the shares in rank order and finishes the layer:
+ * two launches between the experts and the next layer.  Each rank provides hqm_ep_exchange_bytes(world, hidden)
+ * bytes of zeroed device memory that its peers can address (symmetric / IPC-mapped memory); shares[r] is rank r's
+ * buffer as seen from this rank, flags[r] the same buffer + hqm_ep_exchange_flags_offset(); seq is one zeroed
+ * uint32 in this rank's own memory.  All ranks must make the same sequence of exchanges.  Waits on a peer are
+ * bounded (a fraction of a second); a flag that never arrives makes hqm_device_error() return 4. */
+typedef struct hqm_ep_comm {
+    int32_t rank, world;      /* world <= 8 */
+    int32_t hidden, reserved;
+    float* shares[8];
+    uint32_t* flags[8];
+    uint32_t* seq;
+} hqm_ep_comm;
+size_t hqm_ep_exchange_bytes(int32_t world, int32_t hidden);
+size_t hqm_ep_exchange_flags_offset(int32_t world, int32_t hidden);
 size_t hqm_decode_layer_ep_scratch_bytes(const hqm_decoder_layer* layer, int32_t n_local);
-int hqm_decode_layer_ep(uint16_t* h, uint16_t* x, uint16_t* router_logits, float* y_partial,
+int hqm_decode_layer_ep(uint16_t* h, uint16_t* x, uint16_t* router_logits, float* y_partial, const hqm_ep_comm* comm,
                         const hqm_decoder_layer* layer, int32_t expert_lo, int32_t n_local, const int32_t* pos,
                         void* scratch, size_t scratch_bytes, void* stream);
+int hqm_ep_combine_add_rmsnorm(uint16_t* h, const hqm_ep_comm* comm, const uint16_t* weight, uint16_t* x_out,
+                               int32_t hidden, float eps, void* stream);
 /* h = bf16(h + bf16(delta)) with delta in fp32; x_out = rmsnorm(h) * weight (see hqm_add_rmsnorm). */
 int hqm_add_f32_rmsnorm(uint16_t* h, const float* delta, const uint16_t* weight, uint16_t* x_out, int32_t hidden,
                         float eps, void* stream);

@@ -7,7 +7,8 @@ from .build_model import OffloadConfig, QuantConfig, make_empty_expert  # noqa: 
 from .custom_layers import (HQQLinearTritonSavable, MixtralBLockSparseTop2MLP_HQQ, ResidentMoe,  # noqa: F401
                             SparseMoeWrapper)
 from .decode_model import MixtralDecodeModel  # noqa: F401
-from .decoder import AttentionDecode, DecoderLayerDecode, ExpertParallelDecoderLayer, add_rmsnorm  # noqa: F401
+from .decoder import (AttentionDecode, DecoderLayerDecode, ExpertParallelDecoderLayer, PeerExchange,  # noqa: F401
+                      add_rmsnorm)
 from .expert_cache import ExpertCache  # noqa: F401
 from .expert_wrapper import MixtralExpertWrapper  # noqa: F401
 from .quantize import BaseQuantizeConfig  # noqa: F401

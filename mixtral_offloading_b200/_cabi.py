@@ -45,6 +45,14 @@ class HqmDecoderLayer(C.Structure):
     ]
 
 
+class HqmEpComm(C.Structure):
+    """struct hqm_ep_comm."""
+    _fields_ = [
+        ("rank", C.c_int32), ("world", C.c_int32), ("hidden", C.c_int32), ("reserved", C.c_int32),
+        ("shares", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("seq", C.c_void_p),
+    ]
+
+
 _P = C.c_void_p
 _I64 = C.c_int64
 _I32 = C.c_int32
@@ -82,7 +90,11 @@ SIGNATURES = {
     "hqm_decode_layer_scratch_bytes": (C.c_size_t, [C.POINTER(HqmDecoderLayer)]),
     "hqm_decode_layer": (C.c_int, [_P, _P, _P, C.POINTER(HqmDecoderLayer), _P, _P, C.c_size_t, _P]),
     "hqm_decode_layer_ep_scratch_bytes": (C.c_size_t, [C.POINTER(HqmDecoderLayer), _I32]),
-    "hqm_decode_layer_ep": (C.c_int, [_P, _P, _P, _P, C.POINTER(HqmDecoderLayer), _I32, _I32, _P, _P, C.c_size_t, _P]),
+    "hqm_ep_exchange_bytes": (C.c_size_t, [_I32, _I32]),
+    "hqm_ep_exchange_flags_offset": (C.c_size_t, [_I32, _I32]),
+    "hqm_decode_layer_ep": (C.c_int, [_P, _P, _P, _P, C.POINTER(HqmEpComm), C.POINTER(HqmDecoderLayer), _I32, _I32, _P, _P,
+                                      C.c_size_t, _P]),
+    "hqm_ep_combine_add_rmsnorm": (C.c_int, [_P, C.POINTER(HqmEpComm), _P, _P, _I32, C.c_float, _P]),
     "hqm_add_f32_rmsnorm": (C.c_int, [_P, _P, _P, _P, _I32, C.c_float, _P]),
     "hqm_add_rmsnorm": (C.c_int, [_P, _P, _P, _P, _I32, C.c_float, _P]),
     "hqm_router_top2": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),

@@ -293,6 +293,106 @@ __global__ void __launch_bounds__(256) finalize_weighted_f32_kernel(float* __res
     }
 }
 
+// ---- the expert-parallel exchange over peer memory ---------------------------------------------------
+// Every rank keeps a buffer [2][world][hidden] fp32 ("shares": one row per rank, two generations) and flags
+// [2][world][EP_MAX_CHUNKS] that its peers write with plain stores over NVLink.  An exchange has a number s
+// (1, 2, ...; every rank counts its own in device memory and all ranks make the same calls, so the numbers agree):
+// the publish kernel writes this rank's row of generation s & 1 into EVERY rank's buffer, fences, and then stores
+// s into the matching flags, one per 256-element chunk; the combine kernel waits until the flags of all ranks for
+// the chunks it reads show s, adds the rows in rank order and goes on with the residual add and the norm.  A rank
+// cannot publish exchange s + 1 before it has combined s, which needs every peer's share of s, which a peer
+// publishes only after combining s - 1: nobody is more than one exchange ahead, so two generations are enough.
+// Waits are bounded: when a flag does not arrive the kernel records error 4 and goes on with what is there.
+constexpr int EP_CHUNK = 256;
+constexpr int EP_MAX_CHUNKS = 64;
+constexpr uint32_t EP_SPIN_LIMIT = 1u << 21;
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// finalize_weighted_f32_kernel whose result goes to every rank's share buffer instead of local memory.
+// One CTA per chunk of EP_CHUNK elements.
+__global__ void __launch_bounds__(EP_CHUNK) finalize_weighted_publish_kernel(const float* __restrict__ partial,
+                                                                             const float* __restrict__ route_w, int H,
+                                                                             int row, Split sp, ColMap cm, hqm_ep_comm comm) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const uint32_t s = *reinterpret_cast<volatile uint32_t*>(comm.seq) + 1u;
+    const int gen = (int)(s & 1u);
+    const int i = blockIdx.x * EP_CHUNK + threadIdx.x;
+    if (i < H) {
+        float acc = 0.f;
+#pragma unroll
+        for (int l = 0; l < STREAM_MAX_LAYERS; ++l) {
+            if (l < cm.count) {
+                const float v = round_bf16(round_bf16(partial_sum<true>(partial, sp, cm, 0, layer_col0(cm, l) + i, row, row)) * route_w[l]);
+                acc = (l == 0) ? v : round_bf16(acc + v);
+            }
+        }
+        const size_t at = ((size_t)gen * comm.world + comm.rank) * (size_t)H + i;
+        for (int r = 0; r < comm.world; ++r) comm.shares[r][at] = acc;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if ((int)threadIdx.x < comm.world)
+        st_release_sys(comm.flags[threadIdx.x] + ((size_t)gen * comm.world + comm.rank) * EP_MAX_CHUNKS + blockIdx.x, s);
+}
+
+// h = bf16(h + bf16(sum over ranks of their shares of exchange s)), x = rmsnorm(h) * w; closes exchange s.
+__global__ void __launch_bounds__(NORM_THREADS) ep_combine_add_rmsnorm_kernel(uint16_t* __restrict__ h,
+                                                                              const uint16_t* __restrict__ w,
+                                                                              uint16_t* __restrict__ x, int H, float eps,
+                                                                              hqm_ep_comm comm, int* __restrict__ error_flag) {
+    __shared__ float red[32];
+    __shared__ float mine;
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const uint32_t s = *reinterpret_cast<volatile uint32_t*>(comm.seq) + 1u;
+    const int gen = (int)(s & 1u);
+    const float* shares = comm.shares[comm.rank] + (size_t)gen * comm.world * H;
+    const uint32_t* flags = comm.flags[comm.rank] + (size_t)gen * comm.world * EP_MAX_CHUNKS;
+    const int stride = NORM_CTAS * NORM_THREADS, first = blockIdx.x * NORM_THREADS + threadIdx.x;
+    float v[NORM_PER_THREAD];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NORM_PER_THREAD; ++j) {
+        const int i = first + j * stride;
+        v[j] = 0.f;
+        if (i < H) {
+            const int chunk = i / EP_CHUNK;
+            float sum = 0.f;
+            for (int r = 0; r < comm.world; ++r) {
+                const uint32_t* f = flags + r * EP_MAX_CHUNKS + chunk;
+                uint32_t spins = 0;
+                while (ld_acquire_sys(f) != s) {
+                    if (++spins > EP_SPIN_LIMIT) {
+                        if (error_flag) atomicExch(error_flag, 4);
+                        break;
+                    }
+                    __nanosleep(100);
+                }
+                sum += __ldcg(shares + (size_t)r * H + i);
+            }
+            v[j] = round_bf16(bf16_bits_to_float(h[i]) + round_bf16(sum));
+            h[i] = float_to_bf16_bits(v[j]);
+        }
+        ss += v[j] * v[j];
+    }
+    const float rstd = rsqrtf(cluster_sum(ss, red, &mine) / (float)H + eps);
+#pragma unroll
+    for (int j = 0; j < NORM_PER_THREAD; ++j) {
+        const int i = first + j * stride;
+        if (i < H) x[i] = float_to_bf16_bits(bf16_bits_to_float(w[i]) * round_bf16(v[j] * rstd));
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) *comm.seq = s;            // every CTA read the counter before cluster_sum's barriers
+}
+
 // h = bf16(h + bf16(delta)) with delta in fp32 (the all-reduced expert-parallel partials), x = rmsnorm(h) * w.
 __global__ void __launch_bounds__(NORM_THREADS) add_f32_rmsnorm_kernel(uint16_t* __restrict__ h,
                                                                        const float* __restrict__ delta,
@@ -673,7 +773,7 @@ static size_t decoder_layer_bytes(const hqm::AttnPlan& ap, const hqm::MoeDecodeP
 
 // y_partial == nullptr: one GPU, the layer is finished (residual add, next norm).  Otherwise the rank's fp32
 // contribution to the MoE block's output goes to y_partial and h / x are left as they are after the attention half.
-static int decode_layer_run(uint16_t* h, uint16_t* x, uint16_t* router_logits, float* y_partial,
+static int decode_layer_run(uint16_t* h, uint16_t* x, uint16_t* router_logits, float* y_partial, const hqm_ep_comm* comm,
                             const hqm_decoder_layer* L, int ep_lo, int ep_n, int slots, const int32_t* pos, void* scratch,
                             size_t scratch_bytes, void* stream) {
     using namespace hqm;
@@ -753,6 +853,14 @@ static int decode_layer_run(uint16_t* h, uint16_t* x, uint16_t* router_logits, f
     if (rc != HQM_OK) return rc;
     rc = launch_gemv_stream(down, hh, nullptr, 1, down_proj, mp.down, st);
     if (rc != HQM_OK) return rc;
+    if (comm) {
+        // 8''. this rank's weighted share, written straight into every rank's exchange buffer
+        launch_overlapped(finalize_weighted_publish_kernel, (hidden + EP_CHUNK - 1) / EP_CHUNK, EP_CHUNK, 0, st,
+                          (const float*)down, (const float*)local_w, hidden, mp.down.col0[slots], split_of(mp.down),
+                          colmap_of(mp.down), *comm);
+        HQM_LAUNCH_CHECK();
+        return HQM_OK;
+    }
     if (y_partial) {
         // 8'. this rank's weighted share of the block's output, fp32; the caller adds the ranks' shares
         launch_overlapped(finalize_weighted_f32_kernel, (hidden + 255) / 256, 256, 0, st, y_partial, (const float*)down,
@@ -777,8 +885,8 @@ size_t hqm_decode_layer_scratch_bytes(const hqm_decoder_layer* L) {
 
 int hqm_decode_layer(uint16_t* h, uint16_t* x, uint16_t* router_logits, const hqm_decoder_layer* L, const int32_t* pos,
                      void* scratch, size_t scratch_bytes, void* stream) {
-    return decode_layer_run(h, x, router_logits, nullptr, L, 0, L ? L->n_experts : 0, 2, pos, scratch, scratch_bytes,
-                            stream);
+    return decode_layer_run(h, x, router_logits, nullptr, nullptr, L, 0, L ? L->n_experts : 0, 2, pos, scratch,
+                            scratch_bytes, stream);
 }
 
 static int ep_slots(int n_local) { return n_local < 2 ? 1 : 2; }
@@ -790,15 +898,52 @@ size_t hqm_decode_layer_ep_scratch_bytes(const hqm_decoder_layer* L, int32_t n_l
     return decoder_layer_bytes(ap, mp);
 }
 
-int hqm_decode_layer_ep(uint16_t* h, uint16_t* x_moe_unused, uint16_t* router_logits, float* y_partial,
-                        const hqm_decoder_layer* L, int32_t expert_lo, int32_t n_local, const int32_t* pos, void* scratch,
-                        size_t scratch_bytes, void* stream) {
+static int check_comm(const hqm_ep_comm* comm, int hidden) {
     using namespace hqm;
-    HQM_CHECK_ARG(y_partial != nullptr, "decode_layer_ep: null output");
+    HQM_CHECK_ARG(comm->world >= 1 && comm->world <= 8 && comm->rank >= 0 && comm->rank < comm->world && comm->seq,
+                  "ep exchange: rank %d of %d (at most 8) or null counter", comm->rank, comm->world);
+    HQM_CHECK_ARG(comm->hidden == hidden && (hidden + EP_CHUNK - 1) / EP_CHUNK <= EP_MAX_CHUNKS,
+                  "ep exchange: buffers sized for hidden = %d, layer has %d (at most %d)", comm->hidden, hidden,
+                  EP_CHUNK * EP_MAX_CHUNKS);
+    for (int r = 0; r < comm->world; ++r)
+        HQM_CHECK_ARG(comm->shares[r] && comm->flags[r], "ep exchange: null buffer of rank %d", r);
+    return HQM_OK;
+}
+
+size_t hqm_ep_exchange_bytes(int32_t world, int32_t hidden) {
+    if (world < 1 || world > 8 || hidden < 1) return 0;
+    return (size_t)2 * world * hidden * sizeof(float) + (size_t)2 * world * hqm::EP_MAX_CHUNKS * sizeof(uint32_t);
+}
+
+size_t hqm_ep_exchange_flags_offset(int32_t world, int32_t hidden) { return (size_t)2 * world * hidden * sizeof(float); }
+
+int hqm_decode_layer_ep(uint16_t* h, uint16_t* x_moe_unused, uint16_t* router_logits, float* y_partial,
+                        const hqm_ep_comm* comm, const hqm_decoder_layer* L, int32_t expert_lo, int32_t n_local,
+                        const int32_t* pos, void* scratch, size_t scratch_bytes, void* stream) {
+    using namespace hqm;
+    HQM_CHECK_ARG(y_partial != nullptr || comm != nullptr, "decode_layer_ep: neither an output nor an exchange");
     HQM_CHECK_ARG(L && n_local >= 1 && expert_lo >= 0 && expert_lo + n_local <= L->n_experts,
                   "decode_layer_ep: experts [%d, %d) are not a range of the layer's experts", expert_lo, expert_lo + n_local);
-    return decode_layer_run(h, x_moe_unused, router_logits, y_partial, L, expert_lo, n_local, ep_slots(n_local), pos,
+    if (comm) {
+        const int rc = check_comm(comm, L->attn.q.K);
+        if (rc != HQM_OK) return rc;
+    }
+    return decode_layer_run(h, x_moe_unused, router_logits, y_partial, comm, L, expert_lo, n_local, ep_slots(n_local), pos,
                             scratch, scratch_bytes, stream);
+}
+
+int hqm_ep_combine_add_rmsnorm(uint16_t* h, const hqm_ep_comm* comm, const uint16_t* weight, uint16_t* x_out,
+                               int32_t hidden, float eps, void* stream) {
+    using namespace hqm;
+    HQM_CHECK_ARG(h && comm && weight && x_out && hidden > 0 && hidden <= NORM_CTAS * NORM_THREADS * NORM_PER_THREAD,
+                  "ep_combine: null pointer or hidden size %d outside (0, %d]", hidden,
+                  NORM_CTAS * NORM_THREADS * NORM_PER_THREAD);
+    const int rc = check_comm(comm, hidden);
+    if (rc != HQM_OK) return rc;
+    launch_overlapped_cluster(ep_combine_add_rmsnorm_kernel, NORM_CTAS, NORM_THREADS, 0, NORM_CTAS, (cudaStream_t)stream, h,
+                              weight, x_out, (int)hidden, eps, *comm, tc_error_ptr());
+    HQM_LAUNCH_CHECK();
+    return HQM_OK;
 }
 
 int hqm_add_f32_rmsnorm(uint16_t* h, const float* delta, const uint16_t* weight, uint16_t* x_out, int32_t hidden,

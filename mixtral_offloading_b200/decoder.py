@@ -147,6 +147,36 @@ class DecoderLayerDecode(nn.Module):
         return logits
 
 
+class PeerExchange:
+    """The buffers of the expert-parallel exchange over peer memory (struct hqm_ep_comm): every rank allocates
+    hqm_ep_exchange_bytes() of symmetric memory (torch.distributed._symmetric_memory: device memory that the other
+    ranks of the node map into their address space), zeroes it, and learns its peers' addresses at the rendezvous.
+    One object serves all layers of a model (they exchange one after the other)."""
+
+    def __init__(self, group, hidden: int, device: torch.device):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        lib = _cabi.lib()
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        nbytes = lib.hqm_ep_exchange_bytes(self.world, hidden)
+        if nbytes == 0:
+            raise ValueError(f"expert-parallel exchange: {self.world} ranks / hidden {hidden} not supported")
+        with torch.inference_mode(False):
+            self.buffer = symm_mem.empty(nbytes // 4, dtype=torch.float32, device=device)
+            self.buffer.zero_()
+            self.seq = torch.zeros(1, dtype=torch.int32, device=device)
+        self.handle = symm_mem.rendezvous(self.buffer, group)
+        ptrs = list(self.handle.buffer_ptrs)
+        off = lib.hqm_ep_exchange_flags_offset(self.world, hidden)
+        comm = _cabi.HqmEpComm(rank=self.rank, world=self.world, hidden=hidden, reserved=0, seq=self.seq.data_ptr())
+        for r in range(self.world):
+            comm.shares[r] = ptrs[r]
+            comm.flags[r] = ptrs[r] + off
+        self.comm = comm
+        torch.cuda.synchronize(device)
+        dist.barrier(group)                      # everybody's buffer is zero before anybody publishes
+
+
 class ExpertParallelDecoderLayer(nn.Module):
     """DecoderLayerDecode for one rank of an expert-parallel group (torch.distributed): attention, norms and router
     are replicated, the rank holds `experts` = the layer's experts [expert_lo, expert_lo + len(experts)) and runs
@@ -157,13 +187,16 @@ class ExpertParallelDecoderLayer(nn.Module):
     src/custom_layers.py:272-314.
 
     attention: AttentionDecode (same weights on every rank); gate: nn.Linear over ALL n_experts (same on every
-    rank); next_ln as for DecoderLayerDecode; group: the process group (None: no reduction, a single rank)."""
+    rank); next_ln as for DecoderLayerDecode; group: the process group (None: no reduction, a single rank).
+    exchange: a PeerExchange; with it the ranks' shares travel by peer stores from inside the library's kernels
+    (no collective call, two launches between the experts and the next layer) instead of the NCCL all-reduce."""
 
     def __init__(self, attention: AttentionDecode, gate, experts, expert_lo: int, n_experts: int, next_ln: torch.Tensor,
-                 group=None):
+                 group=None, exchange=None):
         super().__init__()
         assert 0 <= expert_lo and expert_lo + len(experts) <= n_experts and len(experts) >= 1
         self.attention, self.gate, self.next_ln, self.group = attention, gate, next_ln, group
+        self.exchange = exchange
         self.expert_lo, self.n_experts = expert_lo, n_experts
         self._experts = list(experts)
         self._table = None
@@ -202,7 +235,15 @@ class ExpertParallelDecoderLayer(nn.Module):
             raise ValueError(lib.hqm_last_error().decode() or "decoder layer: unsupported shapes")
         ws = _scratch(h.device, need)
         logits = torch.empty((1, self.n_experts), dtype=torch.bfloat16, device=h.device)
-        _cabi.check(lib.hqm_decode_layer_ep(_cabi.ptr(h), _cabi.ptr(x), _cabi.ptr(logits), _cabi.ptr(self.y_partial),
+        if self.exchange is not None:
+            comm = C.byref(self.exchange.comm)
+            _cabi.check(lib.hqm_decode_layer_ep(_cabi.ptr(h), _cabi.ptr(x), _cabi.ptr(logits), None, comm, C.byref(layer),
+                                                self.expert_lo, n_local, _cabi.ptr(pos), _cabi.ptr(ws), ws.numel(),
+                                                _cabi.stream_ptr(h.device)))
+            _cabi.check(lib.hqm_ep_combine_add_rmsnorm(_cabi.ptr(h), comm, _cabi.ptr(self.next_ln), _cabi.ptr(x), hidden,
+                                                       self.attention.rms_eps, _cabi.stream_ptr(h.device)))
+            return logits
+        _cabi.check(lib.hqm_decode_layer_ep(_cabi.ptr(h), _cabi.ptr(x), _cabi.ptr(logits), _cabi.ptr(self.y_partial), None,
                                             C.byref(layer), self.expert_lo, n_local, _cabi.ptr(pos), _cabi.ptr(ws),
                                             ws.numel(), _cabi.stream_ptr(h.device)))
         if self.group is not None:

@@ -201,8 +201,8 @@ def test_expert_parallel_decoder_layer_on_one_gpu(ranks):
             ws = _scratch(dev, need)
             logits = torch.empty((1, E), dtype=torch.bfloat16, device=dev)
             _cabi.check(lib.hqm_decode_layer_ep(_cabi.ptr(h), _cabi.ptr(x), _cabi.ptr(logits), _cabi.ptr(layer.y_partial),
-                                                C.byref(d), layer.expert_lo, per, _cabi.ptr(pos), _cabi.ptr(ws), ws.numel(),
-                                                _cabi.stream_ptr(dev)))
+                                                None, C.byref(d), layer.expert_lo, per, _cabi.ptr(pos), _cabi.ptr(ws),
+                                                ws.numel(), _cabi.stream_ptr(dev)))
             states.append((h, x, logits))
             shares.append(layer.y_partial.clone())
         total = torch.stack(shares).sum(0)
@@ -216,3 +216,89 @@ def test_expert_parallel_decoder_layer_on_one_gpu(ranks):
         pos += 1
     assert len(seen) > 2
     assert lib.hqm_device_error() == 0
+
+
+def _decode_problem(dev):
+    """A small decoder layer (8 heads, 8 experts of 3584) from fixed seeds: the same tensors on every rank."""
+    from mixtral_offloading_b200 import AttentionDecode
+    from tests.helpers import layer_from_oracle
+    from tests.test_gpu_parity import make_expert
+    import tests.test_gpu_parity as tp
+    tp.DEV = dev
+    HD, n_heads, n_kv, ffn, E, max_len = 128, 8, 2, 3584, 8, 16
+    hidden = n_heads * HD
+    g = torch.Generator().manual_seed(77)
+    shapes = [(hidden, hidden), (n_kv * HD, hidden), (n_kv * HD, hidden), (hidden, hidden)]
+    attn_ods = [random_layer(N, K, 4, 64, 40 + i, std=0.05) for i, (N, K) in enumerate(shapes)]
+    lns = [(1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16).to(dev) for _ in range(3)]
+    attn = AttentionDecode(*[layer_from_oracle(od, dev) for od in attn_ods], lns[0], lns[1], n_heads, n_kv, HD, max_len)
+    gate = torch.nn.Linear(hidden, E, bias=False, dtype=torch.bfloat16, device=dev)
+    gate.weight.data.copy_((0.5 * torch.randn(E, hidden, generator=g)).to(torch.bfloat16))
+    hs = [torch.randn(1, hidden, generator=g).to(torch.bfloat16) for _ in range(6)]
+
+    def expert(e):
+        return make_expert(hidden, ffn, (random_layer(ffn, hidden, 2, 16, 100 + 3 * e), random_layer(hidden, ffn, 2, 16, 101 + 3 * e),
+                                         random_layer(ffn, hidden, 2, 16, 102 + 3 * e)))
+    return hidden, ffn, E, attn, gate, lns, hs, expert
+
+
+def _gpu_decode_rank(rank, world, port, use_peer, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from mixtral_offloading_b200 import (DecoderLayerDecode, ExpertParallelDecoderLayer, PeerExchange, ResidentMoe, _cabi,
+                                         add_rmsnorm)
+    from tests.test_gpu_parity import Cfg as GCfg
+    hidden, ffn, E, attn, gate, lns, hs, expert = _decode_problem(dev)
+    per = E // world
+    mine = [expert(e) for e in range(rank * per, (rank + 1) * per)]
+    exchange = PeerExchange(dist.group.WORLD, hidden, dev) if use_peer else None
+    layer = ExpertParallelDecoderLayer(attn, gate, mine, rank * per, E, lns[2], group=dist.group.WORLD, exchange=exchange)
+    pos = torch.zeros(1, dtype=torch.int32, device=dev)
+    outs = []
+    for h0 in hs:
+        h = h0.clone().to(dev)
+        x = add_rmsnorm(h, None, lns[0], 1e-5)
+        logits = layer(h, x, pos)
+        outs.append((h.cpu(), x.cpu(), logits.cpu()))
+        pos += 1
+    torch.cuda.synchronize(dev)
+    assert _cabi.lib().hqm_device_error() == 0
+    if rank == 0:
+        # the single-GPU layer over all experts, on this rank's GPU, with a fresh cache
+        _, _, _, attn1, gate1, lns1, _, expert1 = _decode_problem(dev)
+        single = DecoderLayerDecode(attn1, ResidentMoe(GCfg(hidden, ffn, E), 0, gate1, [expert1(e) for e in range(E)]), lns1[2])
+        pos.zero_()
+        same = True
+        for h0, (h_ep, x_ep, lg_ep) in zip(hs, outs):
+            h = h0.clone().to(dev)
+            x = add_rmsnorm(h, None, lns1[0], 1e-5)
+            lg = single(h, x, pos)
+            same = same and torch.equal(h.cpu(), h_ep) and torch.equal(x.cpu(), x_ep) and torch.equal(lg.cpu(), lg_ep)
+            pos += 1
+        result.put(bool(same))
+    dist.barrier()
+    torch.cuda.synchronize(dev)
+    os._exit(0)          # (destroying the group after peer mappings / captured collectives has blocked for minutes)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("use_peer", [False, True])
+def test_two_gpu_ranks_decode_layer_equals_one_gpu(use_peer):
+    """ExpertParallelDecoderLayer on two GPUs (NCCL all-reduce, and the peer-memory exchange from inside the
+    kernels) gives bit for bit the residual stream, next input and router logits of the single-GPU layer."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gpu_decode_rank, args=(r, 2, port, use_peer, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+        if p.is_alive():
+            p.kill()
+        assert p.exitcode == 0
+    assert result.get(timeout=5) is True
