@@ -1,7 +1,6 @@
 """Helpers that define orderings the rest of the package relies on."""
 from __future__ import annotations
 
-from contextlib import contextmanager
 
 import torch
 
@@ -19,14 +18,3 @@ def nested_flatten(t):
             yield from nested_flatten(t[key])
     else:
         yield t
-
-
-@contextmanager
-def with_default_dtype(dtype):
-    """src/utils.py:93-101."""
-    saved = torch.get_default_dtype()
-    torch.set_default_dtype(dtype)
-    try:
-        yield
-    finally:
-        torch.set_default_dtype(saved)

@@ -1,6 +1,6 @@
 """Generate the golden fixtures in this directory from the reference's own code.
 
-Run where the reference tree is available (it is not on the GPU box):
+Run where a checkout of the reference is available:
 
     python tests/golden/make_golden.py /path/to/reference
 
