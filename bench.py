@@ -386,7 +386,7 @@ def run_decode(args):
         return float(t.item())
 
     L, H, NH, NKV, HD, E, V = args.layers, HIDDEN, 32, 8, 128, 8, 32000
-    max_len = args.context + args.steps + args.warmup + 8
+    max_len = max(args.context + args.steps + args.warmup + 8, 512 + 256 + 8)
     attn_cfg = BaseQuantizeConfig(nbits=4, group_size=64, quant_zero=True, quant_scale=True)
     torch.manual_seed(rank)
 
@@ -565,6 +565,20 @@ def run_decode(args):
                 torch.cuda.synchronize(dev)
                 us = k0.elapsed_time(k1) / 16 * 1e3
                 expert_us[str(M)] = {"us": us, "hbm_gbs": EXPERT_BYTES / us / 1e3, "tflops": 2.0 * 3 * FFN * H * M / us / 1e6}
+        # BASELINE configs[3]: one decoder layer at 32 and 256 new tokens behind 512 cached positions
+        layer_us = {}
+        if rank == 0 and not args.no_extras and max_len >= 512 + 256:
+            for T in (32, 256):
+                hT = torch.randn(T, H, device=dev).to(torch.bfloat16)
+                layers[0]["fused"].forward_tokens(hT, 512)
+                torch.cuda.synchronize(dev)
+                k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                k0.record(stream)
+                for i in range(4):
+                    layers[i % L]["fused"].forward_tokens(hT, 512)
+                k1.record(stream)
+                torch.cuda.synchronize(dev)
+                layer_us[str(T)] = k0.elapsed_time(k1) / 4 * 1e3
         clocks = sampler.stop() if sampler is not None else None
         # prompt processing through the same model: a 512-token prompt in one pass (informative, rank 0 only)
         prefill_ms = None
@@ -625,6 +639,7 @@ def run_decode(args):
                               "hbm_gbs": 2 * EXPERT_BYTES / moe_us / 1e3, "frac": 2 * EXPERT_BYTES / moe_us / 1e3 / peak,
                               "what": f"hqm_moe_decode over the {L} layers' experts, {moe_reps} blocks in one graph, fastest of 3"},
         "expert_ffn_configs1": expert_us or None,
+        "decoder_layer_configs3_us": ({"1_step_time_over_layers": ms * 1e3 / L, **layer_us} if layer_us else None),
         "offload_configs4a": offload,
         "prefill_512_tokens_ms": prefill_ms,
         "cpu_baseline": cpu,

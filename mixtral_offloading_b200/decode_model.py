@@ -14,7 +14,7 @@ from typing import List, Sequence
 import torch
 from torch import nn
 
-from .decoder import DecoderLayerDecode, add_rmsnorm
+from .decoder import DecoderLayerDecode, add_rmsnorm, rms_norm_rows
 
 
 class MixtralDecodeModel(nn.Module):
@@ -74,58 +74,35 @@ class MixtralDecodeModel(nn.Module):
         self._graph.replay()
         return self._logits
 
-    # ---- prompt processing: all prompt tokens at once --------------------------------------------------
-    def _rms(self, h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        v = h.float()
-        v = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.rms_eps)).to(torch.bfloat16)
-        return w * v
-
-    @staticmethod
-    def _rope(t: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor:
-        """t: (T, heads, head_dim) bf16; rotate-half RoPE with bf16 cos / sin, as the decode kernel applies it."""
-        hd = t.shape[-1]
-        inv = theta ** (-torch.arange(0, hd, 2, dtype=torch.float32, device=t.device) / hd)
-        ang = positions.float()[:, None] * inv[None, :]
-        cos = torch.cat([ang.cos(), ang.cos()], -1).to(torch.bfloat16)[:, None, :]
-        sin = torch.cat([ang.sin(), ang.sin()], -1).to(torch.bfloat16)[:, None, :]
-        rot = torch.cat([-t[..., hd // 2:], t[..., :hd // 2]], -1)
-        return t * cos + rot * sin
+    # ---- several tokens at once ---------------------------------------------------------------------------
+    @torch.inference_mode()
+    def extend(self, token_ids: Sequence[int]) -> torch.Tensor:
+        """Feeds T tokens in one pass behind whatever the caches already hold (positions self.position ..
+        self.position + T - 1): the quantized linears take the many-row tensor-core path, attention over the cache is
+        torch's scaled_dot_product_attention, the MoE block groups the tokens per expert
+        (DecoderLayerDecode.forward_tokens).  Leaves self.position advanced by T and self.token = the greedy next
+        token.  Returns the logits of the last fed position (1, vocab)."""
+        T = len(token_ids)
+        pos0 = int(self.position.item())
+        if T == 0 or pos0 + T >= self.max_len:
+            raise ValueError(f"{T} tokens at position {pos0} do not fit a cache of {self.max_len}")
+        ids = torch.tensor(list(token_ids), dtype=torch.int64, device=self.embed.device)
+        h = self.embed[ids]                                                # (T, hidden)
+        self.router_logits = []
+        for layer in self.layers:
+            h, logits = layer.forward_tokens(h, pos0)
+            self.router_logits.append(logits)
+        x = rms_norm_rows(h[-1:], self.layers[-1].next_ln, self.rms_eps)
+        logits = torch.matmul(x, self.lm_head.t())
+        self.token.copy_(logits.argmax(-1))
+        self.position.fill_(pos0 + T)
+        return logits
 
     @torch.inference_mode()
     def prefill(self, prompt_ids: Sequence[int]) -> torch.Tensor:
-        """Runs the whole prompt through the model in one pass (the quantized linears take the many-row
-        tensor-core path, attention over the prompt is torch's scaled_dot_product_attention, the MoE block
-        groups the tokens per expert), fills the KV caches for positions 0..T-1, leaves self.position = T and
-        self.token = the greedy next token.  Returns the logits of the last prompt position (1, vocab)."""
-        T = len(prompt_ids)
-        if T == 0 or T >= self.max_len:
-            raise ValueError(f"a prompt of {T} tokens does not fit a cache of {self.max_len}")
-        dev = self.embed.device
-        ids = torch.tensor(list(prompt_ids), dtype=torch.int64, device=dev)
-        positions = torch.arange(T, device=dev)
-        h = self.embed[ids]                                                # (T, hidden)
-        hidden = h.shape[-1]
-        for li, layer in enumerate(self.layers):
-            a = layer.attention
-            # the norm in front of a layer is what the decode step applies: first_ln, then each layer's next_ln
-            x = self._rms(h, self.first_ln if li == 0 else self.layers[li - 1].next_ln)
-            q = a.q_proj(x).view(T, a.n_heads, a.head_dim)
-            k = a.k_proj(x).view(T, a.n_kv_heads, a.head_dim)
-            v = a.v_proj(x).view(T, a.n_kv_heads, a.head_dim)
-            q, k = self._rope(q, positions, a.rope_theta), self._rope(k, positions, a.rope_theta)
-            a.k_cache[:, :T] = k.transpose(0, 1)
-            a.v_cache[:, :T] = v.transpose(0, 1)
-            ctx = torch.nn.functional.scaled_dot_product_attention(
-                q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0), v.transpose(0, 1).unsqueeze(0),
-                is_causal=True, enable_gqa=True)                           # (1, heads, T, head_dim)
-            h = h + a.o_proj(ctx[0].transpose(0, 1).reshape(T, hidden))
-            y, _ = layer.moe(self._rms(h, a.ln_post).view(1, T, hidden))
-            h = h + y.view(T, hidden)
-        last_ln = self.layers[-1].next_ln
-        logits = torch.matmul(self._rms(h[-1:], last_ln), self.lm_head.t())
-        self.token.copy_(logits.argmax(-1))
-        self.position.fill_(T)
-        return logits
+        """The whole prompt in one pass on empty caches: extend() from position 0."""
+        self.position.zero_()
+        return self.extend(prompt_ids)
 
     @torch.inference_mode()
     def generate(self, prompt_ids: Sequence[int], new_tokens: int, use_graph: bool = True,

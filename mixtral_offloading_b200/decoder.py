@@ -36,6 +36,25 @@ def add_rmsnorm(h: torch.Tensor, delta, weight: torch.Tensor, eps: float = 1e-5)
     return x
 
 
+def rms_norm_rows(h: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm of every row as the decode kernels compute it: fp32 normalisation, one rounding to bf16, times the
+    bf16 weight (the Hugging Face form)."""
+    v = h.float()
+    v = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).to(torch.bfloat16)
+    return w * v
+
+
+def rope_rows(t: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor:
+    """t: (T, heads, head_dim) bf16; rotate-half RoPE with bf16 cos / sin, as the decode kernel applies it."""
+    hd = t.shape[-1]
+    inv = theta ** (-torch.arange(0, hd, 2, dtype=torch.float32, device=t.device) / hd)
+    ang = positions.float()[:, None] * inv[None, :]
+    cos = torch.cat([ang.cos(), ang.cos()], -1).to(torch.bfloat16)[:, None, :]
+    sin = torch.cat([ang.sin(), ang.sin()], -1).to(torch.bfloat16)[:, None, :]
+    rot = torch.cat([-t[..., hd // 2:], t[..., :hd // 2]], -1)
+    return t * cos + rot * sin
+
+
 class AttentionDecode(nn.Module):
     """Attention half of a decoder layer for one token at a time, with its own KV cache.
 
@@ -126,6 +145,33 @@ class DecoderLayerDecode(nn.Module):
                 w3=f0.w3.descriptor(), next_ln=_bf16_vec(self.next_ln, hidden).data_ptr(),
                 n_experts=self.moe.num_experts, reserved=0)
         return self._layer
+
+    @torch.inference_mode()
+    def forward_tokens(self, h: torch.Tensor, pos0: int):
+        """T new tokens at once (a prompt, or a chunk of 32 / 256 tokens behind a cache that already holds pos0
+        positions): h (T, hidden) bf16 is the residual stream of the tokens at positions pos0 .. pos0 + T - 1.
+        The quantized projections and the experts take their many-row (tensor-core) kernels; norms, RoPE and the
+        attention over the cache are torch ops; the MoE block groups the tokens per expert.  Appends the tokens'
+        keys and values to the cache; returns (updated h, router logits (T, n_experts))."""
+        a = self.attention
+        T, hidden = h.shape
+        if pos0 < 0 or pos0 + T > a.max_len:
+            raise ValueError(f"{T} tokens at position {pos0} do not fit a cache of {a.max_len}")
+        positions = torch.arange(pos0, pos0 + T, device=h.device)
+        x = rms_norm_rows(h, a.ln_in, a.rms_eps)
+        q = rope_rows(a.q_proj(x).view(T, a.n_heads, a.head_dim), positions, a.rope_theta)
+        k = rope_rows(a.k_proj(x).view(T, a.n_kv_heads, a.head_dim), positions, a.rope_theta)
+        v = a.v_proj(x).view(T, a.n_kv_heads, a.head_dim)
+        a.k_cache[:, pos0:pos0 + T] = k.transpose(0, 1)
+        a.v_cache[:, pos0:pos0 + T] = v.transpose(0, 1)
+        keys, vals = a.k_cache[:, :pos0 + T].unsqueeze(0), a.v_cache[:, :pos0 + T].unsqueeze(0)
+        # token i (position pos0 + i) sees positions 0 .. pos0 + i
+        mask = torch.arange(pos0 + T, device=h.device)[None, :] <= positions[:, None]
+        ctx = torch.nn.functional.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), keys, vals, attn_mask=mask,
+                                                               enable_gqa=True)          # (1, heads, T, head_dim)
+        h = h + a.o_proj(ctx[0].transpose(0, 1).reshape(T, hidden))
+        y, logits = self.moe(rms_norm_rows(h, a.ln_post, a.rms_eps).view(1, T, hidden))
+        return h + y.view(T, hidden), logits
 
     @torch.inference_mode()
     def forward(self, h: torch.Tensor, x: torch.Tensor, pos: torch.Tensor):

@@ -54,7 +54,7 @@ def build_layer(seed, next_ln):
     kc = torch.randn(NKV, CONTEXT, HD, generator=g).to(torch.bfloat16)
     vc = torch.randn(NKV, CONTEXT, HD, generator=g).to(torch.bfloat16)
     attn = AttentionDecode(*[layer_from_oracle(od, DEV) for od in attn_ods], ln_in.to(DEV), ln_post.to(DEV), NH, NKV, HD,
-                           CONTEXT + 8, THETA, EPS)
+                           CONTEXT + 264, THETA, EPS)
     attn.k_cache[:, :CONTEXT], attn.v_cache[:, :CONTEXT] = kc.to(DEV), vc.to(DEV)
     dev_sets = [make_expert(H, FFN, ods) for ods in sets]
     gate = torch.nn.Linear(H, E, bias=False, dtype=torch.bfloat16, device=DEV)
@@ -62,7 +62,7 @@ def build_layer(seed, next_ln):
     moe = ResidentMoe(_Cfg, 0, gate, [dev_sets[e % N_DISTINCT] for e in range(E)])
     layer = DecoderLayerDecode(attn, moe, next_ln.to(DEV))
     ref = A.DecoderLayerOracle(attn_ods, ln_in.float(), ln_post.float(), gate_w, [sets[e % N_DISTINCT] for e in range(E)],
-                               NH, NKV, HD, CONTEXT + 8, THETA, EPS, round_to=torch.bfloat16)
+                               NH, NKV, HD, CONTEXT + 264, THETA, EPS, round_to=torch.bfloat16)
     ref.attn.kc[:, :CONTEXT], ref.attn.vc[:, :CONTEXT] = kc.float(), vc.float()
     return layer, ref
 
@@ -144,6 +144,37 @@ def test_blocks_of_the_layer_full_shape(two_layers):
         assert rel(logits, want_logits) < 1e-2, trial
         assert rel(y.view(1, H), want) < 1e-2, trial
     assert _cabi.lib().hqm_device_error() == 0
+
+
+@pytest.mark.parametrize("T", [32, 256])
+def test_decoder_layer_many_tokens_behind_a_filled_cache(two_layers, T):
+    """BASELINE configs[3]: the layer at 32 and 256 new tokens on a cache of 512 positions
+    (DecoderLayerDecode.forward_tokens: tensor-core linears, torch attention over the cache, per-expert MoE)."""
+    lns, built = two_layers
+    layer, ref = built[1]
+    g = torch.Generator().manual_seed(100 + T)
+    h0 = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    h_dev, logits = layer.forward_tokens(h0.to(DEV), CONTEXT)
+    assert _cabi.lib().hqm_device_error() == 0
+    # oracle: the attention half token by token against the cache, then the MoE block for all tokens at once
+    h_mid = torch.empty(T, H)
+    for t in range(T):
+        x = A.rms_norm(h0[t:t + 1].float(), ref.ln_in, EPS, torch.bfloat16)
+        h_mid[t] = A._rnd(h0[t:t + 1].float() + ref.attn.step(x, CONTEXT + t), torch.bfloat16)[0]
+    x_moe = A.rms_norm(h_mid, ref.ln_post, EPS, torch.bfloat16)
+    lg = logits.float().cpu()
+    p = torch.softmax(lg, dim=1, dtype=torch.float32)
+    w, idx = torch.topk(p, 2, dim=-1)
+    moe_out, want_logits = O.moe_forward(x_moe, ref.gate_w, ref.experts, routing=(w / w.sum(-1, keepdim=True), idx))
+    h_ref = A._rnd(h_mid + A._rnd(moe_out, torch.bfloat16), torch.bfloat16)
+    fig = dict(h=rel(h_dev, h_ref), logits=rel(logits, want_logits),
+               k_rows=rel(layer.attention.k_cache[:, CONTEXT:CONTEXT + T], ref.attn.kc[:, CONTEXT:CONTEXT + T]),
+               v_rows=rel(layer.attention.v_cache[:, CONTEXT:CONTEXT + T], ref.attn.vc[:, CONTEXT:CONTEXT + T]))
+    print(f"decoder layer, {T} tokens behind {CONTEXT} cached positions (max rel diff):", {k: round(v, 5) for k, v in fig.items()})
+    # the rotated keys are bf16 values of magnitude 4..8 that went through three bf16 roundings (two products and a
+    # sum): over 256 x 1024 of them one lands two bf16 steps from the oracle's (2 x 2^-5 = 1.03e-2 of max|k|)
+    assert fig["k_rows"] < 1.6e-2 and fig["v_rows"] < 1e-2 and fig["logits"] < 1e-2
+    assert fig["h"] < 1.6e-2
 
 
 def test_two_layers_teacher_forced_logits(two_layers):
