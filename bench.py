@@ -36,6 +36,7 @@ NBITS, GROUP = 2, 16
 POOL = 8                                     # distinct experts rotated through: 8 x 66.4 MB = 531 MB > 126 MB L2
 METRIC = "decode_tokens_per_s_expert_ffn"
 UNIT = "tok/s"
+METRIC_OFFLOAD = "decode_tokens_per_s_offload_4_of_8"
 
 
 def layer_bytes(N, K, nbits=NBITS, group=GROUP):
@@ -579,6 +580,30 @@ def run_decode(args):
                 k1.record(stream)
                 torch.cuda.synchronize(dev)
                 layer_us[str(T)] = k0.elapsed_time(k1) / 4 * 1e3
+        # BASELINE configs[4] at batch 8: eight sequences, one token each per step, every sequence behind its own
+        # cache of `context` positions (BatchDecode over the same layers)
+        batch8 = None
+        if rank == 0 and not args.no_extras:
+            from mixtral_offloading_b200 import BatchDecode
+            B8, steps8 = 8, 6
+            bd = BatchDecode(model, B8, args.context + steps8 + 4)
+            for kc, vc in zip(bd.k_caches, bd.v_caches):
+                kc[:, :, :args.context].normal_(0, 1), vc[:, :, :args.context].normal_(0, 1)
+            toks = torch.randint(0, V, (B8,), device=dev)
+            for i in range(2):
+                toks = bd.step(toks, args.context + i).argmax(-1)
+            torch.cuda.synchronize(dev)
+            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            k0.record(stream)
+            for i in range(2, steps8):
+                toks = bd.step(toks, args.context + i).argmax(-1)
+            k1.record(stream)
+            torch.cuda.synchronize(dev)
+            ms8 = k0.elapsed_time(k1) / (steps8 - 2)
+            batch8 = {"tokens_per_s": B8 * 1e3 / (ms8 * 32.0 / L), "ms_per_step": ms8, "steps": steps8 - 2,
+                      "what": f"8 sequences, one token each per step, context {args.context} each; issued from the host "
+                              "(one read-back of the routing per layer), no graph"}
+            del bd
         clocks = sampler.stop() if sampler is not None else None
         # prompt processing through the same model: a 512-token prompt in one pass (informative, rank 0 only)
         prefill_ms = None
@@ -640,6 +665,7 @@ def run_decode(args):
                               "what": f"hqm_moe_decode over the {L} layers' experts, {moe_reps} blocks in one graph, fastest of 3"},
         "expert_ffn_configs1": expert_us or None,
         "decoder_layer_configs3_us": ({"1_step_time_over_layers": ms * 1e3 / L, **layer_us} if layer_us else None),
+        "decode_batch8_configs4": batch8,
         "offload_configs4a": offload,
         "prefill_512_tokens_ms": prefill_ms,
         "cpu_baseline": cpu,
@@ -964,6 +990,107 @@ def run_offload(args, quiet=False):
     print(json.dumps(line))
 
 
+def run_offload_model(args):
+    """BASELINE configs[4](a): the whole Mixtral-8x7B-shaped decoder (attention as in the decode workload) with
+    offload_per_layer = 4: per layer 4 experts on the device and 4 in pinned host memory, 4 spare slabs, one
+    ExpertCache over all layers, LRU swap, batch 1.  Greedy decode steps through MixtralOffloadModel (the host reads
+    the router's choice once per layer, as the reference does); timed first without, then with speculative expert
+    loading (both guessed experts, then only the likelier one).  The path is bound by the host link: the line
+    reports host->device GB/s against a pinned-copy peak measured in the same run, hit rate, and what the guesses
+    did."""
+    from mixtral_offloading_b200 import (AttentionDecode, BaseQuantizeConfig, ExpertCache, HQQLinearTritonSavable,
+                                         MixtralOffloadModel, SparseMoeWrapper, _cabi)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    L, H, NH, NKV, HD, E, V = args.layers, HIDDEN, 32, 8, 128, 8, 32000
+    per_layer_off = 4
+    max_len = args.context + 2 * (args.steps + args.warmup) + 8
+    attn_cfg = BaseQuantizeConfig(nbits=4, group_size=64, quant_zero=True, quant_scale=True)
+    torch.manual_seed(11)
+
+    class ModelCfg:
+        hidden_size, intermediate_size, num_local_experts, num_experts_per_tok, hidden_act = H, FFN, E, 2, "silu"
+
+    def qlinear(n_out, n_in):
+        lin = torch.nn.Linear(n_in, n_out, bias=False, device=dev, dtype=torch.float32)
+        lin.weight.data.normal_(0, 0.02)
+        return HQQLinearTritonSavable(lin, attn_cfg)
+    state = {"n": 0}
+
+    def make_module():
+        state["n"] += 1
+        return build_pool(dev, 1, seed0=100000 + state["n"], cpu_first=False)[0]
+    cache = ExpertCache(make_module, main_size=L * (E - per_layer_off), offload_size=L * per_layer_off, buffer_size=4)
+    attentions, blocks = [], []
+    for l in range(L):
+        attn = AttentionDecode(qlinear(NH * HD, H), qlinear(NKV * HD, H), qlinear(NKV * HD, H), qlinear(H, NH * HD),
+                               (1 + 0.05 * torch.randn(H, device=dev)).to(torch.bfloat16),
+                               (1 + 0.05 * torch.randn(H, device=dev)).to(torch.bfloat16), NH, NKV, HD, max_len,
+                               rope_theta=1e6, rms_eps=1e-5)
+        attn.k_cache.normal_(0, 1), attn.v_cache.normal_(0, 1)
+        attentions.append(attn)
+        for e, wrapped in enumerate(build_pool(dev, E, seed0=1000 * l, cpu_first=False)):
+            cache.add_expert((l, e), wrapped, eviction_group=l, offload=(e < per_layer_off))
+        gate = torch.nn.Linear(H, E, bias=False, dtype=torch.bfloat16, device=dev)
+        gate.weight.data.normal_(0, 0.02)
+        blocks.append(SparseMoeWrapper(ModelCfg, l, gate, cache))
+    embed = torch.randn(V, H, device=dev).mul_(0.02).to(torch.bfloat16)
+    lm_head = torch.randn(V, H, device=dev).mul_(0.02).to(torch.bfloat16)
+    model = MixtralOffloadModel(embed, attentions, blocks, torch.ones(H, dtype=torch.bfloat16, device=dev), lm_head)
+    peak_h2d = pinned_copy_peak(dev)
+    lib = _cabi.lib()
+    stream = torch.cuda.current_stream(dev)
+    model.position.fill_(args.context)
+    model.token.fill_(1)
+    legs = {}
+    sampler = ClockSampler(0)
+    for name, speculate, width in (("lru_only", False, 2), ("speculative", True, 2), ("speculative_top1", True, 1)):
+        model.set_speculation(speculate, width)
+        for _ in range(args.warmup):
+            model.step()
+        torch.cuda.synchronize(dev)
+        hm0 = [(cache.group_infos[l].hits, cache.group_infos[l].misses) for l in range(L)]
+        bytes0, swaps0 = cache.stats()
+        pf0 = cache.prefetch_stats()
+        launches0 = lib.hqm_launch_count()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for _ in range(args.steps):
+            model.step()
+        ev1.record(stream)
+        torch.cuda.synchronize(dev)
+        ms = ev0.elapsed_time(ev1)
+        bytes1, swaps1 = cache.stats()
+        pf1 = cache.prefetch_stats()
+        hits = sum(cache.group_infos[l].hits - hm0[l][0] for l in range(L))
+        misses = sum(cache.group_infos[l].misses - hm0[l][1] for l in range(L))
+        legs[name] = {
+            "tokens_per_s": args.steps / (ms * 1e-3), "ms_per_token": ms / args.steps,
+            "hit_rate": hits / max(1, hits + misses), "misses_per_token": misses / args.steps,
+            "h2d_gbs": (bytes1 - bytes0) / (ms * 1e-3) / 1e9, "h2d_bytes_per_token": (bytes1 - bytes0) / args.steps,
+            "h2d_frac_of_pinned_peak": (bytes1 - bytes0) / (ms * 1e-3) / 1e9 / peak_h2d,
+            "swaps": swaps1 - swaps0, "gpu_launches": int(lib.hqm_launch_count() - launches0),
+            "prefetch": dict(zip(("issued", "used", "evicted_unused"), (b - a for a, b in zip(pf0, pf1)))),
+        }
+    clocks = sampler.stop()
+    best = max(legs, key=lambda k: legs[k]["tokens_per_s"])
+    print(json.dumps({
+        "metric": METRIC_OFFLOAD, "value": legs[best]["tokens_per_s"], "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": legs[best]["ms_per_token"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"Mixtral-8x7B-shaped decoder, {L} layers, batch 1, context {args.context}: attention 4-bit "
+                   f"g64, experts 2-bit g16, offload_per_layer={per_layer_off} (4 of 8 experts per layer in pinned host "
+                   f"memory), buffer_size=4, LRU swap through ExpertCache; value = the fastest leg ({best})",
+                   "l2": "a token reads ~1.5 GB of resident weights and the swapped slabs, far above L2"},
+        "legs": legs, "pinned_copy_peak_gbs": peak_h2d, "slab_mb": cache.module_size / 1e6,
+        "e2e": {"value": legs[best]["tokens_per_s"], "unit": UNIT,
+                "h2d_bytes_per_step": legs[best]["h2d_bytes_per_token"], "d2h_bytes_per_step": L * (17 + 16) * 4,
+                "note": "the swapped experts cross the host link inside the timed region; the host reads the router's "
+                        "counts (and the guess) back once per layer"},
+        "gpu_launches": legs[best]["gpu_launches"], "clocks": clocks,
+    }))
+
+
 def profile_linear(args):
     """N launches of one quantized linear on HBM-cold weights, nothing else: the small case meant for ncu.
     --layer NxK:nbits:group picks the layer (default: the expert's w1, 14336x4096:2:16); enough distinct
@@ -1156,10 +1283,12 @@ def main():
     ap.add_argument("--layers", type=int, default=None,
                     help="layers built by the decode (default 32) / offload (default 8) workloads")
     ap.add_argument("--context", type=int, default=512, help="KV-cache positions before the first decoded token")
-    ap.add_argument("--workload", default="decode", choices=["decode", "expert", "moe", "offload"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "expert", "moe", "offload", "offload-model"],
                     help="decode: one greedy decode step of the Mixtral-shaped model (the default, BASELINE "
                          "configs[4](b)); expert: one expert FFN per step (configs[1]); moe: one MoE block per step, "
-                         "expert-parallel over the ranks; offload: ExpertCache with half the experts in host memory")
+                         "expert-parallel over the ranks; offload: ExpertCache with half the experts in host memory (MoE blocks only); "
+                         "offload-model: the whole decoder with half of every layer's experts in host memory "
+                         "(configs[4](a)), without and with speculative loading")
     ap.add_argument("--combine", default="all_reduce", choices=["all_reduce", "all_to_all"])
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="expert-parallel decode: how the ranks' shares of a MoE block's output meet (peer: stores into "
@@ -1173,7 +1302,7 @@ def main():
                          "the small case meant to be run under ncu")
     args = ap.parse_args()
     if args.layers is None:
-        args.layers = 32 if args.workload == "decode" else 8
+        args.layers = 32 if args.workload in ("decode", "offload-model") else 8
     if args.impl == "reference":
         args.steps = 3 if args.steps is None else args.steps
         args.warmup = 1 if args.warmup is None else args.warmup
@@ -1191,6 +1320,10 @@ def main():
         args.steps = 50 if args.steps is None else args.steps
         args.warmup = max(3, 5 if args.warmup is None else args.warmup)
         run_offload(args)
+    elif args.workload == "offload-model":
+        args.steps = 24 if args.steps is None else args.steps
+        args.warmup = max(3, 4 if args.warmup is None else args.warmup)
+        run_offload_model(args)
     elif args.workload == "moe":
         args.steps = 200 if args.steps is None else args.steps
         args.warmup = max(3, 8 if args.warmup is None else args.warmup)

@@ -318,6 +318,15 @@ int hqm_cache_begin(hqm_cache* c, const int64_t* uids, int32_t n, int32_t unorde
 int hqm_cache_next(hqm_cache* c, int64_t* uid_out, void** slab_out, int32_t* slot_out, void* compute_stream);
 int hqm_cache_end(hqm_cache* c, void* compute_stream);
 
+/* Speculative loading: the reference lists it as upcoming (README.md:24-27) and has no code for it.  Outside a
+ * request, the offloaded ones among `uids` are brought onto the device as a miss would bring them (the group's
+ * least recently used resident expert leaves; the copy runs on the side stream and is awaited when the expert is
+ * used), without counting hits or misses and without touching experts that are resident already.  *issued_out =
+ * copies started.  hqm_cache_prefetch_stats: copies started, guesses that were then asked for, guesses evicted
+ * unused. */
+int hqm_cache_prefetch(hqm_cache* c, const int64_t* uids, int32_t n, int32_t* issued_out);
+int hqm_cache_prefetch_stats(hqm_cache* c, int64_t* issued, int64_t* used, int64_t* wasted);
+
 /* hits / misses of a group (expert_cache.py:25-26) and copy counters. */
 int hqm_cache_stats(hqm_cache* c, int32_t eviction_group, int64_t* hits, int64_t* misses, int64_t* h2d_bytes,
                     int64_t* swaps);

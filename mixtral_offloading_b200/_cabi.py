@@ -104,6 +104,8 @@ SIGNATURES = {
     "hqm_cache_begin": (C.c_int, [_P, C.POINTER(_I64), _I32, _I32, C.POINTER(_I64), _P]),
     "hqm_cache_next": (C.c_int, [_P, C.POINTER(_I64), C.POINTER(_P), C.POINTER(_I32), _P]),
     "hqm_cache_end": (C.c_int, [_P, _P]),
+    "hqm_cache_prefetch": (C.c_int, [_P, C.POINTER(_I64), _I32, C.POINTER(_I32)]),
+    "hqm_cache_prefetch_stats": (C.c_int, [_P, C.POINTER(_I64), C.POINTER(_I64), C.POINTER(_I64)]),
     "hqm_cache_stats": (C.c_int, [_P, _I32, C.POINTER(_I64), C.POINTER(_I64), C.POINTER(_I64), C.POINTER(_I64)]),
     "hqm_cache_resident": (C.c_int, [_P, _I32, C.POINTER(_I64), _I32]),
 }

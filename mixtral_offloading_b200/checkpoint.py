@@ -16,6 +16,8 @@ to read those.)
   save_checkpoint(dir, ...)      writes such a directory from live modules
   load_expert(dir, ...)          make_and_load_expert_wrapper, build_model.py:137-155
   load_decode_model(dir, ...)    the resident-expert decoder (MixtralDecodeModel) from a directory
+  build_model(device, quant_config, offload_config, dir)
+                                 build_model.py:166-241: the decoder with offloaded experts (MixtralOffloadModel)
 """
 from __future__ import annotations
 
@@ -26,11 +28,13 @@ from typing import Dict, List, Sequence
 import torch
 from safetensors.torch import load_file, save_file
 
-from .build_model import QuantConfig, make_empty_expert
-from .custom_layers import HQQLinearTritonSavable, ResidentMoe
+from .build_model import OffloadConfig, QuantConfig, make_empty_expert
+from .custom_layers import HQQLinearTritonSavable, ResidentMoe, SparseMoeWrapper
 from .decode_model import MixtralDecodeModel
 from .decoder import AttentionDecode, DecoderLayerDecode
+from .expert_cache import ExpertCache
 from .expert_wrapper import MixtralExpertWrapper
+from .offload_model import MixtralOffloadModel
 from .quantize import BaseQuantizeConfig
 
 INDEX = "model.safetensors.index.json"
@@ -127,27 +131,72 @@ def _load_linear(trunk: Dict[str, torch.Tensor], prefix: str, shape, quant) -> H
     return layer
 
 
+def _bf(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.bfloat16).contiguous()
+
+
+def _load_trunk(states_dir: str, device):
+    wm = _weight_map(states_dir)
+    return load_file(os.path.join(states_dir, wm["model.embed_tokens.weight"]), device=str(device))   # build_model.py:194-202
+
+
+def _load_attention(trunk, cfg: ModelConfig, qc: QuantConfig, l: int, max_len: int) -> AttentionDecode:
+    """The layer's four quantized projections (replace_attn_layers, build_model.py:55-120) and its two norms."""
+    H, nh, nkv, hd = cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    base = f"model.layers.{l}"
+    proj = {n: _load_linear(trunk, f"{base}.self_attn.{n}_proj", shape, qc.attn_config)
+            for n, shape in (("q", (H, nh * hd)), ("k", (H, nkv * hd)), ("v", (H, nkv * hd)), ("o", (nh * hd, H)))}
+    return AttentionDecode(proj["q"], proj["k"], proj["v"], proj["o"], _bf(trunk[f"{base}.input_layernorm.weight"]),
+                           _bf(trunk[f"{base}.post_attention_layernorm.weight"]), nh, nkv, hd, max_len,
+                           rope_theta=cfg.rope_theta, rms_eps=cfg.rms_norm_eps)
+
+
+def _load_gate(trunk, cfg: ModelConfig, l: int, device) -> torch.nn.Linear:
+    gate = torch.nn.Linear(cfg.hidden_size, cfg.num_local_experts, bias=False, dtype=torch.bfloat16, device=device)
+    gate.weight.data = _bf(trunk[f"model.layers.{l}.block_sparse_moe.gate.weight"])
+    return gate
+
+
+def build_model(device, quant_config, offload_config: OffloadConfig, state_path: str, max_len: int = 4096,
+                speculate: bool = False) -> MixtralOffloadModel:
+    """build_model.py:166-241: one ExpertCache of offload_config's sizes over all layers, each layer its own eviction
+    group, the first offload_per_layer experts of every layer placed in host memory (:224), SparseMoeWrapper in every
+    layer.  quant_config=None takes the quantisation recorded in the directory.  The slabs' template is expert (0, 0),
+    as in the reference (:157-163, :176-180)."""
+    device = torch.device(device)
+    cfg = load_config(state_path)
+    qc = quant_config if quant_config is not None else cfg.quant_config()
+    trunk = _load_trunk(state_path, device)
+
+    def _make_module():
+        return load_expert(state_path, cfg, qc, (0, 0), device)
+    cache = ExpertCache(make_module=_make_module, main_size=offload_config.main_size,
+                        offload_size=offload_config.offload_size, buffer_size=offload_config.buffer_size)
+    attentions, blocks = [], []
+    for l in range(cfg.num_hidden_layers):
+        attentions.append(_load_attention(trunk, cfg, qc, l, max_len))
+        blocks.append(SparseMoeWrapper(cfg, l, _load_gate(trunk, cfg, l, device), cache))
+        for e in range(cfg.num_local_experts):
+            wrapper = load_expert(state_path, cfg, qc, (l, e), device)
+            cache.add_expert(uid=(l, e), module=wrapper, eviction_group=l, offload=e < offload_config.offload_per_layer)
+            del wrapper
+    return MixtralOffloadModel(_bf(trunk["model.embed_tokens.weight"]), attentions, blocks, _bf(trunk["model.norm.weight"]),
+                               _bf(trunk["lm_head.weight"]), rms_eps=cfg.rms_norm_eps, speculate=speculate)
+
+
 def load_decode_model(states_dir: str, device, max_len: int) -> MixtralDecodeModel:
     """Every expert resident on `device`: the decoder build_model.py:166-241 would assemble around Hugging Face's
     MixtralForCausalLM, as this package's own decode model."""
     cfg = load_config(states_dir)
     qc = cfg.quant_config()
-    wm = _weight_map(states_dir)
-    trunk = load_file(os.path.join(states_dir, wm["model.embed_tokens.weight"]), device=str(device))   # build_model.py:194-202
-    H, nh, nkv, hd = cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
-    bf = lambda t: t.to(torch.bfloat16).contiguous()
+    trunk = _load_trunk(states_dir, device)
+    bf = _bf
     lns_in = [bf(trunk[f"model.layers.{l}.input_layernorm.weight"]) for l in range(cfg.num_hidden_layers)]
     final_norm = bf(trunk["model.norm.weight"])
     layers: List[DecoderLayerDecode] = []
     for l in range(cfg.num_hidden_layers):
-        base = f"model.layers.{l}"
-        proj = {n: _load_linear(trunk, f"{base}.self_attn.{n}_proj", shape, qc.attn_config)
-                for n, shape in (("q", (H, nh * hd)), ("k", (H, nkv * hd)), ("v", (H, nkv * hd)), ("o", (nh * hd, H)))}
-        attn = AttentionDecode(proj["q"], proj["k"], proj["v"], proj["o"], lns_in[l],
-                               bf(trunk[f"{base}.post_attention_layernorm.weight"]), nh, nkv, hd, max_len,
-                               rope_theta=cfg.rope_theta, rms_eps=cfg.rms_norm_eps)
-        gate = torch.nn.Linear(H, cfg.num_local_experts, bias=False, dtype=torch.bfloat16, device=device)
-        gate.weight.data = bf(trunk[f"{base}.block_sparse_moe.gate.weight"])
+        attn = _load_attention(trunk, cfg, qc, l, max_len)
+        gate = _load_gate(trunk, cfg, l, device)
         experts = [load_expert(states_dir, cfg, qc, (l, e), device) for e in range(cfg.num_local_experts)]
         moe = ResidentMoe(cfg, l, gate, experts)
         next_ln = lns_in[l + 1] if l + 1 < cfg.num_hidden_layers else final_norm

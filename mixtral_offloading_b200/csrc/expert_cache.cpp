@@ -42,6 +42,7 @@ struct Expert {
     int32_t index;          // logical main / offload slot, as ExpertInfo.index
     int32_t slab;           // physical device slab holding its bytes, -1 if none
     const void* host;       // pinned host copy
+    bool prefetched = false;   // brought in by hqm_cache_prefetch and not requested since
 };
 
 struct Group {
@@ -72,6 +73,7 @@ struct hqm_cache {
     std::unordered_map<int64_t, Expert> experts;
     std::map<int32_t, Group> groups;
     int64_t h2d_bytes = 0, swaps = 0;
+    int64_t prefetch_issued = 0, prefetch_used = 0, prefetch_wasted = 0;
     // state of the running request
     bool active = false;
     int32_t cur_group = 0;
@@ -153,6 +155,10 @@ int swap_in(hqm_cache* c, Group& g, int64_t uid_in) {
     in.offloaded = false;
     out.offloaded = true;
     out.slab = -1;
+    if (out.prefetched) {                       // a guess that was never asked for leaves again
+        out.prefetched = false;
+        c->prefetch_wasted += 1;
+    }
     g.off_lru.remove(in.uid);
     g.main_lru.push_back(in.uid);               // most recently used
     g.main_lru.erase(victim_it);
@@ -304,7 +310,11 @@ int hqm_cache_begin(hqm_cache* c, const int64_t* uids, int32_t n, int32_t unorde
         if (c->experts.at(u).group != group) return state_error("experts must be in the same evicton group");
     Group& g = c->groups[group];
     for (int64_t u : req) {   // mark_used, expert_cache.py:44-52
-        const Expert& e = c->experts.at(u);
+        Expert& e = c->experts.at(u);
+        if (e.prefetched) {   // the guess was right: what would have been a miss is a hit
+            e.prefetched = false;
+            c->prefetch_used += 1;
+        }
         std::list<int64_t>& l = e.offloaded ? g.off_lru : g.main_lru;
         l.remove(u);
         l.push_back(u);
@@ -411,6 +421,39 @@ int hqm_cache_end(hqm_cache* c, void* compute_stream) {
     c->in_loading.clear();
     c->pos = 0;
     return rc;
+}
+
+// Speculative loading, which the reference lists as not yet implemented (README.md:24-27): outside a request,
+// bring experts that are expected to be asked for soon onto the device, exactly as a miss would (the group's least
+// recently used resident expert leaves, the copy runs on the side stream), but without counting a hit or a miss
+// and without touching the order of experts that are already resident.
+int hqm_cache_prefetch(hqm_cache* c, const int64_t* uids, int32_t n, int32_t* issued_out) {
+    if (!c || (n > 0 && !uids)) return state_error("cache_prefetch: null argument");
+    if (c->active) return state_error("already loading experts; buffers are busy");
+    int32_t issued = 0;
+    for (int32_t i = 0; i < n; ++i) {
+        auto it = c->experts.find(uids[i]);
+        if (it == c->experts.end()) return state_error("cache_prefetch: expert %lld is not registered", (long long)uids[i]);
+        Expert& e = it->second;
+        if (!e.offloaded) continue;
+        Group& g = c->groups[e.group];
+        if (g.main_lru.empty()) continue;
+        const int rc = swap_in(c, g, e.uid);
+        if (rc != HQM_OK) return rc;
+        e.prefetched = true;
+        c->prefetch_issued += 1;
+        ++issued;
+    }
+    if (issued_out) *issued_out = issued;
+    return HQM_OK;
+}
+
+int hqm_cache_prefetch_stats(hqm_cache* c, int64_t* issued, int64_t* used, int64_t* wasted) {
+    if (!c) return state_error("cache_prefetch_stats: null handle");
+    if (issued) *issued = c->prefetch_issued;
+    if (used) *used = c->prefetch_used;
+    if (wasted) *wasted = c->prefetch_wasted;
+    return HQM_OK;
 }
 
 int hqm_cache_stats(hqm_cache* c, int32_t eviction_group, int64_t* hits, int64_t* misses, int64_t* h2d_bytes,

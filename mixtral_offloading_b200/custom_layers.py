@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import copy
 import ctypes as C
-from typing import Any, Dict
+from typing import Any, Dict, Optional
 
 import torch
 from torch import nn
@@ -285,6 +285,14 @@ class SparseMoeWrapper(nn.Module):
         self.gate = gate
         self.experts = expert_cache
         self._host_counts = None
+        # Speculative loading (README.md:24-27 of the reference lists it as upcoming): when set to the next
+        # layer's SparseMoeWrapper, this block also runs that block's router on its own input, reads the guess
+        # back with its own counts, and after its experts have been requested asks the cache to start loading the
+        # guessed experts of the next layer.  At most SPECULATE_MAX_TOKENS rows (with more, every expert is active).
+        self.speculate_next: Optional["SparseMoeWrapper"] = None
+        self.speculate_width = 2          # guessed experts per token that are prefetched: 2, or 1 (the likelier only)
+
+    SPECULATE_MAX_TOKENS = 8
 
     @torch.inference_mode()
     def route(self, x2d):
@@ -314,18 +322,26 @@ class SparseMoeWrapper(nn.Module):
         x2 = _as_bf16_2d(hidden_states, hidden_dim)
         E = self.num_experts
         logits, _, _, meta, token_idx, token_w = self.route(x2)
+        nxt = self.speculate_next if x2.shape[0] <= self.SPECULATE_MAX_TOKENS else None
         if self._host_counts is None:
             with torch.inference_mode(False):     # a normal tensor: it is written from any mode later
-                self._host_counts = torch.empty((2 * E + 1,), dtype=torch.int32).pin_memory()
-        self._host_counts.copy_(meta, non_blocking=True)
+                self._host_counts = torch.empty((2 * E + 1 + 2 * self.SPECULATE_MAX_TOKENS,), dtype=torch.int32).pin_memory()
+        self._host_counts[:2 * E + 1].copy_(meta, non_blocking=True)
+        n_guess = 0
+        if nxt is not None:
+            guess = nxt.route(x2)[2][:, :self.speculate_width].reshape(-1)
+            n_guess = guess.numel()
+            self._host_counts[2 * E + 1:2 * E + 1 + n_guess].copy_(guess, non_blocking=True)
         torch.cuda.current_stream(x2.device).synchronize()
         host = self._host_counts.tolist()
-        counts, offsets = host[:E], host[E:]
+        counts, offsets = host[:E], host[E:2 * E + 1]
         final = torch.zeros((x2.shape[0], hidden_dim), dtype=torch.bfloat16, device=x2.device)
         active = [e for e in range(E) if counts[e] > 0]
         for (_layer, e), expert in self.experts.load_experts(*((self.layer_id, e) for e in active), unordered=True):
             lo, hi = offsets[e], offsets[e + 1]
             expert.forward_routed(x2, token_idx[lo:hi], token_w[lo:hi], final, accumulate=True)
+        if n_guess:     # after this layer's own copies, so that they are first in line on the copy stream
+            self.experts.prefetch(*((nxt.layer_id, e) for e in sorted(set(host[2 * E + 1:2 * E + 1 + n_guess]))))
         final = final.reshape(batch_size, sequence_length, hidden_dim)
         if hidden_states.dtype != torch.bfloat16:
             final, logits = final.to(hidden_states.dtype), logits.to(hidden_states.dtype)

@@ -14,7 +14,7 @@ from typing import List, Sequence
 import torch
 from torch import nn
 
-from .decoder import DecoderLayerDecode, add_rmsnorm, rms_norm_rows
+from .decoder import DecoderLayerDecode, add_rmsnorm, rms_norm_rows, rope_rows
 
 
 class MixtralDecodeModel(nn.Module):
@@ -127,3 +127,49 @@ class MixtralDecodeModel(nn.Module):
             run()
             out.append(int(self.token.item()))
         return out
+
+
+class BatchDecode:
+    """B independent sequences advanced one token per step through the layers of a MixtralDecodeModel (the same
+    weights), each sequence with its own key/value cache; all of them at the same position.
+
+    The quantized projections and the experts run once per step on all B rows (the few-row streaming kernels read
+    the weights once for the batch); norms, RoPE and attention over the caches are torch ops; the MoE block groups the
+    rows per expert (ResidentMoe with several tokens: one read-back of the row counts per layer, so a step is not
+    captured in a graph)."""
+
+    def __init__(self, model: MixtralDecodeModel, batch: int, max_len: int):
+        self.model, self.batch, self.max_len = model, batch, max_len
+        a0 = model.layers[0].attention
+        dev = model.embed.device
+        shape = (batch, a0.n_kv_heads, max_len, a0.head_dim)
+        self.k_caches = [torch.zeros(shape, dtype=torch.bfloat16, device=dev) for _ in model.layers]
+        self.v_caches = [torch.zeros(shape, dtype=torch.bfloat16, device=dev) for _ in model.layers]
+        self.router_logits: List[torch.Tensor] = []
+
+    @torch.inference_mode()
+    def step(self, tokens: torch.Tensor, pos: int) -> torch.Tensor:
+        """tokens: (B,) int64 on the device, the token each sequence is fed at position pos.  Returns the logits
+        (B, vocab); appends the tokens' keys and values to the caches."""
+        m, B = self.model, self.batch
+        if tokens.shape != (B,) or not 0 <= pos < self.max_len:
+            raise ValueError(f"step wants {B} tokens and a position below {self.max_len}")
+        h = m.embed[tokens]                                                # (B, hidden)
+        hidden = h.shape[-1]
+        positions = torch.full((B,), pos, device=h.device)
+        self.router_logits = []
+        for layer, kc, vc in zip(m.layers, self.k_caches, self.v_caches):
+            a = layer.attention
+            x = rms_norm_rows(h, a.ln_in, a.rms_eps)
+            q = rope_rows(a.q_proj(x).view(B, a.n_heads, a.head_dim), positions, a.rope_theta)
+            k = rope_rows(a.k_proj(x).view(B, a.n_kv_heads, a.head_dim), positions, a.rope_theta)
+            kc[:, :, pos] = k
+            vc[:, :, pos] = a.v_proj(x).view(B, a.n_kv_heads, a.head_dim)
+            ctx = torch.nn.functional.scaled_dot_product_attention(q.unsqueeze(2), kc[:, :, :pos + 1], vc[:, :, :pos + 1],
+                                                                   enable_gqa=True)     # (B, heads, 1, head_dim)
+            h = h + a.o_proj(ctx.reshape(B, hidden))
+            y, logits = layer.moe(rms_norm_rows(h, a.ln_post, a.rms_eps).view(1, B, hidden))
+            h = h + y.view(B, hidden)
+            self.router_logits.append(logits)
+        x = rms_norm_rows(h, m.layers[-1].next_ln, m.rms_eps)
+        return torch.matmul(x, m.lm_head.t())

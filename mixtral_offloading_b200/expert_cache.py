@@ -139,6 +139,24 @@ class ExpertCache:
             self.active = False
             lib.hqm_cache_end(self._handle, stream)
 
+    def prefetch(self, *uids: ExpertUID) -> int:
+        """Speculative loading (the reference lists it as upcoming, README.md:24-27): start bringing the offloaded ones
+        among `uids` onto the device now, as a miss would, so that a later load_experts() finds them resident.
+        Only between load_experts() loops.  Returns the number of copies started."""
+        n = len(uids)
+        if n == 0:
+            return 0
+        keys = (C.c_int64 * n)(*[self._keys[u] for u in uids])
+        issued = C.c_int32()
+        _cabi.check(_cabi.lib().hqm_cache_prefetch(self._handle, keys, n, C.byref(issued)))
+        return issued.value
+
+    def prefetch_stats(self):
+        """(copies started by prefetch, guesses that were then requested, guesses evicted unused)."""
+        vals = [C.c_int64() for _ in range(3)]
+        _cabi.check(_cabi.lib().hqm_cache_prefetch_stats(self._handle, *[C.byref(v) for v in vals]))
+        return tuple(v.value for v in vals)
+
     def stats(self):
         """Copy counters of the runtime: (host->device bytes moved by swaps, number of swaps)."""
         vals = [C.c_int64() for _ in range(4)]

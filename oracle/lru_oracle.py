@@ -111,5 +111,17 @@ class LruOracle:
                 raise RuntimeError("internal error: caching algorithm failed")
         return order, swaps, issued
 
+    def prefetch(self, uids):
+        """NOT in the reference (its README.md:24-27 lists speculative loading as upcoming).  Defined here in the
+        reference's own terms so that the product's prefetch can be checked: each offloaded uid is swapped in as
+        expert_cache.py:181-201 would do it for a miss; hits, misses and resident experts' order are untouched.
+        Returns the swaps."""
+        swaps = []
+        for u in uids:
+            group, offloaded, _ = self.where[u]
+            if offloaded and self.lru_main[group]:
+                swaps.append(self._swap(group, u))
+        return swaps
+
     def resident(self, group=0):
         return list(self.lru_main[group].keys())

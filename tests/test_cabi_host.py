@@ -138,6 +138,47 @@ def test_cache_never_hands_out_an_overwritten_slab(lib):
         pol.close()
 
 
+def test_prefetch_bookkeeping_matches_oracle(lib):
+    """Prefetch = the reference's swap applied early: residency follows the oracle, hits and misses only count
+    requests, and the used / wasted counters add up."""
+    import random
+    from oracle.lru_oracle import LruOracle
+    rng = random.Random(5)
+    for buffers in (2, 4):
+        pol, orc = PolicyHandle(lib, 4, 4, buffers), LruOracle(4, 4, buffers)
+        for e in range(8):
+            assert pol.add(e, 0, e >= 4)[0] == 0
+            orc.add(e, 0, e >= 4)
+        issued_total = 0
+        for step in range(300):
+            if rng.random() < 0.6:
+                guess = rng.sample(range(8), rng.choice([1, 2]))
+                arr, issued = (C.c_int64 * len(guess))(*guess), C.c_int32()
+                before = pol.stats(0)[:2]
+                assert lib.hqm_cache_prefetch(pol.h, arr, len(guess), C.byref(issued)) == 0
+                assert issued.value == len(orc.prefetch(guess))
+                assert pol.stats(0)[:2] == before
+                issued_total += issued.value
+            req = rng.sample(range(8), 2)
+            rc, order = pol.load(req, True)
+            want_order, _, _ = orc.load(req, unordered=True)
+            assert rc == 0 and [o[0] for o in order] == want_order
+            assert pol.resident(0) == orc.resident(0)
+            assert pol.stats(0)[:2] == [orc.hits[0], orc.misses[0]]
+        v = [C.c_int64() for _ in range(3)]
+        assert lib.hqm_cache_prefetch_stats(pol.h, *[C.byref(x) for x in v]) == 0
+        n_issued, used, wasted = [x.value for x in v]
+        assert n_issued == issued_total and used > 0 and wasted > 0
+        assert used + wasted <= n_issued <= used + wasted + 4       # at most the resident set is still undecided
+        # not while a request is running
+        rc, order = pol.load([0, 1], True, consume=1)
+        arr = (C.c_int64 * 1)(0)
+        assert lib.hqm_cache_begin(pol.h, arr, 1, 0, None, None) == 0
+        assert lib.hqm_cache_prefetch(pol.h, arr, 1, None) == _cabi.HQM_ERR_STATE
+        lib.hqm_cache_end(pol.h, None)
+        pol.close()
+
+
 def test_cache_errors_match_reference(lib):
     pol = PolicyHandle(lib, 1, 1, 2)
     assert pol.add(0, 0, False)[0] == 0

@@ -106,3 +106,53 @@ def test_saved_model_decodes_like_the_one_it_was_saved_from(tmp_path):
     prompt = [3, 17, 250, 9]
     assert loaded.generate(prompt, 10, use_graph=False) == live.generate(prompt, 10, use_graph=False)
     assert loaded.generate(prompt, 10, use_graph=True) == live.generate(prompt, 10, use_graph=False)
+
+
+@pytest.mark.gpu
+def test_build_model_offloaded_decodes_like_resident_with_and_without_speculation(tmp_path):
+    """build_model (build_model.py:166-241): 3 of 8 experts per layer in host memory, LRU swaps; the logits follow
+    the resident decoder's on the same fed tokens, and speculative loading changes traffic, not results."""
+    from mixtral_offloading_b200 import OffloadConfig
+    from oracle import hqq_oracle as O
+    dev = torch.device("cuda:0")
+    hidden, ffn, n_heads, n_kv, L, E, vocab, max_len = 512, 1792, 4, 2, 3, 8, 300, 48
+    layers, _, embed, lm_head, final_norm = _model_parts(dev, hidden, ffn, n_heads, n_kv, L, E, vocab, seed=9)
+    d = str(tmp_path)
+    ckpt.save_checkpoint(d, _cfg(hidden, ffn, n_heads, n_kv, L, E, vocab), embed, lm_head, final_norm, layers)
+    resident = ckpt.load_decode_model(d, dev, max_len)
+    off = 3
+    oc = OffloadConfig(main_size=L * (E - off), offload_size=L * off, buffer_size=4, offload_per_layer=off)
+    fed = [3, 17, 250, 9, 44, 120, 7, 299, 51, 8, 200, 13]
+
+    def run(model):
+        out = []
+        model.position.zero_()
+        for t in fed:
+            model.token.fill_(t)
+            out.append(model.step().float().cpu())
+        return torch.cat(out)
+    want = run(resident)
+    results = {}
+    for speculate in (False, True):
+        model = ckpt.build_model(dev, None, oc, d, max_len=max_len, speculate=speculate)
+        got = run(model)
+        cache = model.expert_cache
+        hits = sum(cache.group_infos[l].hits for l in range(L))
+        misses = sum(cache.group_infos[l].misses for l in range(L))
+        assert hits + misses == 2 * L * len(fed)
+        assert all(len(cache.group_infos[l].resident) == E - off for l in range(L))
+        results[speculate] = (got, hits, misses, cache.prefetch_stats(), cache.stats())
+        assert O.rel_err(got, want) < 2e-2, O.rel_err(got, want)
+        assert (got.argmax(-1) == want.argmax(-1)).float().mean() > 0.9
+        del model
+    assert torch.equal(results[False][0], results[True][0])
+    assert results[False][3] == (0, 0, 0)
+    issued, used, wasted = results[True][3]
+    assert issued > 0 and used + wasted <= issued
+    print("misses without / with speculation:", results[False][2], results[True][2], "prefetch:", results[True][3])
+    assert _hqm_device_error() == 0
+
+
+def _hqm_device_error():
+    from mixtral_offloading_b200 import _cabi
+    return _cabi.lib().hqm_device_error()

@@ -196,3 +196,35 @@ def test_two_layers_teacher_forced_logits(two_layers):
     err = rel(logits_dev, logits_ref)
     print("teacher-forced final logits max rel diff:", round(err, 5))
     assert err < 2e-2
+
+
+def test_batch_of_eight_sequences_against_the_oracle(two_layers):
+    """BASELINE configs[4] at batch 8: eight sequences, each one token behind its own 512-position cache, through
+    one full-shape layer, the final norm and a 1000 x 4096 head (BatchDecode); every sequence against the oracle."""
+    from mixtral_offloading_b200 import BatchDecode, MixtralDecodeModel
+    B = 8
+    g = torch.Generator().manual_seed(29)
+    lns, built = two_layers
+    layer, ref = built[0]
+    embed = torch.randn(B, H, generator=g).to(torch.bfloat16)                 # row b = the stream of sequence b
+    lm_head = (0.02 * torch.randn(1000, H, generator=g)).to(torch.bfloat16)
+    model = MixtralDecodeModel(embed.to(DEV), [layer], layer.attention.ln_in, lm_head.to(DEV), rms_eps=EPS)
+    batch = BatchDecode(model, B, CONTEXT + 8)
+    prefix_k, prefix_v = ref.attn.kc[:, :CONTEXT].clone(), ref.attn.vc[:, :CONTEXT].clone()
+    for b in range(B):          # sequence b sees the prefix rolled by b positions: eight different histories
+        batch.k_caches[0][b, :, :CONTEXT] = prefix_k.roll(b, 1).to(torch.bfloat16).to(DEV)
+        batch.v_caches[0][b, :, :CONTEXT] = prefix_v.roll(b, 1).to(torch.bfloat16).to(DEV)
+    logits = batch.step(torch.arange(B, device=DEV), CONTEXT).float().cpu()
+    assert _cabi.lib().hqm_device_error() == 0
+    router = batch.router_logits[0].float().cpu()
+    worst = dict(logits=0.0, router=0.0, k=0.0)
+    for b in range(B):
+        ref.attn.kc[:, :CONTEXT], ref.attn.vc[:, :CONTEXT] = prefix_k.roll(b, 1), prefix_v.roll(b, 1)
+        h_ref, parts = ref.step(embed[b:b + 1].float(), CONTEXT, routing=device_routing(router[b:b + 1].to(torch.bfloat16)))
+        want = A.rms_norm(h_ref, lns[0].float(), EPS, torch.bfloat16) @ lm_head.float().t()
+        worst["logits"] = max(worst["logits"], rel(logits[b:b + 1], want))
+        worst["router"] = max(worst["router"], rel(router[b:b + 1], parts["router_logits"]))
+        worst["k"] = max(worst["k"], rel(batch.k_caches[0][b, :, CONTEXT], ref.attn.kc[:, CONTEXT]))
+    ref.attn.kc[:, :CONTEXT], ref.attn.vc[:, :CONTEXT] = prefix_k, prefix_v
+    print("batch of 8, worst sequence:", {k: round(v, 5) for k, v in worst.items()})
+    assert worst["logits"] < 2e-2 and worst["router"] < 1e-2 and worst["k"] < 1e-2
