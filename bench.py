@@ -590,8 +590,9 @@ def run_decode(args):
             for kc, vc in zip(bd.k_caches, bd.v_caches):
                 kc[:, :, :args.context].normal_(0, 1), vc[:, :, :args.context].normal_(0, 1)
             toks = torch.randint(0, V, (B8,), device=dev)
-            for i in range(2):
-                toks = bd.step(toks, args.context + i).argmax(-1)
+            toks = bd.step(toks, args.context).argmax(-1)
+            bd.capture()
+            toks = bd.step(toks, args.context + 1).argmax(-1)
             torch.cuda.synchronize(dev)
             k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             k0.record(stream)
@@ -601,8 +602,8 @@ def run_decode(args):
             torch.cuda.synchronize(dev)
             ms8 = k0.elapsed_time(k1) / (steps8 - 2)
             batch8 = {"tokens_per_s": B8 * 1e3 / (ms8 * 32.0 / L), "ms_per_step": ms8, "steps": steps8 - 2,
-                      "what": f"8 sequences, one token each per step, context {args.context} each; issued from the host "
-                              "(one read-back of the routing per layer), no graph"}
+                      "what": f"8 sequences, one token each per step, context {args.context} each; per layer one recorded "
+                              "segment (attention half + router), one read-back of the routing, the active experts"}
             del bd
         clocks = sampler.stop() if sampler is not None else None
         # prompt processing through the same model: a 512-token prompt in one pass (informative, rank 0 only)

@@ -135,41 +135,145 @@ class BatchDecode:
 
     The quantized projections and the experts run once per step on all B rows (the few-row streaming kernels read
     the weights once for the batch); norms, RoPE and attention over the caches are torch ops; the MoE block groups the
-    rows per expert (ResidentMoe with several tokens: one read-back of the row counts per layer, so a step is not
-    captured in a graph)."""
+    rows per expert as SparseMoeWrapper.forward does (custom_layers.py:272-314), which needs the row counts on the
+    host once per layer.  A step is therefore a chain of segments, one per layer: [add the previous block's output,
+    attention half, post-attention norm, router] - read the counts back - [the active experts].  capture() records
+    every segment in a CUDA graph (the position is device data: the cache row is written by index_copy_ and
+    attention runs over the whole cache under a mask), so that the host issues one replay and the experts per layer."""
 
     def __init__(self, model: MixtralDecodeModel, batch: int, max_len: int):
         self.model, self.batch, self.max_len = model, batch, max_len
         a0 = model.layers[0].attention
         dev = model.embed.device
+        hidden = model.embed.shape[1]
         shape = (batch, a0.n_kv_heads, max_len, a0.head_dim)
         self.k_caches = [torch.zeros(shape, dtype=torch.bfloat16, device=dev) for _ in model.layers]
         self.v_caches = [torch.zeros(shape, dtype=torch.bfloat16, device=dev) for _ in model.layers]
+        self.tokens = torch.zeros((batch,), dtype=torch.int64, device=dev)
+        self.position = torch.zeros((1,), dtype=torch.int64, device=dev)
+        self.h = torch.zeros((batch, hidden), dtype=torch.bfloat16, device=dev)     # residual streams
+        self.y = torch.zeros((batch, hidden), dtype=torch.bfloat16, device=dev)     # the last MoE block's output
+        self._slots = torch.arange(max_len, device=dev)
+        self._inv_freq = a0.rope_theta ** (-torch.arange(0, a0.head_dim, 2, dtype=torch.float32, device=dev) / a0.head_dim)
+        E = model.layers[0].moe.num_experts
+        self._host_counts = torch.empty((2 * E + 1,), dtype=torch.int32).pin_memory()
         self.router_logits: List[torch.Tensor] = []
+        self._graphs = None
+        self._routes = [None] * len(model.layers)
+        self._x_moe = [None] * len(model.layers)
+        self._rope = None
+        self._logits = None
+
+    # ---- segments ---------------------------------------------------------------------------------------------
+    def _prologue(self):
+        """cos / sin of the position (bf16, as the decode kernel applies them) and the mask of filled cache rows."""
+        ang = self.position.float()[:, None] * self._inv_freq[None, :]
+        cos = torch.cat([ang.cos(), ang.cos()], -1).to(torch.bfloat16)[:, None, :]
+        sin = torch.cat([ang.sin(), ang.sin()], -1).to(torch.bfloat16)[:, None, :]
+        self._rope = (cos, sin, (self._slots <= self.position)[None, None, None, :])
+        self.h.copy_(self.model.embed[self.tokens])
+        self.y.zero_()
+
+    @staticmethod
+    def _rotate(t, cos, sin):
+        hd = t.shape[-1]
+        rot = torch.cat([-t[..., hd // 2:], t[..., :hd // 2]], -1)
+        return t * cos + rot * sin
+
+    def _attention_segment(self, l: int):
+        layer = self.model.layers[l]
+        a, B, h = layer.attention, self.batch, self.h
+        hidden = h.shape[-1]
+        cos, sin, mask = self._rope
+        h.add_(self.y)
+        self.y.zero_()
+        x = rms_norm_rows(h, a.ln_in, a.rms_eps)
+        q = self._rotate(a.q_proj(x).view(B, a.n_heads, a.head_dim), cos, sin)
+        k = self._rotate(a.k_proj(x).view(B, a.n_kv_heads, a.head_dim), cos, sin)
+        v = a.v_proj(x).view(B, a.n_kv_heads, a.head_dim)
+        self.k_caches[l].index_copy_(2, self.position, k.unsqueeze(2))
+        self.v_caches[l].index_copy_(2, self.position, v.unsqueeze(2))
+        ctx = torch.nn.functional.scaled_dot_product_attention(q.unsqueeze(2), self.k_caches[l], self.v_caches[l],
+                                                               attn_mask=mask, enable_gqa=True)   # (B, heads, 1, head_dim)
+        h.add_(a.o_proj(ctx.reshape(B, hidden)))
+        self._x_moe[l] = rms_norm_rows(h, a.ln_post, a.rms_eps)
+        self._routes[l] = layer.moe._router.route(self._x_moe[l])
+
+    def _head_segment(self):
+        self.h.add_(self.y)
+        x = rms_norm_rows(self.h, self.model.layers[-1].next_ln, self.model.rms_eps)
+        self._logits = torch.matmul(x, self.model.lm_head.t())
+
+    def _experts(self, l: int):
+        """The per-expert loop of SparseMoeWrapper.forward (custom_layers.py:295-312) into self.y."""
+        moe = self.model.layers[l].moe
+        E = moe.num_experts
+        logits, _, _, meta, token_idx, token_w = self._routes[l]
+        self._host_counts.copy_(meta, non_blocking=True)
+        torch.cuda.current_stream(self.h.device).synchronize()
+        host = self._host_counts.tolist()
+        counts, offsets = host[:E], host[E:]
+        for e in range(E):
+            if counts[e] > 0:
+                lo, hi = offsets[e], offsets[e + 1]
+                moe._experts[e].forward_routed(self._x_moe[l], token_idx[lo:hi], token_w[lo:hi], self.y, accumulate=True)
+        return logits
+
+    # ---- a step -----------------------------------------------------------------------------------------------
+    @torch.inference_mode()
+    def capture(self) -> None:
+        """Records the segments (call after at least one plain step at this batch size, so that the library's
+        workspace has its size)."""
+        dev = self.h.device
+        tokens, pos = self.tokens.clone(), self.position.clone()
+        caches = [(k[:, :, int(pos)].clone(), v[:, :, int(pos)].clone()) for k, v in zip(self.k_caches, self.v_caches)]
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            self._run_eager()                                              # settles allocations on the capture stream
+        torch.cuda.current_stream(dev).wait_stream(side)
+        graphs, pool = [], None
+        segments = [self._prologue] + [lambda l=l: self._attention_segment(l) for l in range(len(self.model.layers))] \
+            + [self._head_segment]
+        for seg in segments:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=pool):
+                seg()
+            pool = g.pool()
+            graphs.append(g)
+        self._graphs = graphs
+        self.tokens.copy_(tokens)
+        self.position.copy_(pos)
+        for (k0, v0), k, v in zip(caches, self.k_caches, self.v_caches):   # the settling step wrote this row
+            k[:, :, int(pos)], v[:, :, int(pos)] = k0, v0
+
+    def _run_eager(self):
+        self._prologue()
+        self.router_logits = []
+        for l in range(len(self.model.layers)):
+            self._attention_segment(l)
+            self.router_logits.append(self._experts(l))
+        self._head_segment()
+
+    def _run_graphs(self):
+        g = self._graphs
+        g[0].replay()
+        self.router_logits = []
+        for l in range(len(self.model.layers)):
+            g[1 + l].replay()
+            self.router_logits.append(self._experts(l))
+        g[-1].replay()
 
     @torch.inference_mode()
     def step(self, tokens: torch.Tensor, pos: int) -> torch.Tensor:
         """tokens: (B,) int64 on the device, the token each sequence is fed at position pos.  Returns the logits
-        (B, vocab); appends the tokens' keys and values to the caches."""
-        m, B = self.model, self.batch
-        if tokens.shape != (B,) or not 0 <= pos < self.max_len:
-            raise ValueError(f"step wants {B} tokens and a position below {self.max_len}")
-        h = m.embed[tokens]                                                # (B, hidden)
-        hidden = h.shape[-1]
-        positions = torch.full((B,), pos, device=h.device)
-        self.router_logits = []
-        for layer, kc, vc in zip(m.layers, self.k_caches, self.v_caches):
-            a = layer.attention
-            x = rms_norm_rows(h, a.ln_in, a.rms_eps)
-            q = rope_rows(a.q_proj(x).view(B, a.n_heads, a.head_dim), positions, a.rope_theta)
-            k = rope_rows(a.k_proj(x).view(B, a.n_kv_heads, a.head_dim), positions, a.rope_theta)
-            kc[:, :, pos] = k
-            vc[:, :, pos] = a.v_proj(x).view(B, a.n_kv_heads, a.head_dim)
-            ctx = torch.nn.functional.scaled_dot_product_attention(q.unsqueeze(2), kc[:, :, :pos + 1], vc[:, :, :pos + 1],
-                                                                   enable_gqa=True)     # (B, heads, 1, head_dim)
-            h = h + a.o_proj(ctx.reshape(B, hidden))
-            y, logits = layer.moe(rms_norm_rows(h, a.ln_post, a.rms_eps).view(1, B, hidden))
-            h = h + y.view(B, hidden)
-            self.router_logits.append(logits)
-        x = rms_norm_rows(h, m.layers[-1].next_ln, m.rms_eps)
-        return torch.matmul(x, m.lm_head.t())
+        (B, vocab) (a buffer that the next step overwrites); appends the tokens' keys and values to the caches."""
+        if tokens.shape != (self.batch,) or not 0 <= pos < self.max_len:
+            raise ValueError(f"step wants {self.batch} tokens and a position below {self.max_len}")
+        self.tokens.copy_(tokens)
+        self.position.fill_(pos)
+        if self._graphs is not None:
+            self._run_graphs()
+        else:
+            self._run_eager()
+        return self._logits

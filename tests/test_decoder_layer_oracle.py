@@ -217,6 +217,11 @@ def test_batch_of_eight_sequences_against_the_oracle(two_layers):
     logits = batch.step(torch.arange(B, device=DEV), CONTEXT).float().cpu()
     assert _cabi.lib().hqm_device_error() == 0
     router = batch.router_logits[0].float().cpu()
+    k_row = batch.k_caches[0][:, :, CONTEXT].clone()
+    batch.capture()                                  # the same step from recorded segments: identical results
+    batch.k_caches[0][:, :, CONTEXT] = 0
+    again = batch.step(torch.arange(B, device=DEV), CONTEXT).float().cpu()
+    assert torch.equal(again, logits) and torch.equal(batch.k_caches[0][:, :, CONTEXT], k_row)
     worst = dict(logits=0.0, router=0.0, k=0.0)
     for b in range(B):
         ref.attn.kc[:, :CONTEXT], ref.attn.vc[:, :CONTEXT] = prefix_k.roll(b, 1), prefix_v.roll(b, 1)
