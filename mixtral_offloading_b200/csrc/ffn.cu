@@ -45,6 +45,7 @@ static bool same_format(const hqm_weight* a, const hqm_weight* b) {
 struct TcPlan {
     int G1, C1, G2, C2;
     size_t up_bytes, h_bytes, down_bytes;
+    size_t gather_bytes;      // the routed rows of x made contiguous (the TMA-staged GEMM copies x by tiles)
 };
 static bool tc_plan(int64_t M, const hqm_weight* w1, const hqm_weight* w2, const hqm_weight* w3, const void* x,
                     TcPlan* tp) {
@@ -59,6 +60,7 @@ static bool tc_plan(int64_t M, const hqm_weight* w1, const hqm_weight* w2, const
     tp->up_bytes = align_up((size_t)M * 2 * w1->N * sizeof(float), 256);
     tp->h_bytes = align_up((size_t)M * w1->N * 2, 256);
     tp->down_bytes = align_up((size_t)M * w2->N * sizeof(float), 256);
+    tp->gather_bytes = gemm_tma_supported(w1, tp->G1, tp->C1, M) ? align_up((size_t)M * w1->K * 2, 256) : 0;
     return true;
 }
 
@@ -92,7 +94,7 @@ size_t hqm_expert_ffn_scratch_bytes(int64_t M, const hqm_weight* w1, const hqm_w
     if (!w1 || !w2 || !w3 || M <= 0) return 0;
     const size_t H = hqm::SCRATCH_HEADER;
     hqm::TcPlan tp;
-    if (hqm::tc_plan(M, w1, w2, w3, nullptr, &tp)) return H + tp.up_bytes + tp.h_bytes + tp.down_bytes;
+    if (hqm::tc_plan(M, w1, w2, w3, nullptr, &tp)) return H + tp.up_bytes + tp.h_bytes + tp.down_bytes + tp.gather_bytes;
     hqm::FusedPlan fp;
     if (hqm::fused_plan(M, w1, w2, w3, nullptr, &fp)) return H + fp.up_bytes + fp.h_bytes + fp.down_bytes;
     const size_t a = hqm::align_up((size_t)M * (size_t)w1->N * 2, 256);
@@ -130,7 +132,15 @@ int hqm_expert_ffn(uint16_t* out, const uint16_t* x, int64_t M, const int32_t* t
         float* up = (float*)p;
         uint16_t* h = (uint16_t*)(p + tp.up_bytes);
         float* down = (float*)(p + tp.up_bytes + tp.h_bytes);
-        int rc = launch_gemm_tc(up, x, token_idx, M, w1, w3, tp.G1, tp.C1, st);
+        int rc;
+        if (token_idx && tp.gather_bytes) {
+            uint16_t* xg = (uint16_t*)(p + tp.up_bytes + tp.h_bytes + tp.down_bytes);
+            rc = launch_gather_rows(xg, x, token_idx, M, w1->K, st);
+            if (rc != HQM_OK) return rc;
+            rc = launch_gemm_tc(up, xg, nullptr, M, w1, w3, tp.G1, tp.C1, st);
+        } else {
+            rc = launch_gemm_tc(up, x, token_idx, M, w1, w3, tp.G1, tp.C1, st);
+        }
         if (rc != HQM_OK) return rc;
         rc = launch_silu_mul_from_sums(h, up, M, F, st);
         if (rc != HQM_OK) return rc;

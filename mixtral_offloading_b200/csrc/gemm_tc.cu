@@ -402,6 +402,7 @@ static int launch_tc_tokens(const tc::Params& p, int grid, int ntok, cudaStream_
 // sums (M, layers*N) fp32 = x . [w0; w1]^T.  With split K the caller-provided sums are zeroed here first.
 int launch_gemm_tc(float* sums, const uint16_t* x, const int32_t* x_idx, int64_t M, const hqm_weight* w0,
                    const hqm_weight* w1, int G, int C, cudaStream_t st) {
+    if (!x_idx && gemm_tma_supported(w0, G, C, M)) return launch_gemm_tma(sums, x, M, w0, w1, G, C, st);
     const int layers = w1 ? 2 : 1;
     const int per = codes_per_word(w0->nbits);
     const int nb = w0->group_size / 16;

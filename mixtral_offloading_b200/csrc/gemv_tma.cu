@@ -755,6 +755,9 @@ bool prepare_kernel(size_t smem) {
 
 }  // namespace
 
+// cuTensorMapEncodeTiled of the installed driver (null when it cannot be had), for the other TMA users.
+void* tma_encode_entry() { return (void*)encode_fn(); }
+
 // Plans one TMA-staged launch over up to four layers for ONE row of x; false when the shapes are outside it
 // (the caller then falls back to gemv_stream.cu's kernel).
 size_t gemv_tma_scratch_bytes(const StreamPlan& plan, int64_t M) {

@@ -103,6 +103,12 @@ int launch_silu_mul_from_sums(uint16_t* h, const float* sums, int64_t M, int F, 
 int launch_scatter_from_sums(uint16_t* out, const float* sums, const int32_t* token_idx, const float* route_w,
                              int accumulate, int64_t M, int H, cudaStream_t st);
 int* tc_error_ptr();                  // device flag the bounded waits set when they give up
+// gemm_tma.cu — the same GEMM with every operand staged by TMA, persistent stream-K CTAs (contiguous rows of x).
+void* tma_encode_entry();
+bool gemm_tma_supported(const hqm_weight* w, int G, int C, int64_t M);
+int launch_gemm_tma(float* sums, const uint16_t* x, int64_t M, const hqm_weight* w0, const hqm_weight* w1, int G, int C,
+                    cudaStream_t st);
+int launch_gather_rows(uint16_t* dst, const uint16_t* x, const int32_t* idx, int64_t M, int K, cudaStream_t st);
 constexpr int64_t TC_MIN_ROWS = 17;   // fewer rows go to the streaming kernels
 
 // gemm_tc3.cu — the same for 3-bit layers (row counts >= 5).

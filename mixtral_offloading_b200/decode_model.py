@@ -89,9 +89,11 @@ class MixtralDecodeModel(nn.Module):
         ids = torch.tensor(list(token_ids), dtype=torch.int64, device=self.embed.device)
         h = self.embed[ids]                                                # (T, hidden)
         self.router_logits = []
+        ln_in = self.first_ln                       # the norm weights step() applies: first_ln, then each layer's next_ln
         for layer in self.layers:
-            h, logits = layer.forward_tokens(h, pos0)
+            h, logits = layer.forward_tokens(h, pos0, ln_in)
             self.router_logits.append(logits)
+            ln_in = layer.next_ln
         x = rms_norm_rows(h[-1:], self.layers[-1].next_ln, self.rms_eps)
         logits = torch.matmul(x, self.lm_head.t())
         self.token.copy_(logits.argmax(-1))
@@ -187,7 +189,8 @@ class BatchDecode:
         cos, sin, mask = self._rope
         h.add_(self.y)
         self.y.zero_()
-        x = rms_norm_rows(h, a.ln_in, a.rms_eps)
+        ln_in = self.model.first_ln if l == 0 else self.model.layers[l - 1].next_ln     # the weights step() applies
+        x = rms_norm_rows(h, ln_in, a.rms_eps)
         q = self._rotate(a.q_proj(x).view(B, a.n_heads, a.head_dim), cos, sin)
         k = self._rotate(a.k_proj(x).view(B, a.n_kv_heads, a.head_dim), cos, sin)
         v = a.v_proj(x).view(B, a.n_kv_heads, a.head_dim)

@@ -147,18 +147,21 @@ class DecoderLayerDecode(nn.Module):
         return self._layer
 
     @torch.inference_mode()
-    def forward_tokens(self, h: torch.Tensor, pos0: int):
+    def forward_tokens(self, h: torch.Tensor, pos0: int, ln_in=None):
         """T new tokens at once (a prompt, or a chunk of 32 / 256 tokens behind a cache that already holds pos0
         positions): h (T, hidden) bf16 is the residual stream of the tokens at positions pos0 .. pos0 + T - 1.
         The quantized projections and the experts take their many-row (tensor-core) kernels; norms, RoPE and the
         attention over the cache are torch ops; the MoE block groups the tokens per expert.  Appends the tokens'
-        keys and values to the cache; returns (updated h, router logits (T, n_experts))."""
+        keys and values to the cache; returns (updated h, router logits (T, n_experts)).  ln_in: the layer's input
+        norm weight when it is not attention.ln_in (a model hands every layer the weight its predecessor was built
+        with as next_ln, which is what the one-token path applies)."""
         a = self.attention
+        ln_in = a.ln_in if ln_in is None else ln_in
         T, hidden = h.shape
         if pos0 < 0 or pos0 + T > a.max_len:
             raise ValueError(f"{T} tokens at position {pos0} do not fit a cache of {a.max_len}")
         positions = torch.arange(pos0, pos0 + T, device=h.device)
-        x = rms_norm_rows(h, a.ln_in, a.rms_eps)
+        x = rms_norm_rows(h, ln_in, a.rms_eps)
         q = rope_rows(a.q_proj(x).view(T, a.n_heads, a.head_dim), positions, a.rope_theta)
         k = rope_rows(a.k_proj(x).view(T, a.n_kv_heads, a.head_dim), positions, a.rope_theta)
         v = a.v_proj(x).view(T, a.n_kv_heads, a.head_dim)

@@ -546,3 +546,28 @@ def test_state_dict_round_trip_of_layer_and_expert_slab():
     fresh.load_state_dict(sd1)
     assert np.array_equal(fresh.W_q.cpu().numpy(), od["W_q"])
     assert torch.equal(fresh(x), lay(x))
+
+
+def test_many_row_gemm_without_tma_staging():
+    """HQM_GEMM_TMA=0 at load time keeps the many-row GEMM on its first-generation kernel (operand tiles filled by
+    the producer threads): same oracle, same bound; run in a process of its own because the switch is read once."""
+    import subprocess
+    import sys
+    code = (
+        "import torch\n"
+        "from oracle import hqq_oracle as O\n"
+        "from tests.helpers import layer_from_oracle, random_layer\n"
+        "from mixtral_offloading_b200 import _cabi\n"
+        "dev = torch.device('cuda:0')\n"
+        "for nbits, group, N, K, M in ((2, 16, 1792, 1024, 40), (4, 64, 1024, 2048, 300)):\n"
+        "    od = random_layer(N, K, nbits, group, seed=3)\n"
+        "    x = torch.randn(M, K, generator=torch.Generator().manual_seed(M)).to(torch.bfloat16)\n"
+        "    y = layer_from_oracle(od, dev)(x.to(dev)).cpu()\n"
+        "    err = O.rel_err(y, O.linear(x, od))\n"
+        "    assert err < 1e-2, err\n"
+        "assert _cabi.lib().hqm_device_error() == 0\n"
+        "print('ok')\n")
+    env = dict(os.environ, HQM_GEMM_TMA="0")
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=600,
+                         cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert res.returncode == 0 and res.stdout.strip().endswith("ok"), res.stdout + res.stderr
