@@ -105,6 +105,24 @@ struct Cfg {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// Bounded wait for the roles that can afford a late wake-up: sleeps after every look, so that the waiting warps
+// leave the issue slots of their scheduler to the warps that have work (the MMA-issuing lane above all).
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        __nanosleep(i < 16 ? 32 : 128);
+    }
+    return false;
+}
 // Tiled copies global -> shared memory of this CTA, completion counted in bytes on `bar`.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -289,9 +307,9 @@ gemm_tma_kernel(const __grid_constant__ Params prm) {
             }
             cur.advance(PGROUPS, work, prm);
             bool bad = *failed != 0;
-            if (!bad && !mbar_wait(raw_full + r, (it / N_RAW) & 1)) bad = true;
+            if (!bad && !mbar_wait_relaxed(raw_full + r, (it / N_RAW) & 1)) bad = true;
             // the A slot's previous tile (unit it - N_A) has been read by its MMAs
-            if (!bad && it >= N_A && !mbar_wait(done + (it - N_A) % N_B, ((it - N_A) / N_B) & 1)) bad = true;
+            if (!bad && it >= N_A && !mbar_wait_relaxed(done + (it - N_A) % N_B, ((it - N_A) / N_B) & 1)) bad = true;
             bad = group_any(bar_id, bad);                                    // the whole group takes the same decision
             if (bad) {
                 *failed = 1;
@@ -373,8 +391,8 @@ gemm_tma_kernel(const __grid_constant__ Params prm) {
             const int r = it % N_RAW, b = it % N_B;
             int ok = 1;
             if (lane == 0) {
-                if (it >= N_RAW && !mbar_wait(raw_empty + r, ((it / N_RAW) - 1) & 1)) *failed = 1;
-                if (!*failed && it >= N_B && !mbar_wait(done + b, ((it / N_B) - 1) & 1)) *failed = 1;
+                if (it >= N_RAW && !mbar_wait_relaxed(raw_empty + r, ((it / N_RAW) - 1) & 1)) *failed = 1;
+                if (!*failed && it >= N_B && !mbar_wait_relaxed(done + b, ((it / N_B) - 1) & 1)) *failed = 1;
                 ok = *failed ? 0 : 1;
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -459,7 +477,7 @@ gemm_tma_kernel(const __grid_constant__ Params prm) {
         int seg = 0;
         while (cur.it < n_units) {
             const int buf = seg & 1;
-            bool ok = !*failed && mbar_wait(acc_full + buf, (seg >> 1) & 1);
+            bool ok = !*failed && mbar_wait_relaxed(acc_full + buf, (seg >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);                       // tcgen05.ld below is warp-collective
             if (!ok) {
                 *failed = 1;
