@@ -122,7 +122,11 @@ size_t hqm_linear_scratch_bytes(int64_t M, const hqm_weight* w);
  * kernels of triton_kernels.py:37-191 (4-bit), :225-380 (2-bit), :414-564 (3-bit)
  * and the per-call 8-bit scale/zero decode fused in:
  *   y[M, N] = x[M, K] . W_est^T (+ bias[N]),  fp32 accumulation, bf16 in/out.
- * bias may be NULL.  scratch may be NULL when hqm_linear_scratch_bytes() is 0. */
+ * bias may be NULL.  scratch may be NULL when hqm_linear_scratch_bytes() is 0.
+ * Rows 1..16 take the weight-streaming kernels, 17 and more (5 and more for 3-bit layers) the tcgen05 kernels;
+ * HQM_GEMM_TMA=0 in the environment at load time keeps the 2- and 4-bit many-row path on its first-generation
+ * kernel (operand tiles filled by threads instead of TMA), HQM_FORCE_GENERIC=1 routes everything through the
+ * shape-agnostic kernel. */
 int hqm_linear(uint16_t* y, const uint16_t* x, int64_t M, const hqm_weight* w, const uint16_t* bias,
                void* scratch, size_t scratch_bytes, void* stream);
 
