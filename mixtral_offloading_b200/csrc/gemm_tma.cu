@@ -420,12 +420,20 @@ gemm_tma_kernel(const __grid_constant__ Params prm) {
             // instruction descriptor: D fp32, A / B bf16, both K-major, N = NTOK, M = 128
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NTOK >> 3) << 17) |
                                    ((uint32_t)(TILE_ROWS >> 4) << 24);
+            // This lane's instruction stream is the floor of the whole pipeline (a unit's four MMAs take 128 to 512
+            // tensor cycles), so everything per unit is kept incremental: slot indices, phases and the descriptors'
+            // address fields advance by constants, the tile boundaries come from a countdown.
             Cursor<RT> cur;
             cur.locate(0, work, prm);
+            int left = cur.seg_end - cur.seg_begin;                  // units of the current tile still to issue
+            bool first = true;
             int seg = 0;
+            constexpr uint64_t DESC_HI = (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+            const uint32_t a_enc0 = (smem_u32(a_ring) & 0x3FFFFu) >> 4, b_enc0 = (smem_u32(b_ring) & 0x3FFFFu) >> 4;
+            uint32_t a_enc = a_enc0, b_enc = b_enc0;                 // start-address fields of the slots in use
+            int a = 0, b = 0;
+            uint32_t a_par = 0, b_par = 0;
             for (int it = 0; it < n_units; ++it) {
-                const int a = it % N_A, b = it % N_B;
-                const bool first = it == cur.seg_begin, last = it == cur.seg_end - 1;
                 const int buf = seg & 1;
                 if (first && seg >= 2) {            // the epilogue has drained this accumulator
                     if (!mbar_wait(acc_empty + buf, ((seg >> 1) - 1) & 1)) {
@@ -434,28 +442,39 @@ gemm_tma_kernel(const __grid_constant__ Params prm) {
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 }
-                if (*failed) break;
-                if (!mbar_wait(b_full + b, (it / N_B) & 1)) {
-                    *failed = 1;
-                    break;
-                }
-                if (!mbar_wait(a_full + a, (it / N_A) & 1)) {
+                if (!mbar_wait(b_full + b, b_par) || !mbar_wait(a_full + a, a_par)) {
                     *failed = 1;
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t da = smem_desc_sw128(smem_u32(a_ring + (size_t)a * CF::A_BYTES));
-                const uint64_t db = smem_desc_sw128(smem_u32(b_ring + (size_t)b * CF::B_BYTES));
+                const uint64_t da = DESC_HI | a_enc, db = DESC_HI | b_enc;
                 const uint32_t d = tmem_d + (uint32_t)(buf * NTOK);
 #pragma unroll
                 for (int k = 0; k < BK / 16; ++k)   // +32 bytes (2 descriptor units) per K = 16 step
                     umma_bf16(d, da + 2 * k, db + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
                 umma_commit(done + b);              // the A and B slots are free once these MMAs have read them
-                if (last) {
+                first = false;
+                if (--left == 0) {                  // the tile's (or this CTA's share of its) k-blocks are issued
                     umma_commit(acc_full + buf);
                     ++seg;
+                    cur.locate(cur.seg_end, work, prm);
+                    left = cur.seg_end - cur.seg_begin;
+                    first = true;
                 }
-                cur.advance(1, work, prm);
+                if (++a == N_A) {
+                    a = 0;
+                    a_par ^= 1u;
+                    a_enc = a_enc0;
+                } else {
+                    a_enc += CF::A_BYTES >> 4;
+                }
+                if (++b == N_B) {
+                    b = 0;
+                    b_par ^= 1u;
+                    b_enc = b_enc0;
+                } else {
+                    b_enc += CF::B_BYTES >> 4;
+                }
             }
         }
         __syncwarp();
