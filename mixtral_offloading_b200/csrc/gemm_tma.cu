@@ -8,11 +8,11 @@
 //
 // A unit of work is one 64-column k-block of one tile (128 output rows x one chunk of NTOK tokens).  Three rings
 // of shared-memory buffers decouple what has different sizes and latencies:
-//   raw ring (2 PG deep, 3-5 KB)  the packed codes of the tile's storage rows and its scale and zero bytes, as
+//   raw ring (3-4 PG deep, 3-5 KB)  the packed codes of the tile's storage rows and its scale and zero bytes, as
 //                               they lie in HBM
-//   B ring (PG or 2 PG deep)    the x tile (NTOK rows x 64 bf16, 128-byte swizzle): it IS the MMA's B operand
+//   B ring (PG to 3 PG deep)     the x tile (NTOK rows x 64 bf16, 128-byte swizzle): it IS the MMA's B operand
 //   A ring (PG deep, 16 KB)     the dequantised weights, K-major, 128-byte swizzle, plus the decoded scales
-// Roles of the warps of a CTA (one CTA per SM, persistent; PG = 4 producer groups, 3 with 256-token tiles):
+// Roles of the warps of a CTA (one CTA per SM, persistent; PG = 4 producer groups, 3 with 128- and 256-token tiles):
 //   producers    PG groups of 128 threads; group g takes the units g, g+PG, ...: decodes scale / zero (8 bit -> s
 //                and -z*s as bf16; the fp16 meta values are the only thing read with plain loads, requested
 //                before the group waits for its buffers), dequantises 128 x 64 weights into an A slot (one LOP3,
@@ -72,7 +72,7 @@ struct Cfg {
     static constexpr int RES = RT * PER;
     // PG producer groups of 128 threads, PG warps that issue the copies, the MMA warp, 4 epilogue warps (four
     // consecutive warps: each TMEM lane quarter once)
-    static constexpr int PG = NTOK > 128 ? 3 : 4;
+    static constexpr int PG = NTOK >= 128 ? 3 : 4;
     static constexpr int WARP_ISSUE = 4 * PG, WARP_MMA = 5 * PG, WARP_EPI = 5 * PG + 1;
     static constexpr int NTHREADS = (WARP_EPI + 4) * 32;
     // Ring depths.  A wait by phase parity is only sound while the waiter is at most one phase behind the
@@ -80,7 +80,7 @@ struct Cfg {
     // the slot's previous release itself.  A slots rotate over the groups, and their release is read off the
     // per-unit `done` barriers (N_B of them, a multiple of N_A): group g's previous unit is PG back, which proves
     // that the unit PG + N_A back has been consumed; N_B >= PG makes that cover the barrier's previous phase.
-    static constexpr int N_A = PG, N_RAW = 2 * PG;
+    static constexpr int N_A = PG, N_RAW = (NTOK > 128 ? 3 : 4) * PG;
     static constexpr int B_BYTES = NTOK * 128;
     static constexpr int W_BYTES = GS * RT * BK;              // staged packed bytes: [member][residue][64]
     static constexpr int Q_BYTES = RES * BK;                  // staged scale (and zero) bytes: [row][64]
@@ -92,13 +92,13 @@ struct Cfg {
     // A slot: the tile, then s and -z*s
     static constexpr int S_OFF = TILE_ROWS * 128, T_OFF = S_OFF + D_BYTES;
     static constexpr int A_BYTES = (T_OFF + D_BYTES + 1023) / 1024 * 1024;
-    static constexpr int FIXED = 1024 /*alignment slack*/ + 512 /*barriers*/ + EPI_BYTES + N_RAW * RAW_BYTES + N_A * A_BYTES;
+    static constexpr int FIXED = 1024 /*alignment slack*/ + 1024 /*barriers*/ + EPI_BYTES + N_RAW * RAW_BYTES + N_A * A_BYTES;
     static constexpr int NB_FIT = (SMEM_LIMIT - FIXED) / B_BYTES;
-    static constexpr int N_B = (NB_FIT >= 2 * PG ? 2 : 1) * PG;
+    static constexpr int N_B = (NB_FIT >= 3 * PG ? 3 : (NB_FIT >= 2 * PG ? 2 : 1)) * PG;
     static_assert(NB_FIT >= PG, "B ring does not fit");
     static constexpr int B_OFF = 0, A_OFF = N_B * B_BYTES, RAW_OFF = A_OFF + N_A * A_BYTES, EPI_OFF = RAW_OFF + N_RAW * RAW_BYTES,
                          BAR_OFF = EPI_OFF + EPI_BYTES;
-    static constexpr size_t SMEM = (size_t)BAR_OFF + 512 + 1024;
+    static constexpr size_t SMEM = (size_t)BAR_OFF + 1024 + 1024;
     static constexpr uint32_t TMEM_COLS = 2 * NTOK;           // 128 / 256 / 512: a power of two >= 32
 };
 
@@ -239,7 +239,7 @@ gemm_tma_kernel(const __grid_constant__ Params prm) {
     uint64_t* acc_empty = acc_full + 2;            // [2] epilogue -> MMA
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    static_assert((2 * N_RAW + N_A + 2 * N_B + 4) * 8 + 8 <= 512 && N_B % N_A == 0, "barrier area");
+    static_assert((2 * N_RAW + N_A + 2 * N_B + 4) * 8 + 8 <= 1024 && N_B % N_A == 0, "barrier area");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const Work work = work_of(prm);
