@@ -784,17 +784,34 @@ def run_decode_ep(args):
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if int(ok.item()) == 0:
         exchange = None
-    layers = [ExpertParallelDecoderLayer(b["attn"], b["gate"], b["pool"], lo, E, built[i + 1]["ln1"] if i + 1 < L else ln_f,
-                                         group=dist.group.WORLD, exchange=exchange) for i, b in enumerate(built)]
-    model = MixtralDecodeModel(embed, layers, built[0]["ln1"], lm_head)
-    tok, pos32 = model.token, model.position
     lib = __import__("mixtral_offloading_b200")._cabi.lib()
     stream = torch.cuda.current_stream(dev)
+
+    def assemble(exch):
+        lys = [ExpertParallelDecoderLayer(b["attn"], b["gate"], b["pool"], lo, E, built[i + 1]["ln1"] if i + 1 < L else ln_f,
+                                          group=dist.group.WORLD, exchange=exch) for i, b in enumerate(built)]
+        return MixtralDecodeModel(embed, lys, built[0]["ln1"], lm_head)
+    model = assemble(exchange)
     with torch.inference_mode():
-        pos32.fill_(args.context)
+        model.position.fill_(args.context)
         for _ in range(3):
             model.step()                                                 # NCCL connections, scratch sizes
         barrier()
+        if exchange is not None:
+            # a peer's flag that never came (a bounded wait ran out on some rank): every rank switches to the all-reduce
+            bad = torch.tensor([1 if lib.hqm_device_error() != 0 else 0], device=dev)
+            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+            if int(bad.item()) != 0:
+                if rank == 0:
+                    print("peer-memory exchange timed out during warm-up; using NCCL", file=sys.stderr)
+                exchange = None
+                model = assemble(None)
+                model.position.fill_(args.context)
+                for _ in range(3):
+                    model.step()
+                barrier()
+    tok, pos32 = model.token, model.position
+    with torch.inference_mode():
         tok.zero_()
         pos32.fill_(args.context)
         launches0 = lib.hqm_launch_count()
