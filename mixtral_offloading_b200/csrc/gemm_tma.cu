@@ -8,10 +8,10 @@
 //
 // A unit of work is one 64-column k-block of one tile (128 output rows x one chunk of NTOK tokens).  Three rings
 // of shared-memory buffers decouple what has different sizes and latencies:
-//   raw ring (3-4 PG deep, 3-5 KB)  the packed codes of the tile's storage rows and its scale and zero bytes, as
+//   raw ring (2 PG deep, 3-5 KB)    the packed codes of the tile's storage rows and its scale and zero bytes, as
 //                               they lie in HBM
-//   B ring (PG to 3 PG deep)     the x tile (NTOK rows x 64 bf16, 128-byte swizzle): it IS the MMA's B operand
-//   A ring (PG deep, 16 KB)     the dequantised weights, K-major, 128-byte swizzle, plus the decoded scales
+//   B ring (PG or 2 PG deep)     the x tile (NTOK rows x 64 bf16, 128-byte swizzle): it IS the MMA's B operand
+//   A ring (5 to 8 deep, 16 KB)   the dequantised weights, K-major, 128-byte swizzle, plus the decoded scales
 // Roles of the warps of a CTA (one CTA per SM, persistent; PG = 4 producer groups, 3 with 128- and 256-token tiles):
 //   producers    PG groups of 128 threads; group g takes the units g, g+PG, ...: decodes scale / zero (8 bit -> s
 //                and -z*s as bf16; the fp16 meta values are the only thing read with plain loads, requested
@@ -20,7 +20,7 @@
 //   issue warps  PG warps; warp w issues the tiled TMA copies of the units w, w+PG, ...: three lanes the raw
 //                copies, a fourth the x tile; mbarriers count the bytes.  (One thread issuing every copy of
 //                every unit was the bottleneck: a tiled copy costs its issuing thread some hundred cycles.)
-//   MMA warp     one lane issues the four tcgen05.mma (K = 16 each) of a unit and one commit that releases its A
+//   MMA warp     one lane issues the four tcgen05.mma (K = 16 each) of a unit and the commits that release its A
 //                and B slots; at the end of a tile it commits the accumulator to the epilogue warps
 //   epilogue     four warps read a finished accumulator with tcgen05.ld (each its quarter of the TMEM lanes), turn
 //                it round in shared memory and write PER consecutive output rows of a token at a time.  Two
@@ -77,10 +77,11 @@ struct Cfg {
     static constexpr int NTHREADS = (WARP_EPI + 4) * 32;
     // Ring depths.  A wait by phase parity is only sound while the waiter is at most one phase behind the
     // barrier.  Raw and B slots are refilled by one issue warp each (depths are multiples of PG), which waited for
-    // the slot's previous release itself.  A slots rotate over the groups, and their release is read off the
-    // per-unit `done` barriers (N_B of them, a multiple of N_A): group g's previous unit is PG back, which proves
-    // that the unit PG + N_A back has been consumed; N_B >= PG makes that cover the barrier's previous phase.
-    static constexpr int N_A = PG, N_RAW = (NTOK > 128 ? 3 : 4) * PG;
+    // the slot's previous release itself.  A slots rotate over the groups: group g's previous unit is PG back, which
+    // proves that the unit PG + N_A back has been consumed; N_A >= PG makes that cover the slot's last-but-one
+    // release.  The A ring takes what shared memory the B ring (x tiles in flight against the copy latency) leaves.
+    static constexpr int N_RAW = 2 * PG;
+    static constexpr int N_B = NTOK > 128 ? PG : (NTOK > 64 ? 2 * PG : 2 * PG);
     static constexpr int B_BYTES = NTOK * 128;
     static constexpr int W_BYTES = GS * RT * BK;              // staged packed bytes: [member][residue][64]
     static constexpr int Q_BYTES = RES * BK;                  // staged scale (and zero) bytes: [row][64]
@@ -92,10 +93,10 @@ struct Cfg {
     // A slot: the tile, then s and -z*s
     static constexpr int S_OFF = TILE_ROWS * 128, T_OFF = S_OFF + D_BYTES;
     static constexpr int A_BYTES = (T_OFF + D_BYTES + 1023) / 1024 * 1024;
-    static constexpr int FIXED = 1024 /*alignment slack*/ + 1024 /*barriers*/ + EPI_BYTES + N_RAW * RAW_BYTES + N_A * A_BYTES;
-    static constexpr int NB_FIT = (SMEM_LIMIT - FIXED) / B_BYTES;
-    static constexpr int N_B = (NB_FIT >= 3 * PG ? 3 : (NB_FIT >= 2 * PG ? 2 : 1)) * PG;
-    static_assert(NB_FIT >= PG, "B ring does not fit");
+    static constexpr int FIXED = 1024 /*alignment slack*/ + 1024 /*barriers*/ + EPI_BYTES + N_RAW * RAW_BYTES + N_B * B_BYTES;
+    static constexpr int NA_FIT = (SMEM_LIMIT - FIXED) / A_BYTES;
+    static constexpr int N_A = NA_FIT > 8 ? 8 : NA_FIT;
+    static_assert(N_A >= PG, "A ring too shallow for the producer groups");
     static constexpr int B_OFF = 0, A_OFF = N_B * B_BYTES, RAW_OFF = A_OFF + N_A * A_BYTES, EPI_OFF = RAW_OFF + N_RAW * RAW_BYTES,
                          BAR_OFF = EPI_OFF + EPI_BYTES;
     static constexpr size_t SMEM = (size_t)BAR_OFF + 1024 + 1024;
@@ -233,13 +234,14 @@ gemm_tma_kernel(const __grid_constant__ Params prm) {
     uint64_t* raw_full = bars;                     // [N_RAW] copies landed
     uint64_t* raw_empty = raw_full + N_RAW;        // [N_RAW] a producer group has read the slot
     uint64_t* a_full = raw_empty + N_RAW;          // [N_A] A tile written
-    uint64_t* b_full = a_full + N_A;               // [N_B] x tile landed
-    uint64_t* done = b_full + N_B;                 // [N_B] the MMAs of unit it (slot it % N_B) have read their A and B slots
+    uint64_t* a_empty = a_full + N_A;              // [N_A] the MMAs have read the A slot
+    uint64_t* b_full = a_empty + N_A;              // [N_B] x tile landed
+    uint64_t* done = b_full + N_B;                 // [N_B] the MMAs have read the B slot
     uint64_t* acc_full = done + N_B;               // [2] MMA -> epilogue
     uint64_t* acc_empty = acc_full + 2;            // [2] epilogue -> MMA
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    static_assert((2 * N_RAW + N_A + 2 * N_B + 4) * 8 + 8 <= 1024 && N_B % N_A == 0, "barrier area");
+    static_assert((2 * N_RAW + 2 * N_A + 2 * N_B + 4) * 8 + 8 <= 1024, "barrier area");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const Work work = work_of(prm);
@@ -250,7 +252,10 @@ gemm_tma_kernel(const __grid_constant__ Params prm) {
             mbar_init(raw_full + s, 1);
             mbar_init(raw_empty + s, PRODUCERS);
         }
-        for (int s = 0; s < N_A; ++s) mbar_init(a_full + s, PRODUCERS);
+        for (int s = 0; s < N_A; ++s) {
+            mbar_init(a_full + s, PRODUCERS);
+            mbar_init(a_empty + s, 1);
+        }
         for (int s = 0; s < N_B; ++s) {
             mbar_init(b_full + s, 1);
             mbar_init(done + s, 1);
@@ -309,7 +314,7 @@ gemm_tma_kernel(const __grid_constant__ Params prm) {
             bool bad = *failed != 0;
             if (!bad && !mbar_wait_relaxed(raw_full + r, (it / N_RAW) & 1)) bad = true;
             // the A slot's previous tile (unit it - N_A) has been read by its MMAs
-            if (!bad && it >= N_A && !mbar_wait_relaxed(done + (it - N_A) % N_B, ((it - N_A) / N_B) & 1)) bad = true;
+            if (!bad && it >= N_A && !mbar_wait_relaxed(a_empty + a, ((it / N_A) - 1) & 1)) bad = true;
             bad = group_any(bar_id, bad);                                    // the whole group takes the same decision
             if (bad) {
                 *failed = 1;
@@ -452,7 +457,8 @@ gemm_tma_kernel(const __grid_constant__ Params prm) {
 #pragma unroll
                 for (int k = 0; k < BK / 16; ++k)   // +32 bytes (2 descriptor units) per K = 16 step
                     umma_bf16(d, da + 2 * k, db + 2 * k, idesc, (!first || k > 0) ? 1u : 0u);
-                umma_commit(done + b);              // the A and B slots are free once these MMAs have read them
+                umma_commit(a_empty + a);           // the slots are free once these MMAs have read them
+                umma_commit(done + b);
                 first = false;
                 if (--left == 0) {                  // the tile's (or this CTA's share of its) k-blocks are issued
                     umma_commit(acc_full + buf);
