@@ -135,9 +135,25 @@ __global__ void __launch_bounds__(NORM_THREADS) finalize_add_rmsnorm_router_kern
     __shared__ float s_cta[ROUTER_EMAX];
     cg::cluster_group cluster = cg::this_cluster();
     grid_launch_dependents();
-    grid_dependency_wait();
     const int stride = NORM_CTAS * NORM_THREADS, first = blockIdx.x * NORM_THREADS + threadIdx.x;
     const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
+    // the norm weight and the gate rows of this thread's columns are weights: they are fetched while the launch in
+    // front is still finishing
+    uint16_t wv[NORM_PER_THREAD], gv[NORM_PER_THREAD][ROUTER_EMAX];
+#pragma unroll
+    for (int j = 0; j < NORM_PER_THREAD; ++j) {
+        const int i = first + j * stride;
+        wv[j] = 0;
+#pragma unroll
+        for (int e = 0; e < ROUTER_EMAX; ++e) gv[j][e] = 0;
+        if (i < H) {
+            wv[j] = w[i];
+#pragma unroll
+            for (int e = 0; e < ROUTER_EMAX; ++e)
+                if (e < E) gv[j][e] = gate_w[(int64_t)e * H + i];
+        }
+    }
+    grid_dependency_wait();
     float v[NORM_PER_THREAD];
     float ss = 0.f;
 #pragma unroll
@@ -159,12 +175,11 @@ __global__ void __launch_bounds__(NORM_THREADS) finalize_add_rmsnorm_router_kern
     for (int j = 0; j < NORM_PER_THREAD; ++j) {
         const int i = first + j * stride;
         if (i < H) {
-            const uint16_t xb = float_to_bf16_bits(bf16_bits_to_float(w[i]) * round_bf16(v[j] * rstd));
+            const uint16_t xb = float_to_bf16_bits(bf16_bits_to_float(wv[j]) * round_bf16(v[j] * rstd));
             x[i] = xb;
             const float xv = bf16_bits_to_float(xb);
 #pragma unroll
-            for (int e = 0; e < ROUTER_EMAX; ++e)
-                if (e < E) acc[e] = fmaf(xv, bf16_bits_to_float(gate_w[(int64_t)e * H + i]), acc[e]);
+            for (int e = 0; e < ROUTER_EMAX; ++e) acc[e] = fmaf(xv, bf16_bits_to_float(gv[j][e]), acc[e]);
         }
     }
 #pragma unroll
@@ -180,14 +195,19 @@ __global__ void __launch_bounds__(NORM_THREADS) finalize_add_rmsnorm_router_kern
         s_cta[threadIdx.x] = t;
     }
     cluster.sync();
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
+    if (blockIdx.x == 0 && wi == 0) {
+        // lane e adds expert e's dot product over the cluster's CTAs (in rank order, as one thread would); every
+        // lane then holds all E logits and runs the same softmax / top-2
+        float mine_e = 0.f;
+        if (lane < ROUTER_EMAX) {
+#pragma unroll
+            for (int r = 0; r < NORM_CTAS; ++r) mine_e += cluster.map_shared_rank(s_cta, r)[lane];
+            mine_e = round_bf16(mine_e);                // the gate's output in the activation dtype
+        }
         float mx = -INFINITY;
 #pragma unroll
         for (int e = 0; e < ROUTER_EMAX; ++e) {
-            float t = 0.f;
-#pragma unroll
-            for (int r = 0; r < NORM_CTAS; ++r) t += cluster.map_shared_rank(s_cta, r)[e];
-            acc[e] = round_bf16(t);                     // the gate's output in the activation dtype
+            acc[e] = __shfl_sync(0xffffffffu, mine_e, e);
             if (e < E) mx = fmaxf(mx, acc[e]);
         }
         float p[ROUTER_EMAX], sum = 0.f;
@@ -202,34 +222,37 @@ __global__ void __launch_bounds__(NORM_THREADS) finalize_add_rmsnorm_router_kern
         for (int e = 0; e < ROUTER_EMAX; ++e) {
             if (e < E) {
                 const float pe = p[e] / sum;
-                logits_out[e] = float_to_bf16_bits(acc[e]);
                 if (pe > p0) { p1 = p0; i1 = i0; p0 = pe; i0 = e; }
                 else if (pe > p1) { p1 = pe; i1 = e; }
             }
         }
+        if (lane < E) logits_out[lane] = float_to_bf16_bits(mine_e);
         if (i1 < 0) { i1 = i0; p1 = 0.f; }
         const float norm = p0 + p1;
         const float w0 = round_bf16(p0 / norm), w1 = round_bf16(p1 / norm);
-        topk_w[0] = w0;
-        topk_w[1] = w1;
-        topk_idx[0] = i0;
-        topk_idx[1] = i1;
-        if (local_idx) {
-            // expert-parallel rank owning experts [ep_lo, ep_lo + ep_n): the chosen experts it owns, in the router's
-            // order, packed into its `ep_slots` launch slots (index into the rank's own table); -1 = slot unused
-            int n = 0;
+        if (lane == 0) {
+            topk_w[0] = w0;
+            topk_w[1] = w1;
+            topk_idx[0] = i0;
+            topk_idx[1] = i1;
+            if (local_idx) {
+                // expert-parallel rank owning experts [ep_lo, ep_lo + ep_n): the chosen experts it owns, in the
+                // router's order, packed into its `ep_slots` launch slots (index into the rank's own table); -1 =
+                // slot unused
+                int n = 0;
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                const int e = c == 0 ? i0 : i1;
-                if (e >= ep_lo && e < ep_lo + ep_n && n < ep_slots) {
-                    local_idx[n] = e - ep_lo;
-                    local_w[n] = c == 0 ? w0 : w1;
-                    ++n;
+                for (int c = 0; c < 2; ++c) {
+                    const int e = c == 0 ? i0 : i1;
+                    if (e >= ep_lo && e < ep_lo + ep_n && n < ep_slots) {
+                        local_idx[n] = e - ep_lo;
+                        local_w[n] = c == 0 ? w0 : w1;
+                        ++n;
+                    }
                 }
-            }
-            for (; n < ep_slots; ++n) {
-                local_idx[n] = -1;
-                local_w[n] = 0.f;
+                for (; n < ep_slots; ++n) {
+                    local_idx[n] = -1;
+                    local_w[n] = 0.f;
+                }
             }
         }
     }
@@ -245,8 +268,14 @@ __global__ void __launch_bounds__(NORM_THREADS) finalize_scatter_add_rmsnorm_ker
     __shared__ float red[32];
     __shared__ float mine;
     grid_launch_dependents();
-    grid_dependency_wait();
     const int stride = NORM_CTAS * NORM_THREADS, first = blockIdx.x * NORM_THREADS + threadIdx.x;
+    uint16_t wv[NORM_PER_THREAD];                 // the norm weight is fetched while the launch in front finishes
+#pragma unroll
+    for (int j = 0; j < NORM_PER_THREAD; ++j) {
+        const int i = first + j * stride;
+        wv[j] = i < H ? w[i] : (uint16_t)0;
+    }
+    grid_dependency_wait();
     float v[NORM_PER_THREAD];
     float ss = 0.f;
 #pragma unroll
@@ -267,7 +296,7 @@ __global__ void __launch_bounds__(NORM_THREADS) finalize_scatter_add_rmsnorm_ker
 #pragma unroll
     for (int j = 0; j < NORM_PER_THREAD; ++j) {
         const int i = first + j * stride;
-        if (i < H) x[i] = float_to_bf16_bits(bf16_bits_to_float(w[i]) * round_bf16(v[j] * rstd));
+        if (i < H) x[i] = float_to_bf16_bits(bf16_bits_to_float(wv[j]) * round_bf16(v[j] * rstd));
     }
 }
 
@@ -506,12 +535,26 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(uint16_t* __restrict__
     __shared__ float c_acc[HEAD_DIM];
     cg::cluster_group cluster = cg::this_cluster();
     grid_launch_dependents();
-    grid_dependency_wait();
     const int head = blockIdx.x / ATTN_SPLIT, part = blockIdx.x % ATTN_SPLIT;
     const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
     const int pos = pos_ptr[0];
     const int kvh = head / group;
     const float scale = rsqrtf((float)HEAD_DIM);
+    {
+        // The cached rows below `pos` were written by earlier steps and the position is not touched inside a step:
+        // this warp's rows are requested into L2 while the launch in front (the q / k / v projections) is still
+        // running.  A row is 256 bytes = two 128-byte lines; lane -> (row lane / 2 of each batch of 16, line lane % 2).
+        constexpr int WARPS_ALL = 8 * ATTN_SPLIT;
+        const int n = min(max(pos, 0), max_len);
+        const char* kb = reinterpret_cast<const char*>(k_cache + (int64_t)kvh * max_len * HEAD_DIM);
+        const char* vb = reinterpret_cast<const char*>(v_cache + (int64_t)kvh * max_len * HEAD_DIM);
+        for (int j = part * 8 + wi + WARPS_ALL * (lane >> 1); j < n; j += WARPS_ALL * 16) {
+            const int64_t off = (int64_t)j * (HEAD_DIM * 2) + 128 * (lane & 1);
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(kb + off));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(vb + off));
+        }
+    }
+    grid_dependency_wait();
     int len;                                            // positions read from the cache
     bool fresh = false;                                 // the new position is attended to from shared memory
     float q[4];
