@@ -90,8 +90,9 @@ class MixtralDecodeModel(nn.Module):
         h = self.embed[ids]                                                # (T, hidden)
         self.router_logits = []
         ln_in = self.first_ln                       # the norm weights step() applies: first_ln, then each layer's next_ln
+        shared = self.layers[0].tokens_shared(T, pos0, h.device)
         for layer in self.layers:
-            h, logits = layer.forward_tokens(h, pos0, ln_in)
+            h, logits = layer.forward_tokens(h, pos0, ln_in, shared)
             self.router_logits.append(logits)
             ln_in = layer.next_ln
         x = rms_norm_rows(h[-1:], self.layers[-1].next_ln, self.rms_eps)

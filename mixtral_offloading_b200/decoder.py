@@ -44,13 +44,19 @@ def rms_norm_rows(h: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     return w * v
 
 
-def rope_rows(t: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor:
-    """t: (T, heads, head_dim) bf16; rotate-half RoPE with bf16 cos / sin, as the decode kernel applies it."""
-    hd = t.shape[-1]
-    inv = theta ** (-torch.arange(0, hd, 2, dtype=torch.float32, device=t.device) / hd)
+def rope_tables(positions: torch.Tensor, head_dim: int, theta: float):
+    """bf16 cos / sin rows (T, 1, head_dim) of the given positions, as the decode kernel applies them."""
+    inv = theta ** (-torch.arange(0, head_dim, 2, dtype=torch.float32, device=positions.device) / head_dim)
     ang = positions.float()[:, None] * inv[None, :]
     cos = torch.cat([ang.cos(), ang.cos()], -1).to(torch.bfloat16)[:, None, :]
     sin = torch.cat([ang.sin(), ang.sin()], -1).to(torch.bfloat16)[:, None, :]
+    return cos, sin
+
+
+def rope_rows(t: torch.Tensor, positions: torch.Tensor, theta: float, tables=None) -> torch.Tensor:
+    """t: (T, heads, head_dim) bf16; rotate-half RoPE with bf16 cos / sin (rope_tables, computed here unless given)."""
+    hd = t.shape[-1]
+    cos, sin = tables if tables is not None else rope_tables(positions, hd, theta)
     rot = torch.cat([-t[..., hd // 2:], t[..., :hd // 2]], -1)
     return t * cos + rot * sin
 
@@ -146,30 +152,38 @@ class DecoderLayerDecode(nn.Module):
                 n_experts=self.moe.num_experts, reserved=0)
         return self._layer
 
+    def tokens_shared(self, T: int, pos0: int, device):
+        """(positions, RoPE tables, attention mask) of T tokens at positions pos0 .. pos0 + T - 1: token i sees
+        positions 0 .. pos0 + i."""
+        a = self.attention
+        positions = torch.arange(pos0, pos0 + T, device=device)
+        mask = torch.arange(pos0 + T, device=device)[None, :] <= positions[:, None]
+        return positions, rope_tables(positions, a.head_dim, a.rope_theta), mask
+
     @torch.inference_mode()
-    def forward_tokens(self, h: torch.Tensor, pos0: int, ln_in=None):
+    def forward_tokens(self, h: torch.Tensor, pos0: int, ln_in=None, shared=None):
         """T new tokens at once (a prompt, or a chunk of 32 / 256 tokens behind a cache that already holds pos0
         positions): h (T, hidden) bf16 is the residual stream of the tokens at positions pos0 .. pos0 + T - 1.
         The quantized projections and the experts take their many-row (tensor-core) kernels; norms, RoPE and the
         attention over the cache are torch ops; the MoE block groups the tokens per expert.  Appends the tokens'
         keys and values to the cache; returns (updated h, router logits (T, n_experts)).  ln_in: the layer's input
         norm weight when it is not attention.ln_in (a model hands every layer the weight its predecessor was built
-        with as next_ln, which is what the one-token path applies)."""
+        with as next_ln, which is what the one-token path applies).  shared: what tokens_shared() returned for the
+        same (T, pos0), when several layers process the same tokens (positions, RoPE tables and mask are the same
+        for all of them)."""
         a = self.attention
         ln_in = a.ln_in if ln_in is None else ln_in
         T, hidden = h.shape
         if pos0 < 0 or pos0 + T > a.max_len:
             raise ValueError(f"{T} tokens at position {pos0} do not fit a cache of {a.max_len}")
-        positions = torch.arange(pos0, pos0 + T, device=h.device)
+        positions, tables, mask = shared if shared is not None else self.tokens_shared(T, pos0, h.device)
         x = rms_norm_rows(h, ln_in, a.rms_eps)
-        q = rope_rows(a.q_proj(x).view(T, a.n_heads, a.head_dim), positions, a.rope_theta)
-        k = rope_rows(a.k_proj(x).view(T, a.n_kv_heads, a.head_dim), positions, a.rope_theta)
+        q = rope_rows(a.q_proj(x).view(T, a.n_heads, a.head_dim), positions, a.rope_theta, tables)
+        k = rope_rows(a.k_proj(x).view(T, a.n_kv_heads, a.head_dim), positions, a.rope_theta, tables)
         v = a.v_proj(x).view(T, a.n_kv_heads, a.head_dim)
         a.k_cache[:, pos0:pos0 + T] = k.transpose(0, 1)
         a.v_cache[:, pos0:pos0 + T] = v.transpose(0, 1)
         keys, vals = a.k_cache[:, :pos0 + T].unsqueeze(0), a.v_cache[:, :pos0 + T].unsqueeze(0)
-        # token i (position pos0 + i) sees positions 0 .. pos0 + i
-        mask = torch.arange(pos0 + T, device=h.device)[None, :] <= positions[:, None]
         ctx = torch.nn.functional.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), keys, vals, attn_mask=mask,
                                                                enable_gqa=True)          # (1, heads, T, head_dim)
         h = h + a.o_proj(ctx[0].transpose(0, 1).reshape(T, hidden))
