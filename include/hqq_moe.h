@@ -283,6 +283,10 @@ int hqm_add_f32_rmsnorm(uint16_t* h, const float* delta, const uint16_t* weight,
  * of the Hugging Face decoder with the preceding residual add (used for the last layer's output and the final norm). */
 int hqm_add_rmsnorm(uint16_t* h, const uint16_t* delta, const uint16_t* weight, uint16_t* x_out, int32_t hidden,
                     float eps, void* stream);
+/* The same for `rows` rows at once (a prompt, a batch of sequences): h and delta (rows, hidden) bf16, x_out
+ * (rows, hidden) bf16; delta may be NULL (then h is only read). */
+int hqm_add_rmsnorm_rows(uint16_t* h, const uint16_t* delta, const uint16_t* weight, uint16_t* x_out, int64_t rows,
+                         int32_t hidden, float eps, void* stream);
 
 /* ---- expert residency: src/expert_cache.py -------------------------------- */
 /* ExpertCache (expert_cache.py:55-201).  The handle owns the bookkeeping of

@@ -87,6 +87,39 @@ __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(uint16_t* __r
     }
 }
 
+// The same for many rows (a prompt, a batch of sequences): one CTA per row of h (rows, H), two passes over the row
+// (the second re-reads the bf16 values the first one wrote or left in place).
+__global__ void __launch_bounds__(256) add_rmsnorm_rows_kernel(uint16_t* __restrict__ h, const uint16_t* __restrict__ delta,
+                                                               const uint16_t* __restrict__ w, uint16_t* __restrict__ x,
+                                                               int H, float eps) {
+    __shared__ float red[8];
+    __shared__ float s_rstd;
+    uint16_t* hr = h + (int64_t)blockIdx.x * H;
+    const uint16_t* dr = delta ? delta + (int64_t)blockIdx.x * H : nullptr;
+    uint16_t* xr = x + (int64_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += 256) {
+        float v = bf16_bits_to_float(hr[i]);
+        if (dr) {
+            v = round_bf16(v + bf16_bits_to_float(dr[i]));
+            hr[i] = float_to_bf16_bits(v);
+        }
+        ss += v * v;
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < 8 ? red[threadIdx.x] : 0.f;
+        t = warp_sum(t);
+        if (threadIdx.x == 0) s_rstd = rsqrtf(t / (float)H + eps);
+    }
+    __syncthreads();
+    const float rstd = s_rstd;
+    for (int i = threadIdx.x; i < H; i += 256)
+        xr[i] = float_to_bf16_bits(bf16_bits_to_float(w[i]) * round_bf16(bf16_bits_to_float(hr[i]) * rstd));
+}
+
 // h = bf16(h + bf16(o-projection sums)), x = rmsnorm(h) * w.  One cluster; the sums are the partial row-sets
 // of a streaming launch.
 __global__ void __launch_bounds__(NORM_THREADS) finalize_add_rmsnorm_kernel(uint16_t* __restrict__ h,
@@ -732,6 +765,18 @@ int hqm_add_rmsnorm(uint16_t* h, const uint16_t* delta, const uint16_t* weight, 
                   NORM_CTAS * NORM_THREADS * NORM_PER_THREAD);
     launch_overlapped_cluster(add_rmsnorm_kernel, NORM_CTAS, NORM_THREADS, 0, NORM_CTAS, (cudaStream_t)stream, h, delta,
                               weight, x_out, (int)hidden, eps);
+    HQM_LAUNCH_CHECK();
+    return HQM_OK;
+}
+
+int hqm_add_rmsnorm_rows(uint16_t* h, const uint16_t* delta, const uint16_t* weight, uint16_t* x_out, int64_t rows,
+                         int32_t hidden, float eps, void* stream) {
+    using namespace hqm;
+    HQM_CHECK_ARG(rows >= 0 && rows <= INT32_MAX && hidden > 0, "add_rmsnorm_rows: bad shape (%lld, %d)", (long long)rows,
+                  hidden);
+    if (rows == 0) return HQM_OK;
+    HQM_CHECK_ARG(h && weight && x_out, "add_rmsnorm_rows: null pointer");
+    add_rmsnorm_rows_kernel<<<(int)rows, 256, 0, (cudaStream_t)stream>>>(h, delta, weight, x_out, (int)hidden, eps);
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }

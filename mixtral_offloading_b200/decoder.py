@@ -37,11 +37,17 @@ def add_rmsnorm(h: torch.Tensor, delta, weight: torch.Tensor, eps: float = 1e-5)
 
 
 def rms_norm_rows(h: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
-    """RMSNorm of every row as the decode kernels compute it: fp32 normalisation, one rounding to bf16, times the
-    bf16 weight (the Hugging Face form)."""
-    v = h.float()
-    v = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).to(torch.bfloat16)
-    return w * v
+    """RMSNorm of every row of h (rows, hidden) bf16 as the decode kernels compute it: fp32 normalisation, one
+    rounding to bf16, times the bf16 weight (the Hugging Face form).  One launch (hqm_add_rmsnorm_rows)."""
+    rows, hidden = h.shape
+    _cabi.require_cuda(h, w)
+    if h.dtype != torch.bfloat16 or not h.is_contiguous():
+        h = h.to(torch.bfloat16).contiguous()
+    _bf16_vec(w, hidden)
+    x = torch.empty_like(h)
+    _cabi.check(_cabi.lib().hqm_add_rmsnorm_rows(_cabi.ptr(h), None, _cabi.ptr(w), _cabi.ptr(x), rows, hidden, eps,
+                                                 _cabi.stream_ptr(h.device)))
+    return x
 
 
 def rope_tables(positions: torch.Tensor, head_dim: int, theta: float):
