@@ -287,6 +287,16 @@ int hqm_add_rmsnorm(uint16_t* h, const uint16_t* delta, const uint16_t* weight, 
  * (rows, hidden) bf16; delta may be NULL (then h is only read). */
 int hqm_add_rmsnorm_rows(uint16_t* h, const uint16_t* delta, const uint16_t* weight, uint16_t* x_out, int64_t rows,
                          int32_t hidden, float eps, void* stream);
+/* Rotary embedding and cache append for `tokens` tokens at once (modeling_mixtral.py apply_rotary_pos_emb and the
+ * cache update of MixtralAttention.forward, with the arithmetic of hqm_attn_decode): q (tokens, n_heads, 128) bf16 is
+ * rotated in place; k (tokens, n_kv_heads, 128) is rotated and, with v, written to row `pos` of the caches
+ * (n_kv_heads, max_len, 128).  Token t has position base + t * pos_step, base = *pos_device (device memory) when
+ * given, else pos0, and uses the cache batch_stride * t elements further on: a prompt has pos_step 1 and
+ * batch_stride 0, a batch of sequences at one position pos_step 0 and batch_stride = the size of one cache. */
+int hqm_rope_append_rows(uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* k_cache, uint16_t* v_cache,
+                         int64_t tokens, int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, int32_t max_len,
+                         int64_t batch_stride, const int64_t* pos_device, int32_t pos0, int32_t pos_step, float rope_theta,
+                         void* stream);
 
 /* ---- expert residency: src/expert_cache.py -------------------------------- */
 /* ExpertCache (expert_cache.py:55-201).  The handle owns the bookkeeping of

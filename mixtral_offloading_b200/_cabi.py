@@ -98,6 +98,8 @@ SIGNATURES = {
     "hqm_add_f32_rmsnorm": (C.c_int, [_P, _P, _P, _P, _I32, C.c_float, _P]),
     "hqm_add_rmsnorm": (C.c_int, [_P, _P, _P, _P, _I32, C.c_float, _P]),
     "hqm_add_rmsnorm_rows": (C.c_int, [_P, _P, _P, _P, C.c_int64, _I32, C.c_float, _P]),
+    "hqm_rope_append_rows": (C.c_int, [_P, _P, _P, _P, _P, C.c_int64, _I32, _I32, _I32, _I32, C.c_int64, _P, _I32, _I32,
+                                       C.c_float, _P]),
     "hqm_router_top2": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _P]),
     "hqm_cache_create": (C.c_int, [C.POINTER(_P), _I32, _I32, _I32, C.c_size_t, C.POINTER(_P), _I32]),
     "hqm_cache_destroy": (None, [_P]),

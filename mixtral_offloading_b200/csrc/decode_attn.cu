@@ -556,6 +556,47 @@ __device__ __forceinline__ void rope_pair(float a, float b, int d, int pos, floa
     o1 = round_bf16(round_bf16(b * cs) + round_bf16(a * sn));
 }
 
+// RoPE and cache append for many tokens at once (a prompt: token t at position pos0 + t in ONE cache; a batch of
+// sequences: token t at the same position in ITS cache, batch_stride elements further on).  One CTA per token:
+// q (T, n_heads, 128) is rotated in place, k rotated and v copied into row `pos` of the key / value caches
+// (n_kv, max_len, 128).  A position outside the cache sets the error flag and leaves the token untouched.
+__global__ void __launch_bounds__(256) rope_append_rows_kernel(uint16_t* __restrict__ q, const uint16_t* __restrict__ k,
+                                                               const uint16_t* __restrict__ v,
+                                                               uint16_t* __restrict__ k_cache, uint16_t* __restrict__ v_cache,
+                                                               int n_heads, int n_kv, int max_len, int64_t batch_stride,
+                                                               const int64_t* __restrict__ pos_ptr, int pos0, int pos_step,
+                                                               float theta, int* error_flag) {
+    const int t = blockIdx.x;
+    const int pos = (pos_ptr ? (int)pos_ptr[0] : pos0) + t * pos_step;
+    if (pos < 0 || pos >= max_len) {
+        if (threadIdx.x == 0 && error_flag) atomicExch(error_flag, 2);
+        return;
+    }
+    constexpr int HALF = HEAD_DIM / 2;
+    uint16_t* qt = q + (int64_t)t * n_heads * HEAD_DIM;
+    for (int i = threadIdx.x; i < n_heads * HALF; i += 256) {
+        const int head = i / HALF, d = i % HALF;
+        uint16_t* p = qt + head * HEAD_DIM + d;
+        float o0, o1;
+        rope_pair(bf16_bits_to_float(p[0]), bf16_bits_to_float(p[HALF]), d, pos, theta, o0, o1);
+        p[0] = float_to_bf16_bits(o0);
+        p[HALF] = float_to_bf16_bits(o1);
+    }
+    const uint16_t* kt = k + (int64_t)t * n_kv * HEAD_DIM;
+    const uint16_t* vt = v + (int64_t)t * n_kv * HEAD_DIM;
+    for (int i = threadIdx.x; i < n_kv * HALF; i += 256) {
+        const int head = i / HALF, d = i % HALF;
+        const int64_t row = (int64_t)t * batch_stride + ((int64_t)head * max_len + pos) * HEAD_DIM + d;
+        float o0, o1;
+        rope_pair(bf16_bits_to_float(kt[head * HEAD_DIM + d]), bf16_bits_to_float(kt[head * HEAD_DIM + d + HALF]), d, pos, theta,
+                  o0, o1);
+        k_cache[row] = float_to_bf16_bits(o0);
+        k_cache[row + HALF] = float_to_bf16_bits(o1);
+        v_cache[row] = vt[head * HEAD_DIM + d];
+        v_cache[row + HALF] = vt[head * HEAD_DIM + d + HALF];
+    }
+}
+
 template <bool FUSED>
 __global__ void __launch_bounds__(256) attn_decode_kernel(uint16_t* __restrict__ ctx, const uint16_t* __restrict__ qbuf,
                                                           uint16_t* __restrict__ k_cache, uint16_t* __restrict__ v_cache,
@@ -777,6 +818,24 @@ int hqm_add_rmsnorm_rows(uint16_t* h, const uint16_t* delta, const uint16_t* wei
     if (rows == 0) return HQM_OK;
     HQM_CHECK_ARG(h && weight && x_out, "add_rmsnorm_rows: null pointer");
     add_rmsnorm_rows_kernel<<<(int)rows, 256, 0, (cudaStream_t)stream>>>(h, delta, weight, x_out, (int)hidden, eps);
+    HQM_LAUNCH_CHECK();
+    return HQM_OK;
+}
+
+int hqm_rope_append_rows(uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* k_cache, uint16_t* v_cache,
+                         int64_t tokens, int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, int32_t max_len,
+                         int64_t batch_stride, const int64_t* pos_device, int32_t pos0, int32_t pos_step, float rope_theta,
+                         void* stream) {
+    using namespace hqm;
+    HQM_CHECK_ARG(tokens >= 0 && tokens <= INT32_MAX, "rope_append_rows: bad token count %lld", (long long)tokens);
+    if (tokens == 0) return HQM_OK;
+    HQM_CHECK_ARG(q && k && v && k_cache && v_cache, "rope_append_rows: null pointer");
+    HQM_CHECK_ARG(head_dim == HEAD_DIM && n_heads > 0 && n_kv_heads > 0 && max_len > 0,
+                  "rope_append_rows: head_dim %d (only %d), %d / %d heads, cache of %d", head_dim, HEAD_DIM, n_heads,
+                  n_kv_heads, max_len);
+    rope_append_rows_kernel<<<(int)tokens, 256, 0, (cudaStream_t)stream>>>(q, k, v, k_cache, v_cache, n_heads, n_kv_heads,
+                                                                           max_len, batch_stride, pos_device, pos0,
+                                                                           pos_step, rope_theta, tc_error_ptr());
     HQM_LAUNCH_CHECK();
     return HQM_OK;
 }

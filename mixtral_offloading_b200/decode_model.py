@@ -14,7 +14,7 @@ from typing import List, Sequence
 import torch
 from torch import nn
 
-from .decoder import DecoderLayerDecode, add_rmsnorm, rms_norm_rows, rope_rows
+from .decoder import DecoderLayerDecode, add_rmsnorm, rms_norm_rows, rope_append_rows
 
 
 class MixtralDecodeModel(nn.Module):
@@ -141,8 +141,8 @@ class BatchDecode:
     rows per expert as SparseMoeWrapper.forward does (custom_layers.py:272-314), which needs the row counts on the
     host once per layer.  A step is therefore a chain of segments, one per layer: [add the previous block's output,
     attention half, post-attention norm, router] - read the counts back - [the active experts].  capture() records
-    every segment in a CUDA graph (the position is device data: the cache row is written by index_copy_ and
-    attention runs over the whole cache under a mask), so that the host issues one replay and the experts per layer."""
+    every segment in a CUDA graph (the position is device data: hqm_rope_append_rows reads it, and attention runs
+    over the whole cache under a mask), so that the host issues one replay and the experts per layer."""
 
     def __init__(self, model: MixtralDecodeModel, batch: int, max_len: int):
         self.model, self.batch, self.max_len = model, batch, max_len
@@ -157,46 +157,35 @@ class BatchDecode:
         self.h = torch.zeros((batch, hidden), dtype=torch.bfloat16, device=dev)     # residual streams
         self.y = torch.zeros((batch, hidden), dtype=torch.bfloat16, device=dev)     # the last MoE block's output
         self._slots = torch.arange(max_len, device=dev)
-        self._inv_freq = a0.rope_theta ** (-torch.arange(0, a0.head_dim, 2, dtype=torch.float32, device=dev) / a0.head_dim)
         E = model.layers[0].moe.num_experts
         self._host_counts = torch.empty((2 * E + 1,), dtype=torch.int32).pin_memory()
         self.router_logits: List[torch.Tensor] = []
         self._graphs = None
         self._routes = [None] * len(model.layers)
         self._x_moe = [None] * len(model.layers)
-        self._rope = None
+        self._mask = None
         self._logits = None
 
     # ---- segments ---------------------------------------------------------------------------------------------
     def _prologue(self):
-        """cos / sin of the position (bf16, as the decode kernel applies them) and the mask of filled cache rows."""
-        ang = self.position.float()[:, None] * self._inv_freq[None, :]
-        cos = torch.cat([ang.cos(), ang.cos()], -1).to(torch.bfloat16)[:, None, :]
-        sin = torch.cat([ang.sin(), ang.sin()], -1).to(torch.bfloat16)[:, None, :]
-        self._rope = (cos, sin, (self._slots <= self.position)[None, None, None, :])
+        """The streams of the fed tokens and the mask of filled cache rows."""
+        self._mask = (self._slots <= self.position)[None, None, None, :]
         self.h.copy_(self.model.embed[self.tokens])
         self.y.zero_()
-
-    @staticmethod
-    def _rotate(t, cos, sin):
-        hd = t.shape[-1]
-        rot = torch.cat([-t[..., hd // 2:], t[..., :hd // 2]], -1)
-        return t * cos + rot * sin
 
     def _attention_segment(self, l: int):
         layer = self.model.layers[l]
         a, B, h = layer.attention, self.batch, self.h
         hidden = h.shape[-1]
-        cos, sin, mask = self._rope
+        mask = self._mask
         h.add_(self.y)
         self.y.zero_()
         ln_in = self.model.first_ln if l == 0 else self.model.layers[l - 1].next_ln     # the weights step() applies
         x = rms_norm_rows(h, ln_in, a.rms_eps)
-        q = self._rotate(a.q_proj(x).view(B, a.n_heads, a.head_dim), cos, sin)
-        k = self._rotate(a.k_proj(x).view(B, a.n_kv_heads, a.head_dim), cos, sin)
-        v = a.v_proj(x).view(B, a.n_kv_heads, a.head_dim)
-        self.k_caches[l].index_copy_(2, self.position, k.unsqueeze(2))
-        self.v_caches[l].index_copy_(2, self.position, v.unsqueeze(2))
+        q = a.q_proj(x)
+        rope_append_rows(q, a.k_proj(x), a.v_proj(x), self.k_caches[l], self.v_caches[l], a.n_heads, a.n_kv_heads,
+                         a.head_dim, a.rope_theta, self.position, 0)
+        q = q.view(B, a.n_heads, a.head_dim)
         ctx = torch.nn.functional.scaled_dot_product_attention(q.unsqueeze(2), self.k_caches[l], self.v_caches[l],
                                                                attn_mask=mask, enable_gqa=True)   # (B, heads, 1, head_dim)
         h.add_(a.o_proj(ctx.reshape(B, hidden)))

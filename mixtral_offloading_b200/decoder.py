@@ -50,21 +50,27 @@ def rms_norm_rows(h: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     return x
 
 
-def rope_tables(positions: torch.Tensor, head_dim: int, theta: float):
-    """bf16 cos / sin rows (T, 1, head_dim) of the given positions, as the decode kernel applies them."""
-    inv = theta ** (-torch.arange(0, head_dim, 2, dtype=torch.float32, device=positions.device) / head_dim)
-    ang = positions.float()[:, None] * inv[None, :]
-    cos = torch.cat([ang.cos(), ang.cos()], -1).to(torch.bfloat16)[:, None, :]
-    sin = torch.cat([ang.sin(), ang.sin()], -1).to(torch.bfloat16)[:, None, :]
-    return cos, sin
-
-
-def rope_rows(t: torch.Tensor, positions: torch.Tensor, theta: float, tables=None) -> torch.Tensor:
-    """t: (T, heads, head_dim) bf16; rotate-half RoPE with bf16 cos / sin (rope_tables, computed here unless given)."""
-    hd = t.shape[-1]
-    cos, sin = tables if tables is not None else rope_tables(positions, hd, theta)
-    rot = torch.cat([-t[..., hd // 2:], t[..., :hd // 2]], -1)
-    return t * cos + rot * sin
+def rope_append_rows(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     n_heads: int, n_kv_heads: int, head_dim: int, theta: float, pos, pos_step: int) -> None:
+    """Rotary embedding and cache append of T tokens in one launch (hqm_rope_append_rows): q (T, n_heads * head_dim)
+    bf16 is rotated in place; k is rotated and, with v, written into the caches.  A prompt: caches
+    (n_kv_heads, max_len, head_dim), pos = position of the first token (int), pos_step = 1.  A batch of sequences
+    at one position: caches (T, n_kv_heads, max_len, head_dim), pos = int64 device tensor of one element,
+    pos_step = 0."""
+    T = q.shape[0]
+    for t, n in ((q, n_heads), (k, n_kv_heads), (v, n_kv_heads)):
+        assert t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and t.shape == (T, n * head_dim)
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape == v_cache.shape
+    max_len = k_cache.shape[-2]
+    batch_stride = 0 if k_cache.dim() == 3 else n_kv_heads * max_len * head_dim
+    assert k_cache.dim() == 3 or k_cache.shape[0] == T
+    on_device = isinstance(pos, torch.Tensor)
+    if on_device:
+        assert pos.is_cuda and pos.dtype == torch.int64 and pos.numel() == 1
+    _cabi.check(_cabi.lib().hqm_rope_append_rows(
+        _cabi.ptr(q), _cabi.ptr(k), _cabi.ptr(v), _cabi.ptr(k_cache), _cabi.ptr(v_cache), T, n_heads, n_kv_heads, head_dim,
+        max_len, batch_stride, _cabi.ptr(pos) if on_device else None, 0 if on_device else int(pos), pos_step, theta,
+        _cabi.stream_ptr(q.device)))
 
 
 class AttentionDecode(nn.Module):
@@ -158,13 +164,11 @@ class DecoderLayerDecode(nn.Module):
                 n_experts=self.moe.num_experts, reserved=0)
         return self._layer
 
-    def tokens_shared(self, T: int, pos0: int, device):
-        """(positions, RoPE tables, attention mask) of T tokens at positions pos0 .. pos0 + T - 1: token i sees
-        positions 0 .. pos0 + i."""
-        a = self.attention
+    @staticmethod
+    def tokens_shared(T: int, pos0: int, device):
+        """The attention mask of T tokens at positions pos0 .. pos0 + T - 1: token i sees positions 0 .. pos0 + i."""
         positions = torch.arange(pos0, pos0 + T, device=device)
-        mask = torch.arange(pos0 + T, device=device)[None, :] <= positions[:, None]
-        return positions, rope_tables(positions, a.head_dim, a.rope_theta), mask
+        return torch.arange(pos0 + T, device=device)[None, :] <= positions[:, None]
 
     @torch.inference_mode()
     def forward_tokens(self, h: torch.Tensor, pos0: int, ln_in=None, shared=None):
@@ -175,20 +179,18 @@ class DecoderLayerDecode(nn.Module):
         keys and values to the cache; returns (updated h, router logits (T, n_experts)).  ln_in: the layer's input
         norm weight when it is not attention.ln_in (a model hands every layer the weight its predecessor was built
         with as next_ln, which is what the one-token path applies).  shared: what tokens_shared() returned for the
-        same (T, pos0), when several layers process the same tokens (positions, RoPE tables and mask are the same
-        for all of them)."""
+        same (T, pos0), when several layers process the same tokens (the mask is the same for all of them)."""
         a = self.attention
         ln_in = a.ln_in if ln_in is None else ln_in
         T, hidden = h.shape
         if pos0 < 0 or pos0 + T > a.max_len:
             raise ValueError(f"{T} tokens at position {pos0} do not fit a cache of {a.max_len}")
-        positions, tables, mask = shared if shared is not None else self.tokens_shared(T, pos0, h.device)
+        mask = shared if shared is not None else self.tokens_shared(T, pos0, h.device)
         x = rms_norm_rows(h, ln_in, a.rms_eps)
-        q = rope_rows(a.q_proj(x).view(T, a.n_heads, a.head_dim), positions, a.rope_theta, tables)
-        k = rope_rows(a.k_proj(x).view(T, a.n_kv_heads, a.head_dim), positions, a.rope_theta, tables)
-        v = a.v_proj(x).view(T, a.n_kv_heads, a.head_dim)
-        a.k_cache[:, pos0:pos0 + T] = k.transpose(0, 1)
-        a.v_cache[:, pos0:pos0 + T] = v.transpose(0, 1)
+        q = a.q_proj(x)
+        rope_append_rows(q, a.k_proj(x), a.v_proj(x), a.k_cache, a.v_cache, a.n_heads, a.n_kv_heads, a.head_dim,
+                         a.rope_theta, pos0, 1)
+        q = q.view(T, a.n_heads, a.head_dim)
         keys, vals = a.k_cache[:, :pos0 + T].unsqueeze(0), a.v_cache[:, :pos0 + T].unsqueeze(0)
         ctx = torch.nn.functional.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), keys, vals, attn_mask=mask,
                                                                enable_gqa=True)          # (1, heads, T, head_dim)
