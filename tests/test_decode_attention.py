@@ -277,3 +277,51 @@ def test_prefill_matches_feeding_the_prompt_token_by_token():
     assert rel(caches_step[0][1], layers[0].attention.v_cache[:, :20].float().cpu()) < 2e-2
     assert rel(logits_pre, logits_step) < 0.15
     assert len(model.generate(prompt, 5, prefill=True)) == 5
+
+
+def test_row_kernels_against_the_oracle():
+    """hqm_add_rmsnorm_rows and hqm_rope_append_rows (a prompt's layout and a batch's) against the pinned oracle's
+    RMSNorm and rotary embedding with bf16 rounding where the Hugging Face bf16 model rounds."""
+    from mixtral_offloading_b200 import _cabi
+    from mixtral_offloading_b200.decoder import rms_norm_rows, rope_append_rows
+    from oracle import attention_oracle as A
+    g = torch.Generator().manual_seed(5)
+    T, n_heads, n_kv, max_len, theta = 37, 4, 2, 64, 1e6
+    hidden = n_heads * HD
+    h = (3 * torch.randn(T, hidden, generator=g)).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16)
+    x = rms_norm_rows(h.to(DEV), w.to(DEV), 1e-5).float().cpu()
+    want = A.rms_norm(h.float(), w.float(), 1e-5, torch.bfloat16)
+    assert rel(x, want) < 4e-3                                     # one bf16 step where the fp32 normalisation differs
+    q = torch.randn(T, n_heads * HD, generator=g).to(torch.bfloat16)
+    k = torch.randn(T, n_kv * HD, generator=g).to(torch.bfloat16)
+    v = torch.randn(T, n_kv * HD, generator=g).to(torch.bfloat16)
+    pos0 = 11
+    cos, sin = A.rope_cos_sin(torch.arange(pos0, pos0 + T), HD, theta, torch.bfloat16)
+    q_ref = A.apply_rope(q.float().view(T, n_heads, HD), cos[:, None, :], sin[:, None, :], torch.bfloat16)
+    k_ref = A.apply_rope(k.float().view(T, n_kv, HD), cos[:, None, :], sin[:, None, :], torch.bfloat16)
+    # a prompt: one cache, consecutive positions
+    qd = q.clone().to(DEV)
+    kc = torch.zeros(n_kv, max_len, HD, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    rope_append_rows(qd, k.to(DEV), v.to(DEV), kc, vc, n_heads, n_kv, HD, theta, pos0, 1)
+    assert rel(qd.view(T, n_heads, HD), q_ref) < 1e-2
+    assert rel(kc[:, pos0:pos0 + T].transpose(0, 1), k_ref) < 1e-2
+    assert torch.equal(vc[:, pos0:pos0 + T].transpose(0, 1).cpu(), v.view(T, n_kv, HD))
+    assert float(kc[:, :pos0].abs().max()) == 0 and float(kc[:, pos0 + T:].abs().max()) == 0
+    # a batch: one cache per token, all at the position held in device memory
+    B, pos = 5, 23
+    cosb, sinb = A.rope_cos_sin(pos, HD, theta, torch.bfloat16)
+    kb_ref = A.apply_rope(k[:B].float().view(B, n_kv, HD), cosb, sinb, torch.bfloat16)
+    qd = q[:B].clone().to(DEV)
+    kcb = torch.zeros(B, n_kv, max_len, HD, dtype=torch.bfloat16, device=DEV)
+    vcb = torch.zeros_like(kcb)
+    rope_append_rows(qd, k[:B].contiguous().to(DEV), v[:B].contiguous().to(DEV), kcb, vcb, n_heads, n_kv, HD, theta,
+                     torch.tensor([pos], dtype=torch.int64, device=DEV), 0)
+    assert rel(kcb[:, :, pos], kb_ref) < 1e-2
+    assert torch.equal(vcb[:, :, pos].cpu(), v[:B].view(B, n_kv, HD))
+    assert _cabi.lib().hqm_device_error() == 0
+    # a position outside the cache is reported, nothing is written
+    rope_append_rows(qd, k[:B].contiguous().to(DEV), v[:B].contiguous().to(DEV), kcb, vcb, n_heads, n_kv, HD, theta,
+                     torch.tensor([max_len], dtype=torch.int64, device=DEV), 0)
+    assert _cabi.lib().hqm_device_error() == 2
