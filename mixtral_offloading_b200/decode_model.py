@@ -15,6 +15,7 @@ import torch
 from torch import nn
 
 from .decoder import DecoderLayerDecode, add_rmsnorm, rms_norm_rows, rope_append_rows
+from .sampling import sample_token
 
 
 class MixtralDecodeModel(nn.Module):
@@ -108,27 +109,36 @@ class MixtralDecodeModel(nn.Module):
         return self.extend(prompt_ids)
 
     @torch.inference_mode()
-    def generate(self, prompt_ids: Sequence[int], new_tokens: int, use_graph: bool = True,
-                 prefill: bool = False) -> List[int]:
-        """Greedy continuation of prompt_ids.  The prompt is fed token by token through the decode step, or,
-        with prefill=True, in one pass through prefill()."""
-        if len(prompt_ids) == 0 or len(prompt_ids) + new_tokens > self.max_len:
-            raise ValueError(f"prompt of {len(prompt_ids)} + {new_tokens} new tokens does not fit a cache of {self.max_len}")
+    def generate(self, prompt_ids: Sequence[int], new_tokens: int, use_graph: bool = True, prefill: bool = False,
+                 do_sample: bool = False, temperature: float = 1.0, top_p: float = 1.0, generator=None,
+                 eos_token_id=None, continue_cache: bool = False) -> List[int]:
+        """Continuation of prompt_ids: greedy, or (do_sample) drawn with the demo's settings (notebooks/demo.ipynb:
+        temperature and nucleus sampling, sampling.sample_token).  The prompt is fed token by token through the decode
+        step, or, with prefill=True, in one pass through extend().  continue_cache=True keeps what the caches hold
+        and appends behind it (the demo's multi-turn loop passes past_key_values back in); otherwise the caches
+        start empty.  Stops early after eos_token_id.  Returns the new tokens."""
+        start = int(self.position.item()) if continue_cache else 0
+        if len(prompt_ids) == 0 or start + len(prompt_ids) + new_tokens > self.max_len:
+            raise ValueError(f"{start} cached + {len(prompt_ids)} prompt + {new_tokens} new tokens do not fit a cache of "
+                             f"{self.max_len}")
         if use_graph and self._graph is None:
             self.capture()
         run = self.replay if use_graph else self.step
-        out: List[int] = []
+
+        def choose(logits):              # step() leaves the greedy token in self.token; sampling overwrites it
+            if do_sample:
+                self.token.copy_(sample_token(logits, temperature, top_p, generator))
+            return int(self.token.item())
+        self.position.fill_(start)
         if prefill:
-            self.prefill(prompt_ids)
+            logits = self.extend(prompt_ids)
         else:
-            self.position.zero_()
             for t in prompt_ids:
                 self.token.fill_(int(t))
-                run()
-        out.append(int(self.token.item()))
-        for _ in range(new_tokens - 1):
-            run()
-            out.append(int(self.token.item()))
+                logits = run()
+        out: List[int] = [choose(logits)]
+        while len(out) < new_tokens and out[-1] != eos_token_id:
+            out.append(choose(run()))
         return out
 
 

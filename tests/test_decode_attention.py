@@ -325,3 +325,43 @@ def test_row_kernels_against_the_oracle():
     rope_append_rows(qd, k[:B].contiguous().to(DEV), v[:B].contiguous().to(DEV), kcb, vcb, n_heads, n_kv, HD, theta,
                      torch.tensor([max_len], dtype=torch.int64, device=DEV), 0)
     assert _cabi.lib().hqm_device_error() == 2
+
+
+def _small_model(max_len=96, vocab=300, seed=91):
+    from tests.test_gpu_parity import make_expert
+    n_heads, n_kv, ffn, E, L = 4, 2, 1792, 8, 2
+    hidden = n_heads * HD
+    g = torch.Generator().manual_seed(seed)
+    lns = [(1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16).to(DEV) for _ in range(L + 1)]
+    layers = []
+    for l in range(L):
+        attn, _, _ = build(n_heads, n_kv, max_len, seed=seed + 7 * l)
+        experts = [make_expert(hidden, ffn, (random_layer(ffn, hidden, 2, 16, 700 + 30 * l + 3 * e),
+                                             random_layer(hidden, ffn, 2, 16, 701 + 30 * l + 3 * e),
+                                             random_layer(ffn, hidden, 2, 16, 702 + 30 * l + 3 * e))) for e in range(E)]
+        gate = torch.nn.Linear(hidden, E, bias=False, dtype=torch.bfloat16, device=DEV)
+        gate.weight.data.copy_((0.5 * torch.randn(E, hidden, generator=g)).to(torch.bfloat16))
+        layers.append(DecoderLayerDecode(attn, ResidentMoe(_Cfg(hidden, ffn, E), l, gate, experts), lns[l + 1]))
+    embed = torch.randn(vocab, hidden, generator=g).to(torch.bfloat16).to(DEV)
+    head = (0.05 * torch.randn(vocab, hidden, generator=g)).to(torch.bfloat16).to(DEV)
+    return MixtralDecodeModel(embed, layers, lns[0], head), vocab
+
+
+def test_generate_sampling_and_multi_turn():
+    """The demo's generation settings (do_sample, temperature 0.9, top_p 0.9) and its multi-turn loop (the caches are
+    kept and the next turn is appended): sampled tokens are reproducible under a seeded generator, and a second
+    turn behind kept caches equals feeding the whole conversation from empty caches."""
+    model, vocab = _small_model()
+    p1, p2 = [5, 17, 250, 9, 33], [7, 120, 64]
+    out1 = model.generate(p1, 4)
+    out2 = model.generate([out1[-1]] + p2, 3, continue_cache=True)           # the last chosen token has not been fed yet
+    assert model.generate(p1 + out1 + p2, 3) == out2
+    assert model.generate(p1 + out1 + p2, 3, prefill=True, use_graph=False)[0] in range(vocab)
+    draws = []
+    for _ in range(2):
+        g = torch.Generator(device=DEV).manual_seed(11)
+        draws.append(model.generate(p1, 12, do_sample=True, temperature=0.9, top_p=0.9, generator=g))
+    assert draws[0] == draws[1] and len(draws[0]) == 12 and all(0 <= t < vocab for t in draws[0])
+    assert draws[0] != model.generate(p1, 12)                                 # flat random logits: sampling differs from greedy
+    eos = model.generate(p1, 12)[2]
+    assert model.generate(p1, 12, eos_token_id=eos)[-1] == eos and len(model.generate(p1, 12, eos_token_id=eos)) <= 3
