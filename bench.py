@@ -350,6 +350,11 @@ def run_moe(args):
     }))
 
 
+def scale_32(layers):
+    """Factor by which a time measured on `layers` layers is scaled to the 32-layer model."""
+    return 32.0 / layers
+
+
 def run_decode(args):
     """BASELINE configs[4](b) on one GPU: a Mixtral-8x7B-shaped decoder (32 layers unless --layers says
     otherwise, hidden 4096, 32 query / 8 KV heads of 128, RoPE theta 1e6, RMSNorm eps 1e-5, vocab 32000,
@@ -607,7 +612,7 @@ def run_decode(args):
             del bd
         clocks = sampler.stop() if sampler is not None else None
         # prompt processing through the same model: a 512-token prompt in one pass (informative, rank 0 only)
-        prefill_ms = None
+        prefill_ms, request = None, None
         if rank == 0 and args.context >= 512 and max_len > 512:
             prompt = torch.randint(0, V, (512,), generator=torch.Generator().manual_seed(3)).tolist()
             model.prefill(prompt)                                          # warm-up (allocations, scratch)
@@ -617,6 +622,17 @@ def run_decode(args):
             p1.record(stream)
             torch.cuda.synchronize(dev)
             prefill_ms = p0.elapsed_time(p1)
+            # BASELINE configs[4] as one request: a 512-token prompt in one pass, then 128 greedy tokens from the graph
+            if max_len >= 512 + 128 + 1 and not args.no_extras:
+                import time
+                torch.cuda.synchronize(dev)
+                t0 = time.perf_counter()
+                new = model.generate(prompt, 128, use_graph=True, prefill=True)
+                torch.cuda.synchronize(dev)
+                request_ms = (time.perf_counter() - t0) * 1e3
+                request = {"ms": request_ms, "new_tokens": len(new), "tokens_per_s": len(new) / (request_ms * 1e-3) / scale_32(L),
+                           "what": "generate(): 512-token prompt in one pass + 128 greedy tokens, wall clock, the chosen "
+                                   "token read back every step"}
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -669,6 +685,7 @@ def run_decode(args):
         "decode_batch8_configs4": batch8,
         "offload_configs4a": offload,
         "prefill_512_tokens_ms": prefill_ms,
+        "request_512_plus_128": request,
         "cpu_baseline": cpu,
         "e2e": {"value": world * 1e3 / (ms_e2e * scale), "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": 8,
                 "d2h_bytes_per_step": 8},
